@@ -1,0 +1,239 @@
+"""Expert-parallel MoE feed-forward layer with per-step load balancing, on native kernels.
+
+One forward does, entirely on the device and without any host read:
+
+  router (PyTorch)  ->  count + publish omega  ->  solve plan  ->  route units  ->  dispatch
+  token rows into the hosts' buffers  ->  pull replica weights  ->  grouped GEMM1 + SwiGLU  ->
+  grouped GEMM2 with rows scattered back to their source rank  ->  gate-weighted reduce.
+
+and the backward mirrors it (gradient dispatch with fused gate gradients, Wgrad/Dgrad grouped
+GEMMs with the activation gradient fused, owner-side reduction of replica weight gradients).
+This is the B200 counterpart of the reference's apply mode
+(eplb/integration/eplb_manager.py:905-1167 ``sync_free_moe_forward``, megatron_moe.py:156-215).
+
+Weight layout: every rank holds ``w_slots`` expert slots in symmetric memory.  Slots
+``[0, home_cap)`` are the experts this rank owns -- those *are* the parameters, the optimizer
+updates them in place -- and the remaining slots receive replicas chosen by the plan each step.
+Weights use the ``[out, in]`` layout: ``w1[slot]`` is ``[2F, H]`` (gate rows then up rows) and
+``w2[slot]`` is ``[H, F]`` (reference: eplb/integration/grouped_mlp.py:117-137).
+
+Weight gradients are written straight into ``param.grad`` (a view of the symmetric gradient
+slots), overwriting the previous content; replicas' contributions are added by the owner.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..core.config import EPLBConfig
+from ..core.problem import ProblemSpec
+from ..core.topology import Topology
+from ..ops.extension import load
+from ..parallel.symm import HeapLayout, SymmetricHeap
+from ..utils import profiling
+
+STATUS_NAMES = {0: "ok", 1: "barrier timeout", 2: "signal timeout", 3: "pipeline timeout", 4: "row overflow",
+                5: "bad argument"}
+
+
+@dataclass
+class MoEConfig:
+    hidden: int
+    ffn: int
+    num_experts: int
+    top_k: int
+    max_tokens: int  # tokens per rank per step
+    extra_slots: int = 2  # replica slots per rank on top of the owned experts
+    capacity_factor: float = 2.0  # receive-buffer rows as a multiple of this rank's units
+    num_domains: int = 1
+    intra_cost: int = 1
+    inter_cost: int = 8
+    router_dtype: torch.dtype = torch.float32
+    normalize_topk: bool = True
+
+
+def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
+    """Symmetric regions of one layer (identical on every rank)."""
+    E, H, F = cfg.num_experts, cfg.hidden, cfg.ffn
+    home_cap = -(-E // world)
+    w_slots = home_cap + (cfg.extra_slots if world > 1 else 0)
+    U = cfg.max_tokens * cfg.top_k
+    cap = row_capacity(cfg, world)
+    lay = HeapLayout()
+    lay.add("omega", (world, E), torch.int32)
+    lay.add("signals", (16,), torch.int32)
+    lay.add("xbuf", (cap, H), torch.bfloat16)
+    lay.add("meta", (cap, 2), torch.int32)
+    lay.add("ybuf", (U, H), torch.bfloat16)
+    lay.add("dybuf", (cap, H), torch.bfloat16)
+    lay.add("dxbuf", (U, H), torch.bfloat16)
+    lay.add("w1", (w_slots, 2 * F, H), torch.bfloat16)
+    lay.add("w2", (w_slots, H, F), torch.bfloat16)
+    lay.add("gw1", (w_slots, 2 * F, H), torch.bfloat16)
+    lay.add("gw2", (w_slots, H, F), torch.bfloat16)
+    return lay
+
+
+def row_capacity(cfg: MoEConfig, world: int) -> int:
+    U = cfg.max_tokens * cfg.top_k
+    home_cap = -(-cfg.num_experts // world)
+    w_slots = home_cap + (cfg.extra_slots if world > 1 else 0)
+    rows = int(U * (cfg.capacity_factor if world > 1 else 1.0)) + 128 * w_slots
+    return (rows + 127) // 128 * 128
+
+
+class _FusedMoEFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, tokens, topk_idx, topk_prob, layer):
+        n = tokens.shape[0]
+        out = torch.empty_like(tokens)
+        layer.rt.forward(tokens.data_ptr(), topk_idx.data_ptr(), topk_prob.data_ptr(), out.data_ptr(), n)
+        ctx.layer = layer
+        ctx.save_for_backward(topk_prob)
+        ctx.n = n
+        ctx.keep = (tokens, topk_idx)  # inputs stay alive until the enqueued kernels have read them
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        layer = ctx.layer
+        (topk_prob,) = ctx.saved_tensors
+        dout = dout.contiguous()
+        dtokens = torch.empty_like(dout)
+        dprob = torch.empty_like(topk_prob)
+        layer.rt.backward(dout.data_ptr(), topk_prob.data_ptr(), dtokens.data_ptr(), dprob.data_ptr(), ctx.n)
+        layer.bind_grads()
+        return dtokens, None, dprob, None
+
+
+class FusedMoE(nn.Module):
+    """One MoE FFN layer of an expert-parallel group (``world`` ranks; this object is rank ``rank``).
+
+    ``heap`` is a :class:`SymmetricHeap` built from :func:`heap_layout`; with the ``local`` backend
+    several ``FusedMoE`` objects (one per logical rank) can share one heap in a single process.
+    """
+
+    def __init__(self, cfg: MoEConfig, heap: SymmetricHeap, rank: int, world: int, *,
+                 solver_cfg: Optional[EPLBConfig] = None, multi_rank_sync: bool = True, seed: int = 0) -> None:
+        super().__init__()
+        self.cfg, self.heap, self.rank, self.world = cfg, heap, int(rank), int(world)
+        self.solver_cfg = solver_cfg or EPLBConfig()
+        dev = heap.device
+        self.device = dev
+        E, H, F, K = cfg.num_experts, cfg.hidden, cfg.ffn, cfg.top_k
+        if E % world:
+            raise ValueError("num_experts must be divisible by the expert-parallel world size")
+        self.home_cap = E // world
+        self.w_slots = self.home_cap + (cfg.extra_slots if world > 1 else 0)
+        self.n_slot_plan = self.w_slots
+        self.row_capacity = row_capacity(cfg, world)
+        self.max_units = cfg.max_tokens * K
+        self.topo = Topology.logical(world, cfg.num_domains, cfg.intra_cost, cfg.inter_cost)
+        wbytes = 3 * H * F * 2
+        self.spec = ProblemSpec.contiguous_main_placement(E, world, wbytes, H * 2, self.n_slot_plan)
+
+        # ---- parameters: router + the owned expert slots (views of symmetric memory)
+        g = torch.Generator(device="cpu").manual_seed(1234 + seed)
+        self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(dev, cfg.router_dtype))
+        w1_all, w2_all = heap.tensor("w1", rank), heap.tensor("w2", rank)
+        ge = torch.Generator(device="cpu")
+        for i in range(self.home_cap):
+            e = rank * self.home_cap + i
+            ge.manual_seed(10_000 + 7919 * seed + e)  # weights depend on the expert id only
+            w1_all[i].copy_((torch.randn(2 * F, H, generator=ge) * 0.02).to(torch.bfloat16))
+            w2_all[i].copy_((torch.randn(H, F, generator=ge) * 0.02).to(torch.bfloat16))
+        self.w1 = nn.Parameter(w1_all[: self.home_cap])
+        self.w2 = nn.Parameter(w2_all[: self.home_cap])
+        self._gw1 = heap.tensor("gw1", rank)[: self.home_cap]
+        self._gw2 = heap.tensor("gw2", rank)[: self.home_cap]
+        self.router_bias: Optional[torch.Tensor] = None  # additive logit skew (synthetic workloads)
+
+        # ---- local state
+        i32 = dict(dtype=torch.int32, device=dev)
+        R = world
+        self.loc: Dict[str, torch.Tensor] = {
+            "dom": self.topo.domain_of_rank.to(**i32), "cost": self.topo.cost.to(**i32).contiguous(),
+            "main_rank": self.spec.main_rank.to(**i32), "weight_bytes": self.spec.weight_bytes.to(dev),
+            "home_index": (torch.arange(E) % self.home_cap).to(**i32),
+            "x": torch.zeros((E, R), dtype=torch.int8, device=dev), "q": torch.zeros((R, E, R), **i32),
+            "erl": torch.zeros((E, R), **i32), "rank_load": torch.zeros(R, **i32),
+            "slot_used": torch.zeros(R, **i32), "stuck": torch.zeros(R, dtype=torch.uint8, device=dev),
+            "theta": torch.zeros(1, dtype=torch.int64, device=dev),
+            "control": torch.zeros(3, dtype=torch.int64, device=dev), "sync": torch.zeros(2, **i32),
+            "status": torch.zeros(4, **i32), "epochs": torch.zeros(8, **i32),
+            "slot_of": torch.full((E, R), -1, **i32), "row_base": torch.full((E, R), -1, **i32),
+            "group_expert": torch.full((self.w_slots,), -1, **i32), "group_wslot": torch.zeros(self.w_slots, **i32),
+            "group_off": torch.zeros(self.w_slots + 1, **i32), "group_rows": torch.zeros(self.w_slots, **i32),
+            "totals": torch.zeros(2, **i32),
+            "unit_dst": torch.zeros(self.max_units, **i32), "unit_row": torch.zeros(self.max_units, **i32),
+            "hbuf": torch.zeros((self.row_capacity, 2 * F), dtype=torch.bfloat16, device=dev),
+            "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
+        }
+        ptrs = {k: v.data_ptr() for k, v in self.loc.items()}
+        for name in ("omega", "signals", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"):
+            ptrs[name] = heap.address(name, rank)
+        self._tables: List[torch.Tensor] = []
+        for name, key in (("omega", "omega_ptrs"), ("signals", "signal_ptrs"), ("xbuf", "xbuf_ptrs"),
+                          ("meta", "meta_ptrs"), ("ybuf", "ybuf_ptrs"), ("dybuf", "dybuf_ptrs"),
+                          ("dxbuf", "dxbuf_ptrs"), ("w1", "w1_ptrs"), ("w2", "w2_ptrs"), ("gw1", "gw1_ptrs"),
+                          ("gw2", "gw2_ptrs")):
+            t = heap.peer_ptrs(name)
+            self._tables.append(t)
+            ptrs[key] = t.data_ptr()
+        sc = self.solver_cfg
+        iters = sc.device_stage2_iters
+        props = torch.cuda.get_device_properties(dev)
+        rt_cfg = dict(R=R, me=rank, E=E, H=H, F=F, topk=K, w_slots=self.w_slots, home_cap=self.home_cap,
+                      n_slot_plan=self.n_slot_plan, row_capacity=self.row_capacity, max_units=self.max_units,
+                      D=cfg.num_domains, u_min=sc.u_min, iters=iters, patience=sc.stage2_stagnation_patience,
+                      allow_cross=int(sc.allow_cross_domain),
+                      probe=int(sc.stage2_patience_all_scales and iters > sc.stage2_stagnation_patience + 1),
+                      s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync))
+        self.rt = load().MoeRuntime(rt_cfg, ptrs)
+        self.bind_grads()
+
+    # ---- gradients ---------------------------------------------------------
+    def bind_grads(self) -> None:
+        """Point ``.grad`` of the expert parameters at the symmetric gradient slots."""
+        if self.w1.grad is None or self.w1.grad.data_ptr() != self._gw1.data_ptr():
+            self.w1.grad = self._gw1
+        if self.w2.grad is None or self.w2.grad.data_ptr() != self._gw2.data_ptr():
+            self.w2.grad = self._gw2
+
+    # ---- routing -----------------------------------------------------------
+    def route_tokens(self, tokens: torch.Tensor):
+        """fp32 router: logits = x . W_r^T (+ bias), top-k, softmax over the selected logits."""
+        with profiling.record("apply/route", time_it=True, device=tokens.device):
+            logits = tokens.to(self.router.dtype) @ self.router.t()
+            if self.router_bias is not None:
+                logits = logits + self.router_bias
+            top_val, top_idx = torch.topk(logits, self.cfg.top_k, dim=-1)
+            prob = torch.softmax(top_val.float(), dim=-1) if self.cfg.normalize_topk else torch.sigmoid(top_val.float())
+        return top_idx.contiguous(), prob.contiguous()
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        if tokens.dtype != torch.bfloat16 or tokens.dim() != 2 or tokens.shape[1] != self.cfg.hidden:
+            raise ValueError("tokens must be bf16 [num_tokens, hidden]")
+        if tokens.shape[0] > self.cfg.max_tokens:
+            raise ValueError("more tokens than MoEConfig.max_tokens")
+        tokens = tokens.contiguous()
+        top_idx, prob = self.route_tokens(tokens)
+        return _FusedMoEFunction.apply(tokens, top_idx, prob, self)
+
+    # ---- introspection (these read device memory: debugging / tests only) ---
+    def check_status(self) -> None:
+        st = self.loc["status"].tolist()
+        if st[0] != 0:
+            raise RuntimeError(f"MoE runtime status: {STATUS_NAMES.get(st[0], st[0])} (site {st[1]}, detail {st[2]})")
+
+    def last_plan(self):
+        from ..core.plan import Plan
+
+        return Plan(self.loc["x"].clone(), self.loc["q"].to(torch.int64), self.loc["theta"][0].clone())
+
+    def rank_loads(self) -> torch.Tensor:
+        return self.loc["rank_load"].clone()

@@ -1,0 +1,246 @@
+// Python bindings.  Kernels take raw device pointers; tensors are only unwrapped here.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <string>
+
+#include "grouped_gemm.h"
+#include "route.h"
+#include "runtime.h"
+#include "solver.h"
+
+namespace py = pybind11;
+using epb::LayerConfig;
+using epb::MoeRuntime;
+
+namespace {
+
+cudaStream_t current_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+void cuda_check(cudaError_t e, const char* what) {
+  TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
+}
+
+template <typename T>
+T* dptr(const torch::Tensor& t, const char* name, c10::ScalarType st) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+  TORCH_CHECK(t.scalar_type() == st, name, " has the wrong dtype");
+  return reinterpret_cast<T*>(t.data_ptr());
+}
+
+int get_int(const py::dict& d, const char* key, int fallback) {
+  return d.contains(key) ? d[key].cast<int>() : fallback;
+}
+
+LayerConfig config_from_dict(const py::dict& d) {
+  LayerConfig c;
+  c.R = get_int(d, "R", 1);
+  c.me = get_int(d, "me", 0);
+  c.E = get_int(d, "E", 0);
+  c.H = get_int(d, "H", 0);
+  c.F = get_int(d, "F", 0);
+  c.topk = get_int(d, "topk", 1);
+  c.w_slots = get_int(d, "w_slots", 0);
+  c.home_cap = get_int(d, "home_cap", 0);
+  c.n_slot_plan = get_int(d, "n_slot_plan", 0);
+  c.row_capacity = get_int(d, "row_capacity", 0);
+  c.max_units = get_int(d, "max_units", 0);
+  c.D = get_int(d, "D", 1);
+  c.u_min = get_int(d, "u_min", 1);
+  c.iters = get_int(d, "iters", 64);
+  c.patience = get_int(d, "patience", 8);
+  c.allow_cross = get_int(d, "allow_cross", 1);
+  c.probe = get_int(d, "probe", 0);
+  c.s_tok = d.contains("s_tok") ? d["s_tok"].cast<int64_t>() : 0;
+  c.num_sms = get_int(d, "num_sms", 148);
+  c.multi_rank_sync = get_int(d, "multi_rank_sync", 1);
+  return c;
+}
+
+// Stand-alone solve on tensors (the library API path).  All tensors live on the same device.
+void solve_plan(torch::Tensor omega, torch::Tensor dom, torch::Tensor cost, torch::Tensor main_rank,
+                torch::Tensor weight_bytes, int64_t s_tok, int64_t D, int64_t n_slot, int64_t u_min, int64_t iters,
+                int64_t patience, bool allow_cross, bool probe, torch::Tensor x, torch::Tensor q, torch::Tensor erl,
+                torch::Tensor rank_load, torch::Tensor slot_used, torch::Tensor stuck, torch::Tensor theta,
+                torch::Tensor control, torch::Tensor sync, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(omega.device());
+  epb::SolverParams p{};
+  p.omega = dptr<const int32_t>(omega, "omega", torch::kInt32);
+  p.dom = dptr<const int32_t>(dom, "dom", torch::kInt32);
+  p.cost = dptr<const int32_t>(cost, "cost", torch::kInt32);
+  p.main_rank = dptr<const int32_t>(main_rank, "main_rank", torch::kInt32);
+  p.weight_bytes = dptr<const int64_t>(weight_bytes, "weight_bytes", torch::kInt64);
+  p.s_tok = s_tok;
+  p.R = (int)omega.size(0);
+  p.E = (int)omega.size(1);
+  TORCH_CHECK(p.R >= 1 && p.R <= 1024, "device solver requires 1 <= R <= 1024");
+  TORCH_CHECK(p.E >= 1, "device solver requires E > 0");
+  TORCH_CHECK(D >= 1 && D <= p.R, "device solver requires 1 <= num_domains <= R");
+  TORCH_CHECK(n_slot > 0 && u_min > 0 && iters > 0 && patience > 0, "solver knobs must be positive");
+  p.D = (int)D;
+  p.n_slot = (int)n_slot;
+  p.u_min = (int)u_min;
+  p.iters = (int)iters;
+  p.patience = (int)patience;
+  p.allow_cross = allow_cross ? 1 : 0;
+  p.probe = probe ? 1 : 0;
+  p.x = dptr<int8_t>(x, "x", torch::kInt8);
+  p.q = dptr<int32_t>(q, "q", torch::kInt32);
+  p.erl = dptr<int32_t>(erl, "erl", torch::kInt32);
+  p.rank_load = dptr<int32_t>(rank_load, "rank_load", torch::kInt32);
+  p.slot_used = dptr<int32_t>(slot_used, "slot_used", torch::kInt32);
+  p.stuck = dptr<unsigned char>(stuck, "stuck", torch::kUInt8);
+  p.theta = dptr<int64_t>(theta, "theta", torch::kInt64);
+  p.control = dptr<int64_t>(control, "control", torch::kInt64);
+  p.sync = reinterpret_cast<unsigned*>(dptr<int32_t>(sync, "sync", torch::kInt32));
+  p.status = dptr<int>(status, "status", torch::kInt32);
+  epb::RankTables t{};
+  t.me = -1;
+  cuda_check(epb::launch_solver(p, t, current_stream()), "launch_solver");
+}
+
+// Stand-alone grouped GEMM on tensors (tests and generic use).
+//   mode kPlain/kFwd2: C[T, N] = A[T, K] . W[slot]^T with W [S, N, K]
+//   mode kFwd1:        h[T, 2N], act[T, N] from A[T, K], W [S, 2N, K]
+//   mode kDgrad1:      C[T, N] = A[T, K] . W[slot] with W [S, K, N]
+//   mode kDgrad2:      h[T, 2N] updated in place from A = dY[T, K], W [S, K, N]
+//   mode kWgrad:       out[S, M_out, N] = P[T, M_out]^T Q[T, N] per group
+void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor out0, c10::optional<torch::Tensor> out1,
+                  torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor group_wslot, torch::Tensor totals,
+                  torch::Tensor status, int64_t num_sms) {
+  const c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "bf16 operands only");
+  TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && out0.is_contiguous(), "operands must be contiguous");
+  epb::GemmArgs g{};
+  g.mode = (int)mode;
+  g.group_off = dptr<const int32_t>(group_off, "group_off", torch::kInt32);
+  g.group_rows = dptr<const int32_t>(group_rows, "group_rows", torch::kInt32);
+  g.group_wslot = dptr<const int32_t>(group_wslot, "group_wslot", torch::kInt32);
+  g.totals = dptr<const int32_t>(totals, "totals", torch::kInt32);
+  g.n_groups_cap = (int)group_rows.size(0);
+  g.row_capacity = (int)a.size(0);
+  g.status = dptr<int>(status, "status", torch::kInt32);
+  g.out0 = out0.data_ptr();
+  g.out1 = out1.has_value() ? out1->data_ptr() : nullptr;
+  CUtensorMap tmA, tmB;
+  const uint64_t T = a.size(0);
+  bool ok = true;
+  switch (mode) {
+    case epb::kPlain:
+    case epb::kFwd2:
+      g.N = (int)b.size(1);
+      g.K = (int)a.size(1);
+      ok = epb::make_tmap_2d(&tmA, a.data_ptr(), T, a.size(1), 64, 128) &&
+           epb::make_tmap_3d(&tmB, b.data_ptr(), b.size(0), b.size(1), b.size(2), 64, 128);
+      break;
+    case epb::kFwd1:
+      g.N = (int)b.size(1) / 2;
+      g.K = (int)a.size(1);
+      ok = epb::make_tmap_2d(&tmA, a.data_ptr(), T, a.size(1), 64, 128) &&
+           epb::make_tmap_3d(&tmB, b.data_ptr(), b.size(0), b.size(1), b.size(2), 64, 128);
+      break;
+    case epb::kDgrad1:
+    case epb::kDgrad2:
+      g.N = (int)b.size(2);
+      g.K = (int)a.size(1);
+      ok = epb::make_tmap_2d(&tmA, a.data_ptr(), T, a.size(1), 64, 128) &&
+           epb::make_tmap_3d(&tmB, b.data_ptr(), b.size(0), b.size(1), b.size(2), 64, 64);
+      break;
+    case epb::kWgrad:
+      g.N = (int)b.size(1);
+      g.M_out = (int)a.size(1);
+      ok = epb::make_tmap_2d(&tmA, a.data_ptr(), T, a.size(1), 64, 64) &&
+           epb::make_tmap_2d(&tmB, b.data_ptr(), b.size(0), b.size(1), 64, 64);
+      break;
+    default:
+      TORCH_CHECK(false, "unknown grouped GEMM mode");
+  }
+  TORCH_CHECK(ok, "cuTensorMapEncodeTiled failed");
+  cuda_check(epb::launch_grouped_gemm(tmA, tmB, g, (int)num_sms, current_stream()), "launch_grouped_gemm");
+}
+
+void wait_probe(torch::Tensor flag, int64_t target, int64_t budget_ns, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(flag.device());
+  cuda_check(epb::launch_wait_probe(reinterpret_cast<const unsigned*>(dptr<int32_t>(flag, "flag", torch::kInt32)),
+                                    (unsigned)target, (unsigned long long)budget_ns,
+                                    dptr<int>(status, "status", torch::kInt32), current_stream()),
+             "launch_wait_probe");
+}
+
+// ---- symmetric heap over CUDA IPC: one cudaMalloc per rank, mapped into every peer process
+py::tuple ipc_alloc(int64_t nbytes) {
+  void* p = nullptr;
+  cuda_check(cudaMalloc(&p, (size_t)nbytes), "cudaMalloc(symmetric heap)");
+  cuda_check(cudaMemset(p, 0, (size_t)nbytes), "cudaMemset(symmetric heap)");
+  cudaIpcMemHandle_t h;
+  cuda_check(cudaIpcGetMemHandle(&h, p), "cudaIpcGetMemHandle");
+  return py::make_tuple((uint64_t)(uintptr_t)p, py::bytes(reinterpret_cast<const char*>(&h), sizeof(h)));
+}
+uint64_t ipc_open(py::bytes handle) {
+  std::string raw = handle;
+  TORCH_CHECK(raw.size() == sizeof(cudaIpcMemHandle_t), "bad IPC handle size");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, raw.data(), sizeof(h));
+  void* p = nullptr;
+  cuda_check(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess), "cudaIpcOpenMemHandle");
+  return (uint64_t)(uintptr_t)p;
+}
+void ipc_close(uint64_t p) { cuda_check(cudaIpcCloseMemHandle(reinterpret_cast<void*>((uintptr_t)p)), "cudaIpcCloseMemHandle"); }
+void ipc_free(uint64_t p) { cuda_check(cudaFree(reinterpret_cast<void*>((uintptr_t)p)), "cudaFree"); }
+torch::Tensor tensor_from_ptr(uint64_t p, int64_t nbytes, int64_t device) {
+  auto opts = torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, (int)device);
+  return torch::from_blob(reinterpret_cast<void*>((uintptr_t)p), {nbytes}, [](void*) {}, opts);
+}
+
+const void* cp(uint64_t a) { return reinterpret_cast<const void*>(static_cast<uintptr_t>(a)); }
+void* mp(uint64_t a) { return reinterpret_cast<void*>(static_cast<uintptr_t>(a)); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.doc() = "ep_balance_b200 native kernels (sm_100a)";
+  m.def("solve_plan", &solve_plan);
+  m.def("grouped_gemm", &grouped_gemm);
+  m.def("wait_probe", &wait_probe);
+  m.def("ipc_alloc", &ipc_alloc);
+  m.def("ipc_open", &ipc_open);
+  m.def("ipc_close", &ipc_close);
+  m.def("ipc_free", &ipc_free);
+  m.def("tensor_from_ptr", &tensor_from_ptr);
+
+  py::class_<MoeRuntime>(m, "MoeRuntime")
+      .def(py::init([](const py::dict& cfg, const std::map<std::string, uint64_t>& ptrs) {
+        return new MoeRuntime(config_from_dict(cfg), ptrs);
+      }))
+      .def("launches", &MoeRuntime::launches)
+      .def("reset_launches", &MoeRuntime::reset_launches)
+      .def("publish", [](MoeRuntime& r, uint64_t idx, int u) { r.publish((const int64_t*)cp(idx), u, current_stream()); })
+      .def("solve", [](MoeRuntime& r) { r.solve(current_stream()); })
+      .def("route", [](MoeRuntime& r, uint64_t idx, int u) { r.route((const int64_t*)cp(idx), u, current_stream()); })
+      .def("dispatch_tokens", [](MoeRuntime& r, uint64_t tok, int u) { r.dispatch_tokens(cp(tok), u, current_stream()); })
+      .def("pull_weights", [](MoeRuntime& r) { r.pull_weights(current_stream()); })
+      .def("barrier", [](MoeRuntime& r, int slot) { r.barrier(slot, current_stream()); })
+      .def("gemm1", [](MoeRuntime& r) { r.gemm1(current_stream()); })
+      .def("gemm2", [](MoeRuntime& r) { r.gemm2(current_stream()); })
+      .def("reduce_out", [](MoeRuntime& r, uint64_t prob, uint64_t out, int n) {
+        r.reduce_out((const float*)cp(prob), mp(out), n, current_stream());
+      })
+      .def("dispatch_grads", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dprob, int u) {
+        r.dispatch_grads(cp(dout), (const float*)cp(prob), (float*)mp(dprob), u, current_stream());
+      })
+      .def("wgrad2", [](MoeRuntime& r) { r.wgrad2(current_stream()); })
+      .def("dgrad2", [](MoeRuntime& r) { r.dgrad2(current_stream()); })
+      .def("wgrad1", [](MoeRuntime& r) { r.wgrad1(current_stream()); })
+      .def("dgrad1", [](MoeRuntime& r) { r.dgrad1(current_stream()); })
+      .def("reduce_dtokens", [](MoeRuntime& r, uint64_t dt, int n) { r.reduce_dtokens(mp(dt), n, current_stream()); })
+      .def("reduce_weight_grads", [](MoeRuntime& r) { r.reduce_weight_grads(current_stream()); })
+      .def("forward", [](MoeRuntime& r, uint64_t tok, uint64_t idx, uint64_t prob, uint64_t out, int n) {
+        r.forward(cp(tok), (const int64_t*)cp(idx), (const float*)cp(prob), mp(out), n, current_stream());
+      })
+      .def("backward", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dtok, uint64_t dprob, int n) {
+        r.backward(cp(dout), (const float*)cp(prob), mp(dtok), (float*)mp(dprob), n, current_stream());
+      });
+}

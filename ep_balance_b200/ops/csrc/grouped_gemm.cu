@@ -1,0 +1,583 @@
+// Ragged grouped GEMM for sm_100a: TMA-fed shared-memory tiles, tcgen05.mma issued by one thread,
+// accumulators in tensor memory, epilogue warps reading them back with tcgen05.ld.
+//
+// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues MMAs, warps 2-5 run the
+// epilogue (each owns one 32-lane quarter of TMEM).  A 4-stage smem ring (A 16 KB + B 32 KB per
+// stage) feeds 128x256x16 UMMAs; two 256-column accumulators in TMEM let the epilogue of tile i
+// overlap the main loop of tile i+1.  The kernel is persistent: CTA c processes tiles
+// c, c+grid, ... of a tile list derived on device from the plan's group table.
+//
+// This replaces torch._grouped_mm / torch.bmm plus the unfused activation, slot sort, index_add
+// and activation-gradient kernels of the reference (eplb/integration/grouped_mlp.py:88-137,
+// 219-236; overlap.py:368-408; manual_block.py:184-221, 293-342).
+//
+// Every mbarrier wait is bounded; on timeout the CTA records a status, stops issuing work,
+// lets its outstanding copies land, frees its tensor memory and returns.
+#include "grouped_gemm.h"
+
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace epb {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;            // 16 KB
+constexpr int B_BYTES = BN * BK * 2;            // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int TMEM_COLS = 512;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_GROUPS = 320;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: returns false (and raises the CTA's abort flag) when the budget is spent.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int site) {
+  unsigned long long t0 = 0;
+  for (unsigned spin = 0;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 1023u) == 1023u) {
+      if (*abort_flag) return false;
+      unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitBudgetNs) {
+        *abort_flag = 1;
+        set_status(status, kStatusPipeTimeout, site, (int)blockIdx.x);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier once every MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------- descriptors
+// Shared-memory matrix descriptor, 128-byte swizzle, tile base 1024-byte aligned.
+//   bits  0-13 start address >> 4      bits 16-29 leading byte offset >> 4
+//   bits 32-45 stride byte offset >> 4 bits 46-47 version (1 on sm_100)   bits 61-63 layout (2 = SW128)
+// K-major:  rows are 128 B apart, 8-row groups are SBO = 1024 B apart; LBO is unused.
+// MN-major: 64 contiguous MN elements per 128-B row of k; 8-k groups are SBO = 1024 B apart and
+//           the next 64 MN elements start LBO = BK*128 B = 8192 B further (one TMA box each).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, M = 128.
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+// ---------------------------------------------------------------- tiles
+struct Tile {
+  int g, mt, nt;
+  int rows;      // real rows of the group
+  int row0;      // first buffer row of the group
+  int wslot;
+  int kblocks;
+};
+
+struct Shape {
+  int n_groups, n_tiles_n, tile_n, m_tiles_fixed, kblocks_fixed;
+};
+
+template <int kMode>
+__device__ __forceinline__ Shape make_shape(const GemmArgs& a) {
+  Shape s;
+  int ng = a.totals[1];
+  s.n_groups = ng < a.n_groups_cap ? ng : a.n_groups_cap;
+  s.tile_n = kMode == kFwd1 ? 128 : BN;
+  s.n_tiles_n = ceil_div(a.N, s.tile_n);
+  s.m_tiles_fixed = kMode == kWgrad ? ceil_div(a.M_out, BM) : 0;
+  s.kblocks_fixed = kMode == kWgrad ? 0 : ceil_div(a.K, BK);
+  return s;
+}
+
+template <int kMode>
+__device__ __forceinline__ bool find_tile(const GemmArgs& a, const Shape& s, const int* tile_prefix, int t, Tile& out) {
+  int g = 0;
+  while (g < s.n_groups && t >= tile_prefix[g + 1]) ++g;
+  if (g >= s.n_groups) return false;
+  const int local = t - tile_prefix[g];
+  out.g = g;
+  out.mt = local / s.n_tiles_n;
+  out.nt = local - out.mt * s.n_tiles_n;
+  out.rows = a.group_rows[g];
+  out.row0 = a.group_off[g];
+  out.wslot = a.group_wslot[g];
+  out.kblocks = kMode == kWgrad ? ceil_div(out.rows, BK) : s.kblocks_fixed;
+  return true;
+}
+
+// ---------------------------------------------------------------- epilogue helpers
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
+}
+__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// Store 32 consecutive bf16 (64 B) given as 32 fp32 register values.
+__device__ __forceinline__ void store32(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 v;
+    v.x = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
+    v.y = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
+    v.z = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
+    v.w = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
+    d4[i] = v;
+  }
+}
+__device__ __forceinline__ void store32_zero(__nv_bfloat16* dst) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) d4[i] = make_uint4(0, 0, 0, 0);
+}
+
+// ---------------------------------------------------------------- kernel
+template <int kMode>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs args) {
+  constexpr bool kAMn = kMode == kWgrad;
+  constexpr bool kBMn = kMode == kWgrad || kMode == kDgrad2 || kMode == kDgrad1;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;  // [2]
+  uint64_t* acc_empty = acc_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* tile_prefix = abort_flag + 1;  // [MAX_GROUPS + 1]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const Shape shape = make_shape<kMode>(args);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 4);
+    }
+    *abort_flag = 0;
+    int acc = 0;
+    tile_prefix[0] = 0;
+    for (int g = 0; g < shape.n_groups; ++g) {
+      int mt = kMode == kWgrad ? shape.m_tiles_fixed : ceil_div(args.group_rows[g], BM);
+      acc += mt * shape.n_tiles_n;
+      tile_prefix[g + 1] = acc;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = tile_prefix[shape.n_groups];
+  volatile int* abort_v = abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      Tile t;
+      for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x) {
+        if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
+        const int arow = t.row0 + t.mt * BM;
+        for (int kb = 0; kb < t.kblocks; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v, args.status, 1)) break;
+          uint8_t* sA = tiles + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+          if (kMode == kWgrad) {
+            const int krow = t.row0 + kb * BK;
+            for (int i = 0; i < 2; ++i) tma_load_2d(sA + i * 8192, &tmA, &full_bar[stage], t.mt * BM + 64 * i, krow);
+            for (int j = 0; j < 4; ++j) tma_load_2d(sB + j * 8192, &tmB, &full_bar[stage], t.nt * BN + 64 * j, krow);
+          } else {
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, arow);
+            if (kMode == kFwd1) {
+              tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, t.nt * 128, t.wslot);
+              tma_load_3d(sB + 16384, &tmB, &full_bar[stage], kb * BK, args.N + t.nt * 128, t.wslot);
+            } else if (kBMn) {
+              for (int j = 0; j < 4; ++j)
+                tma_load_3d(sB + j * 8192, &tmB, &full_bar[stage], t.nt * BN + 64 * j, kb * BK, t.wslot);
+            } else {
+              tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, t.nt * BN, t.wslot);
+              tma_load_3d(sB + 16384, &tmB, &full_bar[stage], kb * BK, t.nt * BN + 128, t.wslot);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int local = 0;
+      Tile t;
+      for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x, ++local) {
+        if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
+        const int buf = local & 1;
+        if (!mbar_wait(&acc_empty[buf], acc_phase[buf] ^ 1u, abort_v, args.status, 2)) break;
+        acc_phase[buf] ^= 1u;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        // columns the MMA must produce for this tile (multiple of 16, at most 256)
+        int ncols = BN;
+        if (kMode != kFwd1) {
+          int left = args.N - t.nt * BN;
+          if (left < BN) ncols = round_up(left, 16);
+        }
+        const uint32_t idesc = make_idesc(kAMn, kBMn, ncols);
+        bool failed = false;
+        for (int kb = 0; kb < t.kblocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_v, args.status, 3)) {
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(tiles + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+          const uint64_t da = kAMn ? make_desc(sA, 8192, 1024) : make_desc(sA, 16, 1024);
+          const uint64_t db = kBMn ? make_desc(sB, 8192, 1024) : make_desc(sB, 16, 1024);
+          constexpr uint32_t a_step = kAMn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+          constexpr uint32_t b_step = kBMn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma_bf16(tmem_d, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), idesc, (kb | k) ? 1u : 0u);
+          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (failed) break;
+        umma_commit(&acc_full[buf]);  // accumulator ready for the epilogue
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    uint32_t acc_phase[2] = {0, 0};
+    int local = 0;
+    Tile t;
+    __nv_bfloat16* out0 = reinterpret_cast<__nv_bfloat16*>(args.out0);
+    __nv_bfloat16* out1 = reinterpret_cast<__nv_bfloat16*>(args.out1);
+    for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x, ++local) {
+      if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
+      const int buf = local & 1;
+      if (!mbar_wait(&acc_full[buf], acc_phase[buf], abort_v, args.status, 4)) break;
+      acc_phase[buf] ^= 1u;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      const int r_in_tile = quarter * 32 + lane;
+      uint32_t v[32];
+
+      if (kMode == kFwd1) {
+        const int row_in_group = t.mt * BM + r_in_tile;
+        const size_t row = (size_t)t.row0 + row_in_group;  // rows up to the padded end exist in the buffers
+        const bool in_buf = row < (size_t)args.row_capacity;
+        const bool real = row_in_group < t.rows && in_buf;
+        const int F = args.N;
+        __nv_bfloat16* hrow = out0 + row * (size_t)(2 * F) + t.nt * 128;
+        __nv_bfloat16* arow = out1 + row * (size_t)F + t.nt * 128;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t up[32];
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld32(taddr + 128 + c * 32, up);
+          tmem_ld_wait();
+          if (real) {
+            store32(hrow + c * 32, v);
+            store32(hrow + F + c * 32, up);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              // activation computed from the bf16-rounded pre-activations that backward will see
+              float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
+              float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[i])));
+              v[i] = __float_as_uint(g * sigmoidf_fast(g) * u);
+            }
+            store32(arow + c * 32, v);
+          } else if (in_buf) {
+            store32_zero(hrow + c * 32);
+            store32_zero(hrow + F + c * 32);
+            store32_zero(arow + c * 32);
+          }
+        }
+      } else if (kMode == kDgrad2) {
+        const int row_in_group = t.mt * BM + r_in_tile;
+        const size_t row = (size_t)t.row0 + row_in_group;
+        const bool in_buf = row < (size_t)args.row_capacity;
+        const bool real = row_in_group < t.rows && in_buf;
+        const int F = args.N;
+        __nv_bfloat16* hrow = out0 + row * (size_t)(2 * F);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = t.nt * BN + c * 32;
+          if (col >= F) break;
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (real) {
+            uint4* gp = reinterpret_cast<uint4*>(hrow + col);
+            uint4* up = reinterpret_cast<uint4*>(hrow + F + col);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 gv = gp[i], uv = up[i], dg, du;
+              uint32_t* gs = &gv.x;
+              uint32_t* us = &uv.x;
+              uint32_t* dgs = &dg.x;
+              uint32_t* dus = &du.x;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 g2 = unpack_bf16(gs[j]), u2 = unpack_bf16(us[j]);
+                float d0 = __uint_as_float(v[8 * i + 2 * j]), d1 = __uint_as_float(v[8 * i + 2 * j + 1]);
+                float s0 = sigmoidf_fast(g2.x), s1 = sigmoidf_fast(g2.y);
+                // d/dg [g*s(g)] = s + g*s*(1-s)
+                dgs[j] = pack_bf16(d0 * u2.x * (s0 + g2.x * s0 * (1.f - s0)), d1 * u2.y * (s1 + g2.y * s1 * (1.f - s1)));
+                dus[j] = pack_bf16(d0 * g2.x * s0, d1 * g2.y * s1);
+              }
+              gp[i] = dg;
+              up[i] = du;
+            }
+          } else if (in_buf) {
+            store32_zero(hrow + col);
+            store32_zero(hrow + F + col);
+          }
+        }
+      } else if (kMode == kWgrad) {
+        const int m = t.mt * BM + r_in_tile;
+        const bool real = m < args.M_out;
+        __nv_bfloat16* orow = out0 + ((size_t)t.wslot * args.M_out + (real ? m : 0)) * (size_t)args.N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = t.nt * BN + c * 32;
+          if (col >= args.N) break;
+          if (t.kblocks > 0) {
+            tmem_ld32(taddr + c * 32, v);
+            tmem_ld_wait();
+            if (real) store32(orow + col, v);
+          } else if (real) {
+            store32_zero(orow + col);  // an expert that received no rows has a zero gradient
+          }
+        }
+      } else {
+        // kFwd2 / kDgrad1 / kPlain: plain rows, optionally scattered to the unit's source rank
+        const int row_in_group = t.mt * BM + r_in_tile;
+        const size_t row = (size_t)t.row0 + row_in_group;
+        const bool real = row_in_group < t.rows && row < (size_t)args.row_capacity;
+        __nv_bfloat16* orow = nullptr;
+        if (real) {
+          if (args.meta != nullptr) {
+            const int2 mt = args.meta[row];
+            __nv_bfloat16* base = args.out_ptrs ? reinterpret_cast<__nv_bfloat16*>(args.out_ptrs[mt.x]) : out0;
+            orow = base + (size_t)mt.y * args.N;
+          } else {
+            orow = out0 + row * (size_t)args.N;
+          }
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col = t.nt * BN + c * 32;
+          if (col >= args.N) break;
+          tmem_ld32(taddr + c * 32, v);
+          tmem_ld_wait();
+          if (real) store32(orow + col, v);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_v && threadIdx.x == 0) {
+    // let copies that were already issued land before the shared memory is released
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+constexpr size_t kSmemBytes = STAGES * STAGE_BYTES + 1024 /*align*/ + 16 * 8 /*barriers*/ + 16 + 4 * (MAX_GROUPS + 2);
+
+// ---------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                  uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_tmap_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                  uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  cuuint64_t dims[3] = {cols, rows, slots};
+  cuuint64_t strides[2] = {cols * 2, rows * cols * 2};
+  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int kMode>
+static cudaError_t launch_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
+                               cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  grouped_gemm_kernel<kMode><<<num_sms, NUM_THREADS, kSmemBytes, stream>>>(tmA, tmB, args);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_grouped_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
+                                cudaStream_t stream) {
+  if (args.n_groups_cap > MAX_GROUPS) return cudaErrorInvalidValue;
+  if (args.mode == kFwd1 && args.N % 128 != 0) return cudaErrorInvalidValue;
+  if (args.N % 32 != 0) return cudaErrorInvalidValue;
+  switch (args.mode) {
+    case kFwd1: return launch_mode<kFwd1>(tmA, tmB, args, num_sms, stream);
+    case kFwd2: return launch_mode<kFwd2>(tmA, tmB, args, num_sms, stream);
+    case kDgrad2: return launch_mode<kDgrad2>(tmA, tmB, args, num_sms, stream);
+    case kDgrad1: return launch_mode<kDgrad1>(tmA, tmB, args, num_sms, stream);
+    case kWgrad: return launch_mode<kWgrad>(tmA, tmB, args, num_sms, stream);
+    case kPlain: return launch_mode<kPlain>(tmA, tmB, args, num_sms, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace epb

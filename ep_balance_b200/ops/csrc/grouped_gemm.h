@@ -1,0 +1,55 @@
+// Ragged grouped GEMM on the 5th-generation tensor cores (grouped_gemm.cu).
+//
+// One persistent kernel (one CTA per SM) covers the six expert GEMMs of an MoE layer step:
+//   kFwd1    h = X W1^T  with SwiGLU epilogue        (A K-major, B K-major, gate/up pair per tile)
+//   kFwd2    y = act W2^T, rows scattered to sources  (A K-major, B K-major)
+//   kDgrad2  dact = dY W2, act-grad fused, in place   (A K-major, B MN-major)
+//   kDgrad1  dX = dH W1, rows scattered to sources    (A K-major, B MN-major)
+//   kWgrad   dW[slot] = P^T Q over the slot's rows    (A MN-major, B MN-major, K = ragged rows)
+//   kPlain   C = A B^T per group, rows kept local      (testing / generic use)
+// Group geometry (row offsets, row counts, weight slots) is read from device memory, so the host
+// never learns the routing outcome.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace epb {
+
+enum GemmMode : int { kFwd1 = 0, kFwd2 = 1, kDgrad2 = 2, kDgrad1 = 3, kWgrad = 4, kPlain = 5 };
+
+struct GemmArgs {
+  int mode;
+  // group geometry (device)
+  const int32_t* group_off;    // [n_groups_cap + 1] first row of each group (multiple of 128)
+  const int32_t* group_rows;   // [n_groups_cap]
+  const int32_t* group_wslot;  // [n_groups_cap]
+  const int32_t* totals;       // [2]: padded rows, number of groups
+  int n_groups_cap;
+  int row_capacity;            // rows of the token buffers; tiles never write past it
+  // problem extents
+  int N;                       // output columns (kFwd1: F, gate/up pairs; kWgrad: columns of Q)
+  int K;                       // reduction extent (ignored for kWgrad: the group's padded rows)
+  int M_out;                   // kWgrad only: rows of the output (columns of P)
+  // epilogue operands
+  void* out0;                  // kFwd1: h [T, 2N];  kDgrad2: h (in/out);  kWgrad: dW [slots, M_out, N];
+                               // kPlain: C [T, N];  scatter modes with out_ptrs == null: local [T, N]
+  void* out1;                  // kFwd1: act [T, N]
+  void* const* out_ptrs;       // scatter modes: R peer buffers [units, N] (null -> local out0)
+  const int2* meta;            // scatter modes: {src rank, unit} per row
+  int* status;
+};
+
+// Host-side tensor-map helpers (driver entry point fetched at run time; no -lcuda needed).
+// 2-D: tensor [rows, cols] row-major bf16, box {box_cols, box_rows}, 128-byte swizzle.
+bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+                  uint32_t box_rows);
+// 3-D: tensor [slots, rows, cols] bf16, box {box_cols, box_rows, 1}.
+bool make_tmap_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols,
+                  uint32_t box_cols, uint32_t box_rows);
+
+cudaError_t launch_grouped_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
+                                cudaStream_t stream);
+
+}  // namespace epb

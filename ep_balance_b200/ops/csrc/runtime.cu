@@ -1,0 +1,287 @@
+// MoeRuntime: wires one layer's buffers into the solver, routing and grouped-GEMM kernels.
+//
+// Step order (forward):  publish -> solve -> route -> dispatch -> pull -> [barrier] -> gemm1 ->
+// gemm2 (rows scattered to source ranks) -> [barrier] -> reduce_out.
+// Step order (backward): dispatch_grads (+ gate grads) -> [barrier] -> wgrad2 -> dgrad2 -> wgrad1
+// -> dgrad1 (rows scattered) -> [barrier] -> reduce_dtokens -> reduce_weight_grads.
+// This is the schedule the reference drives from Python over NCCL (eplb_manager.py:905-1167,
+// manual_block.py:127-367), restated as a fixed sequence of device-side kernels.
+#include "runtime.h"
+
+#include <stdexcept>
+
+namespace epb {
+
+template <typename T>
+T* MoeRuntime::ptr(const char* name, bool required) const {
+  auto it = ptrs_.find(name);
+  if (it == ptrs_.end() || it->second == 0) {
+    if (required) throw std::runtime_error(std::string("MoeRuntime: missing device pointer '") + name + "'");
+    return nullptr;
+  }
+  return reinterpret_cast<T*>(static_cast<uintptr_t>(it->second));
+}
+
+void MoeRuntime::check(cudaError_t e, const char* what) {
+  ++launches_;
+  if (e != cudaSuccess) throw std::runtime_error(std::string("MoeRuntime: ") + what + ": " + cudaGetErrorString(e));
+}
+
+void MoeRuntime::tmap2(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br) {
+  if (!make_tmap_2d(m, base, rows, cols, bc, br)) throw std::runtime_error("MoeRuntime: cuTensorMapEncodeTiled (2-D) failed");
+}
+void MoeRuntime::tmap3(CUtensorMap* m, const void* base, uint64_t slots, uint64_t rows, uint64_t cols, uint32_t bc,
+                       uint32_t br) {
+  if (!make_tmap_3d(m, base, slots, rows, cols, bc, br)) throw std::runtime_error("MoeRuntime: cuTensorMapEncodeTiled (3-D) failed");
+}
+
+MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint64_t>& ptrs) : cfg_(cfg), ptrs_(ptrs) {
+  const LayerConfig& c = cfg_;
+  if (c.H % 64 || c.F % 128) throw std::runtime_error("MoeRuntime: need H % 64 == 0 and F % 128 == 0");
+  if (c.row_capacity % 128) throw std::runtime_error("MoeRuntime: row_capacity must be a multiple of 128");
+
+  sp_.omega = ptr<const int32_t>("omega");
+  sp_.dom = ptr<const int32_t>("dom");
+  sp_.cost = ptr<const int32_t>("cost");
+  sp_.main_rank = ptr<const int32_t>("main_rank");
+  sp_.weight_bytes = ptr<const int64_t>("weight_bytes");
+  sp_.s_tok = c.s_tok;
+  sp_.R = c.R;
+  sp_.E = c.E;
+  sp_.D = c.D;
+  sp_.n_slot = c.n_slot_plan;
+  sp_.u_min = c.u_min;
+  sp_.iters = c.iters;
+  sp_.patience = c.patience;
+  sp_.allow_cross = c.allow_cross;
+  sp_.probe = c.probe;
+  sp_.x = ptr<int8_t>("x");
+  sp_.q = ptr<int32_t>("q");
+  sp_.erl = ptr<int32_t>("erl");
+  sp_.rank_load = ptr<int32_t>("rank_load");
+  sp_.slot_used = ptr<int32_t>("slot_used");
+  sp_.stuck = ptr<unsigned char>("stuck");
+  sp_.theta = ptr<int64_t>("theta");
+  sp_.control = ptr<int64_t>("control", false);
+  sp_.sync = ptr<unsigned>("sync");
+  sp_.status = ptr<int>("status");
+  sp_.omega_signal = ptr<const unsigned>("signals");
+  sp_.omega_epoch = ptr<const unsigned>("epochs");
+
+  tables_.me = c.me;
+  tables_.n_slot = c.w_slots;
+  tables_.row_align = 128;
+  tables_.row_capacity = c.row_capacity;
+  tables_.home_cap = c.home_cap;
+  tables_.home_index = ptr<const int32_t>("home_index");
+  tables_.slot_of = ptr<int32_t>("slot_of");
+  tables_.row_base = ptr<int32_t>("row_base");
+  tables_.group_expert = ptr<int32_t>("group_expert");
+  tables_.group_wslot = ptr<int32_t>("group_wslot");
+  tables_.group_off = ptr<int32_t>("group_off");
+  tables_.group_rows = ptr<int32_t>("group_rows");
+  tables_.totals = ptr<int32_t>("totals");
+
+  const uint64_t T = c.row_capacity, H = c.H, F = c.F, S = c.w_slots;
+  // K-major A operands: box {64 k, 128 rows}
+  tmap2(&tm_x_k_, ptr<void>("xbuf"), T, H, 64, 128);
+  tmap2(&tm_act_k_, ptr<void>("act"), T, F, 64, 128);
+  tmap2(&tm_dy_k_, ptr<void>("dybuf"), T, H, 64, 128);
+  tmap2(&tm_dh_k_, ptr<void>("hbuf"), T, 2 * F, 64, 128);
+  // weights, K-major B: box {64 k, 128 n, 1}
+  tmap3(&tm_w1_k_, ptr<void>("w1"), S, 2 * F, H, 64, 128);
+  tmap3(&tm_w2_k_, ptr<void>("w2"), S, H, F, 64, 128);
+  // weights, MN-major B: box {64 n, 64 k, 1}
+  tmap3(&tm_w1_mn_, ptr<void>("w1"), S, 2 * F, H, 64, 64);
+  tmap3(&tm_w2_mn_, ptr<void>("w2"), S, H, F, 64, 64);
+  // Wgrad operands, MN-major: box {64 cols, 64 rows}
+  tmap2(&tm_dy_mn_, ptr<void>("dybuf"), T, H, 64, 64);
+  tmap2(&tm_act_mn_, ptr<void>("act"), T, F, 64, 64);
+  tmap2(&tm_dh_mn_, ptr<void>("hbuf"), T, 2 * F, 64, 64);
+  tmap2(&tm_x_mn_, ptr<void>("xbuf"), T, H, 64, 64);
+}
+
+// ------------------------------------------------------------------ forward pieces
+void MoeRuntime::publish(const int64_t* topk_idx, int num_units, cudaStream_t stream) {
+  check(launch_count_publish(topk_idx, num_units, cfg_.E, cfg_.R, cfg_.me, ptr<int32_t* const>("omega_ptrs"),
+                             ptr<unsigned* const>("signal_ptrs"), ptr<unsigned>("epochs"), stream),
+        "count_publish");
+}
+
+void MoeRuntime::solve(cudaStream_t stream) { check(launch_solver(sp_, tables_, stream), "solver"); }
+
+void MoeRuntime::route(const int64_t* topk_idx, int num_units, cudaStream_t stream) {
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  const int32_t* q_me = sp_.q + (size_t)cfg_.me * cfg_.E * cfg_.R;
+  check(launch_route_assign(topk_idx, num_units, cfg_.E, cfg_.R, q_me, tables_.row_base, ptr<int32_t>("unit_dst"),
+                            ptr<int32_t>("unit_row"), sp_.status, stream),
+        "route_assign");
+}
+
+void MoeRuntime::dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream) {
+  DispatchArgs a{};
+  a.rows = tokens;
+  a.num_units = num_units;
+  a.topk = cfg_.topk;
+  a.H = cfg_.H;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.unit_dst = ptr<const int32_t>("unit_dst");
+  a.unit_row = ptr<const int32_t>("unit_row");
+  a.buf_ptrs = ptr<void* const>("xbuf_ptrs");
+  a.meta_ptrs = ptr<int2* const>("meta_ptrs");
+  a.local_buf = ptr<void>("xbuf");
+  a.slot_off = tables_.group_off;
+  a.slot_rows = tables_.group_rows;
+  a.n_slot = cfg_.w_slots;
+  a.row_capacity = cfg_.row_capacity;
+  check(launch_dispatch(a, stream), "dispatch");
+}
+
+void MoeRuntime::pull_weights(cudaStream_t stream) {
+  if (cfg_.w_slots <= cfg_.home_cap) return;
+  WeightPullArgs a{};
+  a.slot_of = tables_.slot_of;
+  a.main_rank = sp_.main_rank;
+  a.home_index = tables_.home_index;
+  a.E = cfg_.E;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.home_cap = cfg_.home_cap;
+  a.n_slot = cfg_.w_slots;
+  a.w_ptrs = ptr<void* const>("w1_ptrs");
+  a.elems_per_slot = (size_t)2 * cfg_.F * cfg_.H;
+  check(launch_weight_pull(a, stream), "weight_pull(w1)");
+  a.w_ptrs = ptr<void* const>("w2_ptrs");
+  a.elems_per_slot = (size_t)cfg_.F * cfg_.H;
+  check(launch_weight_pull(a, stream), "weight_pull(w2)");
+}
+
+void MoeRuntime::barrier(int slot, cudaStream_t stream) {
+  if (!cfg_.multi_rank_sync || cfg_.R <= 1) return;
+  check(launch_symm_barrier(ptr<unsigned* const>("signal_ptrs"), slot, cfg_.R, cfg_.me, ptr<unsigned>("epochs") + slot,
+                            sp_.status, stream),
+        "symm_barrier");
+}
+
+void MoeRuntime::gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int N, int K, int M_out, void* out0,
+                      void* out1, void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
+  GemmArgs g{};
+  g.mode = mode;
+  g.group_off = tables_.group_off;
+  g.group_rows = tables_.group_rows;
+  g.group_wslot = tables_.group_wslot;
+  g.totals = tables_.totals;
+  g.n_groups_cap = cfg_.w_slots;
+  g.row_capacity = cfg_.row_capacity;
+  g.N = N;
+  g.K = K;
+  g.M_out = M_out;
+  g.out0 = out0;
+  g.out1 = out1;
+  g.out_ptrs = out_ptrs;
+  g.meta = meta;
+  g.status = sp_.status;
+  check(launch_grouped_gemm(a, b, g, cfg_.num_sms, stream), "grouped_gemm");
+}
+
+void MoeRuntime::gemm1(cudaStream_t stream) {
+  gemm(kFwd1, tm_x_k_, tm_w1_k_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), ptr<void>("act"), nullptr, nullptr, stream);
+}
+void MoeRuntime::gemm2(cudaStream_t stream) {
+  gemm(kFwd2, tm_act_k_, tm_w2_k_, cfg_.H, cfg_.F, 0, nullptr, nullptr, ptr<void* const>("ybuf_ptrs"),
+       ptr<const int2>("meta"), stream);
+}
+void MoeRuntime::reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream) {
+  check(launch_unit_reduce(ptr<void>("ybuf"), topk_prob, out, num_tokens, cfg_.topk, cfg_.H, stream), "unit_reduce");
+}
+
+// ------------------------------------------------------------------ backward pieces
+void MoeRuntime::dispatch_grads(const void* dout, const float* topk_prob, float* dprob, int num_units,
+                                cudaStream_t stream) {
+  DispatchArgs a{};
+  a.rows = dout;
+  a.unit_scale = topk_prob;
+  a.saved_out = ptr<void>("ybuf");
+  a.unit_dot = dprob;
+  a.num_units = num_units;
+  a.topk = cfg_.topk;
+  a.H = cfg_.H;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.unit_dst = ptr<const int32_t>("unit_dst");
+  a.unit_row = ptr<const int32_t>("unit_row");
+  a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
+  a.meta_ptrs = nullptr;
+  a.local_buf = ptr<void>("dybuf");
+  a.slot_off = tables_.group_off;
+  a.slot_rows = tables_.group_rows;
+  a.n_slot = cfg_.w_slots;
+  a.row_capacity = cfg_.row_capacity;
+  check(launch_dispatch(a, stream), "dispatch_grads");
+}
+void MoeRuntime::wgrad2(cudaStream_t stream) {
+  gemm(kWgrad, tm_dy_mn_, tm_act_mn_, cfg_.F, 0, cfg_.H, ptr<void>("gw2"), nullptr, nullptr, nullptr, stream);
+}
+void MoeRuntime::dgrad2(cudaStream_t stream) {
+  gemm(kDgrad2, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), nullptr, nullptr, nullptr, stream);
+}
+void MoeRuntime::wgrad1(cudaStream_t stream) {
+  gemm(kWgrad, tm_dh_mn_, tm_x_mn_, cfg_.H, 0, 2 * cfg_.F, ptr<void>("gw1"), nullptr, nullptr, nullptr, stream);
+}
+void MoeRuntime::dgrad1(cudaStream_t stream) {
+  gemm(kDgrad1, tm_dh_k_, tm_w1_mn_, cfg_.H, 2 * cfg_.F, 0, nullptr, nullptr, ptr<void* const>("dxbuf_ptrs"),
+       ptr<const int2>("meta"), stream);
+}
+void MoeRuntime::reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream) {
+  check(launch_unit_reduce(ptr<void>("dxbuf"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H, stream), "unit_reduce(bwd)");
+}
+void MoeRuntime::reduce_weight_grads(cudaStream_t stream) {
+  if (cfg_.R <= 1) return;
+  GradReduceArgs a{};
+  a.slot_of = tables_.slot_of;
+  a.main_rank = sp_.main_rank;
+  a.home_index = tables_.home_index;
+  a.E = cfg_.E;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.home_cap = cfg_.home_cap;
+  a.g_ptrs = ptr<void* const>("gw1_ptrs");
+  a.elems_per_slot = (size_t)2 * cfg_.F * cfg_.H;
+  check(launch_grad_reduce(a, stream), "grad_reduce(w1)");
+  a.g_ptrs = ptr<void* const>("gw2_ptrs");
+  a.elems_per_slot = (size_t)cfg_.F * cfg_.H;
+  check(launch_grad_reduce(a, stream), "grad_reduce(w2)");
+}
+
+// ------------------------------------------------------------------ whole passes
+void MoeRuntime::forward(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out,
+                         int num_tokens, cudaStream_t stream) {
+  const int U = num_tokens * cfg_.topk;
+  publish(topk_idx, U, stream);
+  solve(stream);
+  route(topk_idx, U, stream);
+  dispatch_tokens(tokens, U, stream);
+  pull_weights(stream);
+  barrier(1, stream);
+  gemm1(stream);
+  gemm2(stream);
+  barrier(2, stream);
+  reduce_out(topk_prob, out, num_tokens, stream);
+}
+
+void MoeRuntime::backward(const void* dout, const float* topk_prob, void* dtokens, float* dprob, int num_tokens,
+                          cudaStream_t stream) {
+  const int U = num_tokens * cfg_.topk;
+  dispatch_grads(dout, topk_prob, dprob, U, stream);
+  barrier(3, stream);
+  wgrad2(stream);
+  dgrad2(stream);
+  wgrad1(stream);
+  dgrad1(stream);
+  barrier(4, stream);
+  reduce_dtokens(dtokens, num_tokens, stream);
+  reduce_weight_grads(stream);
+}
+
+}  // namespace epb

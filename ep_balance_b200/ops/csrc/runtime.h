@@ -1,0 +1,85 @@
+// Per-layer runtime: owns no memory, holds the device pointers of one MoE layer's buffers and
+// launches the step's kernels in order on a caller-provided stream.  The host never reads device
+// data on this path; routing, group sizes and slot use stay on the GPU.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <string>
+
+#include "grouped_gemm.h"
+#include "route.h"
+#include "solver.h"
+
+namespace epb {
+
+struct LayerConfig {
+  int R = 1, me = 0, E = 0, H = 0, F = 0, topk = 0;
+  int w_slots = 0;        // weight slots per rank (home_cap + replica slots)
+  int home_cap = 0;       // experts owned per rank (upper bound)
+  int n_slot_plan = 0;    // slot budget the solver enforces (C4)
+  int row_capacity = 0;   // rows of the receive buffers
+  int max_units = 0;      // tokens * topk this rank can route per step
+  int D = 1, u_min = 1, iters = 64, patience = 8, allow_cross = 1, probe = 0;
+  int64_t s_tok = 0;
+  int num_sms = 148;
+  int multi_rank_sync = 1;  // 0: one process emulates all ranks, kernels are ordered by the stream
+};
+
+class MoeRuntime {
+ public:
+  MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint64_t>& ptrs);
+
+  // ---- forward pieces (each enqueues on `stream` and returns)
+  void publish(const int64_t* topk_idx, int num_units, cudaStream_t stream);
+  void solve(cudaStream_t stream);
+  void route(const int64_t* topk_idx, int num_units, cudaStream_t stream);
+  void dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream);
+  void pull_weights(cudaStream_t stream);
+  void barrier(int slot, cudaStream_t stream);
+  void gemm1(cudaStream_t stream);
+  void gemm2(cudaStream_t stream);
+  void reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream);
+  // ---- backward pieces
+  void dispatch_grads(const void* dout, const float* topk_prob, float* dprob, int num_units, cudaStream_t stream);
+  void wgrad2(cudaStream_t stream);
+  void dgrad2(cudaStream_t stream);
+  void wgrad1(cudaStream_t stream);
+  void dgrad1(cudaStream_t stream);
+  void reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream);
+  void reduce_weight_grads(cudaStream_t stream);
+
+  // ---- whole passes
+  void forward(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out, int num_tokens,
+               cudaStream_t stream);
+  void backward(const void* dout, const float* topk_prob, void* dtokens, float* dprob, int num_tokens,
+                cudaStream_t stream);
+
+  int launches() const { return launches_; }
+  void reset_launches() { launches_ = 0; }
+  const LayerConfig& config() const { return cfg_; }
+
+ private:
+  template <typename T>
+  T* ptr(const char* name, bool required = true) const;
+  void check(cudaError_t e, const char* what);
+  void gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int N, int K, int M_out, void* out0, void* out1,
+            void* const* out_ptrs, const int2* meta, cudaStream_t stream);
+  void tmap2(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br);
+  void tmap3(CUtensorMap* m, const void* base, uint64_t slots, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br);
+
+  LayerConfig cfg_;
+  std::map<std::string, uint64_t> ptrs_;
+  SolverParams sp_{};
+  RankTables tables_{};
+  int launches_ = 0;
+  // tensor maps (built once: every buffer has a fixed address)
+  CUtensorMap tm_x_k_, tm_act_k_, tm_dy_k_, tm_dh_k_;           // K-major A operands
+  CUtensorMap tm_w1_k_, tm_w2_k_, tm_w1_mn_, tm_w2_mn_;          // weights as B
+  CUtensorMap tm_dy_mn_, tm_act_mn_, tm_dh_mn_, tm_x_mn_;        // Wgrad operands (MN-major)
+};
+
+}  // namespace epb

@@ -1,0 +1,631 @@
+// On-device plan solver: one cooperative launch computes placement x, routing quota q and
+// the per-rank routing tables, with no host decision and no q memset.
+//
+// Semantics (must equal solver/device_semantics.py element for element; they restate the
+// reference's CUDA path, eplb/cuda_solve.py:36-68 and eplb/csrc/fast_solver.cu:34-643):
+//   phase 0  per domain: demand T[d,e], gate + benefit, stable descending order, greedy admission
+//   phase 1  per (src, e): even split over active hosts in ascending rank id
+//   phase 2  per domain: bounded greedy repair (busiest rank -> best (expert, target))
+//   phase 3  routing tables for the calling rank (slot layout, destination row bases)
+// The reference spends a sort + ~10 torch kernels + 3 launches and R*E blocks on this; here
+// phases are separated by a bounded grid barrier inside one launch, one CTA per domain.
+#include "solver.h"
+
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace epb {
+namespace {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+struct Cand {
+  int delta, load, cost, expert, target;
+};
+__device__ __forceinline__ Cand no_cand() { return Cand{0, INT_MAX, INT_MAX, INT_MAX, INT_MAX}; }
+__device__ __forceinline__ bool better(const Cand& a, const Cand& b) {
+  if (a.delta != b.delta) return a.delta > b.delta;
+  if (a.load != b.load) return a.load < b.load;
+  if (a.cost != b.cost) return a.cost < b.cost;
+  if (a.expert != b.expert) return a.expert < b.expert;
+  return a.target < b.target;
+}
+__device__ __forceinline__ Cand warp_best(Cand v) {
+  for (int off = kWarp / 2; off > 0; off >>= 1) {
+    Cand o{__shfl_down_sync(kFull, v.delta, off), __shfl_down_sync(kFull, v.load, off),
+           __shfl_down_sync(kFull, v.cost, off), __shfl_down_sync(kFull, v.expert, off),
+           __shfl_down_sync(kFull, v.target, off)};
+    if (better(o, v)) v = o;
+  }
+  return v;
+}
+
+__device__ __forceinline__ int safe_move(int have, int there, int left, int u_min) {
+  int upper = min(have, left);
+  if (upper <= 0) return 0;
+  if (upper == have && there + upper >= u_min) return upper;
+  int cap = min(upper, max(have - u_min, 0));
+  return cap >= (there > 0 ? 1 : u_min) ? cap : 0;
+}
+
+// Bounded grid barrier on a monotonically increasing arrival counter.  All CTAs of the launch
+// are co-resident (cooperative launch).  Returns false when the wait ran out.
+__device__ bool grid_barrier(const SolverParams& p, int site) {
+  __shared__ int ok;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ok = 1;
+    if (gridDim.x > 1) {
+      __threadfence();
+      unsigned old = atomicAdd(p.sync, 1u);
+      unsigned target = (old / gridDim.x + 1u) * gridDim.x;
+      if (!wait_ge<false>(p.sync, target, kWaitBudgetNs)) {
+        set_status(p.status, kStatusBarrierTimeout, site);
+        ok = 0;
+      }
+      __threadfence();
+    }
+  }
+  __syncthreads();
+  return ok != 0;
+}
+
+struct Smem {
+  long long* prio;  // [E]
+  int* order;       // [E]
+  int* dom_ranks;   // [R] ranks of the domain being processed, ascending
+  int* local_idx;   // [R] rank -> index in dom_ranks or -1
+  int* load;        // [R] by domain-local index
+  int* slot;        // [R]
+  int* stuck;       // [R]
+  Cand* wcand;      // [32]
+};
+
+__device__ Smem carve(unsigned char* base, int R, int E) {
+  Smem s;
+  s.prio = reinterpret_cast<long long*>(base);
+  base += sizeof(long long) * E;
+  s.order = reinterpret_cast<int*>(base);
+  base += sizeof(int) * E;
+  s.dom_ranks = reinterpret_cast<int*>(base);
+  base += sizeof(int) * R;
+  s.local_idx = reinterpret_cast<int*>(base);
+  base += sizeof(int) * R;
+  s.load = reinterpret_cast<int*>(base);
+  base += sizeof(int) * R;
+  s.slot = reinterpret_cast<int*>(base);
+  base += sizeof(int) * R;
+  s.stuck = reinterpret_cast<int*>(base);
+  base += sizeof(int) * R;
+  s.wcand = reinterpret_cast<Cand*>(base);
+  return s;
+}
+
+__device__ int collect_domain(const SolverParams& p, Smem& s, int d) {
+  __shared__ int n_sh;
+  __syncthreads();
+  for (int r = threadIdx.x; r < p.R; r += blockDim.x) s.local_idx[r] = -1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int n = 0;
+    for (int r = 0; r < p.R; ++r)
+      if (p.dom[r] == d) {
+        s.local_idx[r] = n;
+        s.dom_ranks[n++] = r;
+      }
+    n_sh = n;
+  }
+  __syncthreads();
+  return n_sh;
+}
+
+// ------------------------------------------------------------------ phase 0
+__device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
+  __shared__ int n_valid;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int R = p.R, E = p.E;
+  const int n = collect_domain(p, s, d);
+  if (n == 0) return;
+  if (tid == 0) n_valid = 0;
+  for (int i = tid; i < n; i += nt) s.slot[i] = 0;
+  __syncthreads();
+  // owners: x[e, r] = (main(e) == r) for this domain's columns; slots used by owners
+  for (int idx = tid; idx < E * n; idx += nt) {
+    int e = idx / n, i = idx - e * n;
+    int r = s.dom_ranks[i];
+    bool own = p.main_rank[e] == r;
+    p.x[(size_t)e * R + r] = own ? 1 : 0;
+    if (own) atomicAdd(&s.slot[i], 1);
+  }
+  // gate and benefit
+  for (int e = tid; e < E; e += nt) {
+    long long T = 0;
+    for (int i = 0; i < n; ++i) T += p.omega[(size_t)s.dom_ranks[i] * E + e];
+    long long rhs = 2 * T * p.s_tok;
+    bool valid = p.allow_cross && p.dom[p.main_rank[e]] != d && T > 0 && p.weight_bytes[e] < rhs;
+    s.prio[e] = valid ? rhs - p.weight_bytes[e] : -1;
+    if (valid) atomicAdd(&n_valid, 1);
+  }
+  __syncthreads();
+  const int nv = n_valid;
+  if (nv > 0) {
+    // stable descending order by counting how many entries precede each valid one
+    for (int e = tid; e < E; e += nt) {
+      long long pe = s.prio[e];
+      if (pe < 0) continue;
+      int pos = 0;
+      for (int o = 0; o < E; ++o) {
+        long long po = s.prio[o];
+        pos += (po > pe) || (po == pe && o < e);
+      }
+      s.order[pos] = e;
+    }
+    __syncthreads();
+    if (tid < kWarp) {
+      const int lane = tid;
+      for (int c = 0; c < nv; ++c) {
+        const int e = s.order[c];
+        bool present = false;
+        long long key = LLONG_MAX;  // (slots used, domain-local index) of the best free rank
+        for (int i = lane; i < n; i += kWarp) {
+          if (p.x[(size_t)e * R + s.dom_ranks[i]] != 0) present = true;
+          int used = s.slot[i];
+          if (used < p.n_slot) key = min(key, ((long long)used << 32) | (unsigned)i);
+        }
+        const unsigned any = __ballot_sync(kFull, present);
+        for (int off = kWarp / 2; off > 0; off >>= 1) key = min(key, __shfl_down_sync(kFull, key, off));
+        if (lane == 0 && any == 0 && key != LLONG_MAX) {
+          int i = (int)(key & 0xffffffffll);
+          p.x[(size_t)e * R + s.dom_ranks[i]] = 1;
+          s.slot[i] += 1;
+        }
+        __syncwarp(kFull);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < n; i += nt) p.slot_used[s.dom_ranks[i]] = s.slot[i];
+}
+
+// ------------------------------------------------------------------ phase 1
+__device__ void phase1_routing(const SolverParams& p) {
+  const int R = p.R, E = p.E, u_min = p.u_min;
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int gwarp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int total_warps = gridDim.x * warps_per_block;
+  const unsigned lt = (1u << lane) - 1u;
+  for (int e = gwarp; e < E; e += total_warps) {
+    int* erl = p.erl + (size_t)e * R;
+    const signed char* xe = p.x + (size_t)e * R;
+    for (int dst = lane; dst < R; dst += kWarp) erl[dst] = 0;
+    __syncwarp(kFull);
+    for (int src = 0; src < R; ++src) {
+      const int need = p.omega[(size_t)src * E + e];
+      const int dsrc = p.dom[src];
+      int cnt_all = 0, cnt_loc = 0;
+      for (int base = 0; base < R; base += kWarp) {
+        int dst = base + lane;
+        bool h = dst < R && xe[dst] != 0;
+        bool loc = h && p.dom[dst] == dsrc;
+        cnt_all += __popc(__ballot_sync(kFull, h));
+        cnt_loc += __popc(__ballot_sync(kFull, loc));
+      }
+      const bool has_local = cnt_loc > 0;
+      const int count = has_local ? cnt_loc : cnt_all;
+      int n = count;
+      if (u_min > 1 && need >= u_min) n = min(count, need / u_min);
+      else if (need < u_min) n = 1;
+      int seen = 0;
+      int* qrow = p.q + ((size_t)src * E + e) * R;
+      for (int base = 0; base < R; base += kWarp) {
+        int dst = base + lane;
+        bool h = dst < R && xe[dst] != 0;
+        bool act = h && (!has_local || p.dom[dst] == dsrc);
+        unsigned m = __ballot_sync(kFull, act);
+        int pos = seen + __popc(m & lt);
+        int give = 0;
+        if (act && need > 0 && count > 0 && pos < n) give = need / n + (pos < need % n ? 1 : 0);
+        if (dst < R) {
+          qrow[dst] = give;
+          if (give) erl[dst] += give;
+        }
+        seen += __popc(m);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ phase 2
+struct ProbeState {
+  bool on;
+  int patience;
+};
+
+__device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, ProbeState probe) {
+  __shared__ int busy_idx, busy_rank, busy_load, finished, sel_idx, apply_move;
+  __shared__ int best_theta, stagnant;
+  __shared__ Cand best_sh;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
+  const int R = p.R, E = p.E, u_min = p.u_min;
+  const int n = collect_domain(p, s, d);
+  if (n == 0) return;
+  for (int i = tid; i < n; i += nt) {
+    int r = s.dom_ranks[i];
+    s.load[i] = p.rank_load[r];
+    s.slot[i] = p.slot_used[r];
+    s.stuck[i] = probe.on ? p.stuck[r] : 0;
+  }
+  __syncthreads();
+
+  for (int it = 0; it < iters; ++it) {
+    if (tid == 0) {
+      int bi = -1, br = -1, bl = -1, theta = -1;
+      for (int i = 0; i < n; ++i) {
+        int l = s.load[i];
+        theta = max(theta, l);
+        if (s.stuck[i] == 0 && l > bl) {  // ascending rank order: first max wins ties
+          bi = i;
+          br = s.dom_ranks[i];
+          bl = l;
+        }
+      }
+      bool stop = false;
+      if (probe.on) {
+        if (it == 0 || theta < best_theta) {
+          best_theta = theta;
+          stagnant = 0;
+        } else {
+          ++stagnant;
+        }
+        stop = stagnant >= probe.patience;
+      }
+      busy_idx = bi;
+      busy_rank = br;
+      busy_load = bl;
+      finished = stop || br < 0 || bl <= 0;
+    }
+    __syncthreads();
+    if (finished) break;
+    const int src = busy_rank, top = busy_load;
+
+    Cand mine = no_cand();
+    for (int e = tid; e < E; e += nt) {
+      const int avail = p.erl[(size_t)e * R + src];
+      if (avail <= 0) continue;
+      for (int ti = 0; ti < n; ++ti) {
+        const int t = s.dom_ranks[ti], tl = s.load[ti];
+        if (t == src || tl >= top) continue;
+        if (p.x[(size_t)e * R + t] == 0 && s.slot[ti] >= p.n_slot) continue;
+        const int delta = min(avail, (top - tl) / 2);
+        if (delta < u_min) continue;
+        Cand c{delta, tl, p.cost[(size_t)src * R + t], e, t};
+        if (better(c, mine)) mine = c;
+      }
+    }
+    mine = warp_best(mine);
+    if (lane == 0) s.wcand[warp] = mine;
+    __syncthreads();
+    if (warp == 0) {
+      Cand c = lane < nwarps ? s.wcand[lane] : no_cand();
+      c = warp_best(c);
+      if (lane == 0) best_sh = c;
+    }
+    __syncthreads();
+    const Cand best = best_sh;
+
+    if (u_min == 1) {
+      if (tid == 0) {
+        sel_idx = best.delta > 0 ? s.local_idx[best.target] : -1;
+        apply_move = best.delta > 0 && sel_idx >= 0;
+        if (!apply_move) {
+          s.stuck[busy_idx] = 1;
+        } else {
+          signed char* cell = p.x + (size_t)best.expert * R + best.target;
+          if (*cell == 0) {
+            *cell = 1;
+            s.slot[sel_idx] += 1;
+          }
+        }
+      }
+      __syncthreads();
+      if (apply_move) {
+        if (warp == 0) {
+          // prefix over source ranks: source s gives min(q_s, max(delta - sum_{s'<s} q_s', 0))
+          int carry = 0;
+          for (int base = 0; base < R && carry < best.delta; base += kWarp) {
+            const int sr = base + lane;
+            int* from = p.q + ((size_t)sr * E + best.expert) * R + src;
+            int* to = p.q + ((size_t)sr * E + best.expert) * R + best.target;
+            const int have = sr < R ? *from : 0;
+            int incl = have;
+            for (int off = 1; off < kWarp; off <<= 1) {
+              int o = __shfl_up_sync(kFull, incl, off);
+              if (lane >= off) incl += o;
+            }
+            const int before = carry + incl - have;
+            const int mv = min(have, max(best.delta - before, 0));
+            if (sr < R && mv > 0) {
+              *from = have - mv;
+              *to += mv;
+            }
+            carry += __shfl_sync(kFull, incl, kWarp - 1);
+          }
+        }
+        if (tid == 0) {
+          p.erl[(size_t)best.expert * R + src] -= best.delta;
+          p.erl[(size_t)best.expert * R + best.target] += best.delta;
+          s.load[busy_idx] -= best.delta;
+          s.load[sel_idx] += best.delta;
+          for (int i = 0; i < n; ++i) s.stuck[i] = 0;
+        }
+      }
+    } else if (tid == 0) {
+      if (best.delta <= 0) {
+        s.stuck[busy_idx] = 1;
+      } else {
+        const int ti = s.local_idx[best.target];
+        auto qa = [&](int sr, int dst) { return p.q + ((size_t)sr * E + best.expert) * R + dst; };
+        auto dry = [&](int limit) {
+          int left = limit, tot = 0;
+          for (int sr = 0; sr < R; ++sr) {
+            int mv = safe_move(*qa(sr, src), *qa(sr, best.target), left, u_min);
+            left -= mv;
+            tot += mv;
+          }
+          return tot;
+        };
+        int limit = best.delta;
+        int actual = dry(limit);
+        if (actual < u_min) {
+          limit = top - best.load - 1;
+          actual = dry(limit);
+        }
+        if (actual < u_min) {
+          s.stuck[busy_idx] = 1;
+        } else {
+          signed char* cell = p.x + (size_t)best.expert * R + best.target;
+          if (*cell == 0) {
+            *cell = 1;
+            s.slot[ti] += 1;
+          }
+          int left = limit;
+          for (int sr = 0; sr < R; ++sr) {
+            int have = *qa(sr, src), there = *qa(sr, best.target);
+            int mv = safe_move(have, there, left, u_min);
+            *qa(sr, src) = have - mv;
+            *qa(sr, best.target) = there + mv;
+            left -= mv;
+          }
+          p.erl[(size_t)best.expert * R + src] -= actual;
+          p.erl[(size_t)best.expert * R + best.target] += actual;
+          s.load[busy_idx] -= actual;
+          s.load[ti] += actual;
+          for (int i = 0; i < n; ++i) s.stuck[i] = 0;
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+  for (int i = tid; i < n; i += nt) {
+    int r = s.dom_ranks[i];
+    p.rank_load[r] = s.load[i];
+    p.slot_used[r] = s.slot[i];
+    p.stuck[r] = (unsigned char)s.stuck[i];
+  }
+  __syncthreads();
+}
+
+__device__ void rank_loads_from_erl(const SolverParams& p) {
+  // rank_load[r] = sum_e erl[e, r]; ranks are spread over all warps of the grid
+  const int lane = threadIdx.x & 31;
+  const int wpb = blockDim.x >> 5;
+  const int gwarp = blockIdx.x * wpb + (threadIdx.x >> 5);
+  for (int r = gwarp; r < p.R; r += gridDim.x * wpb) {
+    int acc = 0;
+    for (int e = lane; e < p.E; e += kWarp) acc += p.erl[(size_t)e * p.R + r];
+    for (int off = kWarp / 2; off > 0; off >>= 1) acc += __shfl_down_sync(kFull, acc, off);
+    if (lane == 0) {
+      p.rank_load[r] = acc;
+      p.stuck[r] = 0;
+    }
+  }
+}
+
+__device__ int global_theta(const SolverParams& p) {
+  int th = -1;
+  for (int r = 0; r < p.R; ++r) th = max(th, p.rank_load[r]);
+  return th;
+}
+
+// ------------------------------------------------------------------ phase 3
+__device__ void build_tables(const SolverParams& p, const RankTables& t, int me) {
+  const int R = p.R, E = p.E;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  for (int h = warp; h < R; h += nwarps) {
+    int groups = 0, replicas = 0, rows = 0;  // running counts / padded row offset on rank h
+    for (int base = 0; base < E; base += kWarp) {
+      const int e = base + lane;
+      const bool hosted = e < E && p.x[(size_t)e * R + h] != 0;
+      const bool is_main = hosted && p.main_rank[e] == h;
+      const int size = hosted ? p.erl[(size_t)e * R + h] : 0;
+      const int padded = round_up(size, t.row_align);
+      const unsigned m = __ballot_sync(kFull, hosted);
+      const unsigned mr = __ballot_sync(kFull, hosted && !is_main);
+      const int my_group = groups + __popc(m & lt);
+      const int my_rep = replicas + __popc(mr & lt);
+      int incl = padded;
+      for (int off = 1; off < kWarp; off <<= 1) {
+        int o = __shfl_up_sync(kFull, incl, off);
+        if (lane >= off) incl += o;
+      }
+      const int my_off = rows + incl - padded;
+      int wslot = my_group;
+      if (t.home_index != nullptr) wslot = is_main ? t.home_index[e < E ? e : 0] : t.home_cap + my_rep;
+      if (e < E) {
+        if (t.slot_of) t.slot_of[(size_t)e * R + h] = hosted ? wslot : -1;
+        if (t.row_base && me >= 0) {
+          int before = 0;
+          if (hosted)
+            for (int s2 = 0; s2 < me; ++s2) before += p.q[((size_t)s2 * E + e) * R + h];
+          t.row_base[(size_t)e * R + h] = hosted ? my_off + before : -1;
+        }
+        if (hosted && h == me && my_group < t.n_slot) {
+          t.group_expert[my_group] = e;
+          t.group_wslot[my_group] = wslot;
+          t.group_off[my_group] = my_off;
+          t.group_rows[my_group] = size;
+        }
+      }
+      groups += __popc(m);
+      replicas += __popc(mr);
+      rows += __shfl_sync(kFull, incl, kWarp - 1);
+    }
+    if (h == me) {
+      for (int g = groups + lane; g < t.n_slot; g += kWarp) {
+        t.group_expert[g] = -1;
+        t.group_wslot[g] = 0;
+        t.group_off[g] = rows;
+        t.group_rows[g] = 0;
+      }
+      if (lane == 0) {
+        t.group_off[t.n_slot] = rows;
+        t.totals[0] = rows;
+        t.totals[1] = groups < t.n_slot ? groups : t.n_slot;
+        if (t.row_capacity > 0 && rows > t.row_capacity) set_status(p.status, kStatusRowOverflow, 30, rows);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ kernels
+__global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables tables) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  Smem s = carve(smem_raw, p.R, p.E);
+
+  // Wait (bounded) until every rank's row of omega has landed in the gather buffer.
+  if (p.omega_signal != nullptr) {
+    __shared__ int sig_ok;
+    if (threadIdx.x == 0) {
+      sig_ok = wait_ge<true>(p.omega_signal, (*p.omega_epoch) * (unsigned)p.R, kWaitBudgetNs) ? 1 : 0;
+      if (!sig_ok) set_status(p.status, kStatusSignalTimeout, 10);
+    }
+    __syncthreads();
+    if (!sig_ok) return;  // every CTA fails the same bounded wait; nobody is left at a barrier
+  }
+
+  bool ok = true;
+  for (int d = blockIdx.x; d < p.D; d += gridDim.x) phase0_domain(p, s, d);
+  ok = ok && grid_barrier(p, 11);
+  if (ok) phase1_routing(p);
+  ok = ok && grid_barrier(p, 12);
+  if (ok) rank_loads_from_erl(p);
+  ok = ok && grid_barrier(p, 13);
+
+  if (ok) {
+    if (!p.probe) {
+      for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, p.iters, ProbeState{false, 0});
+    } else {
+      // Stagnation probe: 1 repair round, then `patience` rounds, then the remainder unless the
+      // global max load stopped improving.  Every CTA evaluates the same control values.
+      ProbeState pr{true, p.patience};
+      for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, 1, pr);
+      ok = ok && grid_barrier(p, 14);
+      long long best = global_theta(p);
+      long long stagnant = 0, stop = 0;
+      int left = p.iters - 1;
+      const int probe_iters = min(p.patience, left);
+      if (ok && probe_iters > 0)
+        for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, probe_iters, pr);
+      left -= probe_iters;
+      ok = ok && grid_barrier(p, 15);
+      if (ok && left > 0) {
+        long long th = global_theta(p);
+        if (th < best) {
+          best = th;
+          stagnant = 0;
+        } else {
+          stagnant += probe_iters;
+          if (stagnant >= p.patience) stop = 1;
+        }
+        if (!stop)
+          for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, left, pr);
+      }
+      if (blockIdx.x == 0 && threadIdx.x == 0 && p.control) {
+        p.control[0] = best;
+        p.control[1] = stagnant;
+        p.control[2] = stop;
+      }
+    }
+  }
+  ok = ok && grid_barrier(p, 16);
+
+  if (ok && blockIdx.x == 0) {
+    if (threadIdx.x == 0) p.theta[0] = global_theta(p);
+    if (tables.me >= 0) build_tables(p, tables, tables.me);
+  }
+
+  // Last CTA out rewinds the barrier counters so the workspace can be reused by any grid size.
+  __syncthreads();
+  if (threadIdx.x == 0 && gridDim.x > 1) {
+    unsigned left_before = atomicAdd(p.sync + 1, 1u);
+    if (left_before == gridDim.x - 1) {
+      p.sync[0] = 0;
+      p.sync[1] = 0;
+      __threadfence();
+    }
+  }
+}
+
+__global__ void __launch_bounds__(1024) tables_kernel(SolverParams p, RankTables tables) {
+  build_tables(p, tables, tables.me);
+}
+
+size_t solver_smem_bytes(int R, int E) {
+  return sizeof(long long) * E + sizeof(int) * E + sizeof(int) * 5 * R + sizeof(Cand) * 32 + 64;
+}
+
+int pow2_threads(int R, int E) {
+  int want = E > R ? E : R;
+  int t = 128;
+  while (t < want && t < 1024) t <<= 1;
+  return t;
+}
+
+}  // namespace
+
+cudaError_t launch_solver(const SolverParams& p, const RankTables& tables, cudaStream_t stream) {
+  int dev = 0, sms = 0;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return err;
+  err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (err != cudaSuccess) return err;
+  const size_t smem = solver_smem_bytes(p.R, p.E);
+  if (smem > 48 * 1024) {
+    err = cudaFuncSetAttribute(solver_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return err;
+  }
+  int grid = p.D < sms ? p.D : sms;
+  if (grid < 1) grid = 1;
+  const int threads = pow2_threads(p.R, p.E);
+  SolverParams pc = p;
+  RankTables tc = tables;
+  void* args[] = {&pc, &tc};
+  if (grid > 1) return cudaLaunchCooperativeKernel((void*)solver_kernel, dim3(grid), dim3(threads), args, smem, stream);
+  solver_kernel<<<1, threads, smem, stream>>>(pc, tc);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_tables(const SolverParams& p, const RankTables& tables, cudaStream_t stream) {
+  int threads = 32 * (p.R < 32 ? p.R : 32);
+  if (threads < 32) threads = 32;
+  tables_kernel<<<1, threads, 0, stream>>>(p, tables);
+  return cudaGetLastError();
+}
+
+}  // namespace epb
