@@ -1,0 +1,395 @@
+"""Headline benchmark: one MoE FFN layer training step (forward + backward + optimizer) with
+per-step expert load balancing, bf16, expert-parallel over N GPUs of one node.
+
+Config (fixed per GPU, i.e. weak scaling): hidden 2048, 64 experts, SwiGLU intermediate 1408, top-6
+fp32 router, 8192 tokens per rank, router skew tuned to expert max/mean ~= 3.5, 2 replica slots per
+rank, replica weight transfer and gradient return every step.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference ...      # the unmodified upstream package from baseline/_ref
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG = dict(hidden=2048, ffn=1408, num_experts=64, top_k=6, tokens_per_rank=8192, extra_slots=2,
+           imbalance_target=3.5, router_std=0.02)
+DOMAINS = {1: 1, 2: 1, 4: 2, 8: 2}
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--tokens", type=int, default=CFG["tokens_per_rank"])
+    p.add_argument("--phases", action="store_true", help="also print a per-phase device-time table (stderr)")
+    return p.parse_args()
+
+
+# ---------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int) -> None:
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line.strip())
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------- shared set-up
+def init_dist(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    return world, rank, local
+
+
+def host_batches(tokens: int, hidden: int, rank: int, count: int = 4):
+    """Pinned host batches of synthetic N(0,1) activations (bf16); cycled by the end-to-end loop."""
+    import torch
+
+    g = torch.Generator().manual_seed(777 + rank)
+    return [torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).pin_memory() for _ in range(count)]
+
+
+def timed_loop(step_fn, steps: int, world: int):
+    """Barrier + sync, K steps between CUDA events on the current stream, sync + barrier."""
+    import torch
+    import torch.distributed as dist
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        step_fn(i)
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([t0.elapsed_time(t1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms) / steps
+
+
+def emit(args, world, impl, ms_dev, ms_e2e, launches, clocks, h2d, d2h, extra_cfg):
+    tokens_total = args.tokens * world
+    line = {
+        "metric": "moe_layer_train_tokens_per_s", "value": tokens_total / (ms_dev * 1e-3), "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_dev,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": impl,
+        "config": {"model": "single MoE FFN layer: hidden 2048, 64 experts, SwiGLU 1408, top-6, fp32 router",
+                   "global_batch": tokens_total, "seq_len": args.tokens, "parallelism": f"ep{world}",
+                   "domains": DOMAINS.get(world, 1), "replica_slots_per_rank": CFG["extra_slots"] if world > 1 else 0,
+                   "step": "forward + backward + fused AdamW, plan solved every step",
+                   "l2": "per-step working set (activations + expert weights) is several hundred MB, far above the 126 MB L2",
+                   **extra_cfg},
+        "clocks": clocks,
+        "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------- our implementation
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world, rank, local = init_dist(args)
+    from ep_balance_b200.models.moe_layer import FusedMoE, MoEConfig, heap_layout
+    from ep_balance_b200.parallel.symm import SymmetricHeap
+    from ep_balance_b200.utils.workload import router_bias_for_imbalance
+
+    dev = torch.device("cuda", local)
+    cfg = MoEConfig(hidden=CFG["hidden"], ffn=CFG["ffn"], num_experts=CFG["num_experts"], top_k=CFG["top_k"],
+                    max_tokens=args.tokens, extra_slots=CFG["extra_slots"], num_domains=DOMAINS.get(world, 1))
+    heap = SymmetricHeap(heap_layout(cfg, world), dev)
+    layer = FusedMoE(cfg, heap, rank, world)
+    # same router on every rank
+    if world > 1:
+        dist.broadcast(layer.router.data, src=0)
+    logit_std = CFG["router_std"] * CFG["hidden"] ** 0.5
+    layer.router_bias = router_bias_for_imbalance(CFG["num_experts"], CFG["top_k"], logit_std,
+                                                  CFG["imbalance_target"]).to(dev)
+    opt = torch.optim.AdamW(layer.parameters(), lr=1e-5, fused=True)
+    batches = host_batches(args.tokens, CFG["hidden"], rank)
+    dev_batches = [b.to(dev) for b in batches]
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def train_step(x):
+        out = layer(x)
+        loss = out.float().square().mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def step_device(i):
+        x = dev_batches[i % len(dev_batches)].detach().requires_grad_(True)
+        train_step(x)
+
+    def step_e2e(i):
+        x = batches[i % len(batches)].to(dev, non_blocking=True).requires_grad_(True)
+        loss = train_step(x)
+        loss_host.copy_(loss.detach().reshape(1), non_blocking=False)  # device->host read of the step's loss
+
+    for i in range(args.warmup):
+        step_device(i)
+    torch.cuda.synchronize()
+    layer.check_status()
+    layer.rt.reset_launches()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_dev = timed_loop(step_device, args.steps, world)
+    launches = layer.rt.launches()
+    for i in range(min(3, args.warmup)):
+        step_e2e(i)
+    ms_e2e = timed_loop(step_e2e, args.steps, world)
+    clocks = sampler.stop() if rank == 0 else {}
+    layer.check_status()
+
+    if args.phases and rank == 0:
+        phase_table(layer, dev_batches[0])
+    plan = layer.last_plan()
+    loads = layer.rank_loads().float()
+    extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],
+             "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return"}
+    if rank == 0:
+        emit(args, world, "ours", ms_dev, ms_e2e, launches, clocks, batches[0].numel() * 2, 4, extra)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def phase_table(layer, x):
+    """Device time of each native phase, measured one by one (not part of the headline number)."""
+    import torch
+
+    rt, K = layer.rt, layer.cfg.top_k
+    n = x.shape[0]
+    idx, prob = layer.route_tokens(x)
+    out = torch.empty_like(x)
+    dprob = torch.empty_like(prob)
+    phases = [
+        ("publish", lambda: rt.publish(idx.data_ptr(), n * K)), ("solve", rt.solve),
+        ("route", lambda: rt.route(idx.data_ptr(), n * K)),
+        ("dispatch", lambda: rt.dispatch_tokens(x.data_ptr(), n * K)), ("pull_weights", rt.pull_weights),
+        ("gemm1", rt.gemm1), ("gemm2", rt.gemm2),
+        ("reduce_out", lambda: rt.reduce_out(prob.data_ptr(), out.data_ptr(), n)),
+        ("dispatch_grads", lambda: rt.dispatch_grads(out.data_ptr(), prob.data_ptr(), dprob.data_ptr(), n * K)),
+        ("wgrad2", rt.wgrad2), ("dgrad2", rt.dgrad2), ("wgrad1", rt.wgrad1), ("dgrad1", rt.dgrad1),
+        ("reduce_dtokens", lambda: rt.reduce_dtokens(out.data_ptr(), n)),
+    ]
+    if layer.world > 1:
+        return  # phases that wait on peers cannot be timed one rank at a time
+    rows = []
+    for name, fn in phases:
+        fn()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        fn()
+        t1.record()
+        torch.cuda.synchronize()
+        rows.append((name, t0.elapsed_time(t1)))
+    for name, ms in rows:
+        print(f"[phase] {name:<16} {ms:8.3f} ms", file=sys.stderr)
+
+
+# ---------------------------------------------------------------- the reference
+def run_reference(args):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir("/root/repo/baseline/_ref/eplb"):
+        ref_root = "/root/repo/baseline/_ref"  # stable path: lets a pre-built solver extension be reused
+    if not os.path.isdir(os.path.join(ref_root, "eplb")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference)"}))
+        return
+    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ref_root, "_torch_ext"))
+    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0+PTX")
+    sys.path.insert(0, ref_root)
+    import torch
+    import torch.distributed as dist
+    import torch.nn.functional as F
+
+    world, rank, local = init_dist(args)
+    if world == 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", local))
+    try:
+        import eplb
+        from eplb.integration.eplb_manager import AllToAllAdapter, sync_free_moe_forward
+        from eplb.integration.grouped_mlp import make_batched_gated_mlp, make_grouped_gated_mlp
+        from eplb.integration.rebalancer import EPLBRebalancer
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(exc).__name__}: {exc}"[:300]}))
+        return
+    from ep_balance_b200.utils.workload import router_bias_for_imbalance  # input generator only
+
+    dev = torch.device("cuda", local)
+    E, H, Fd, K = CFG["num_experts"], CFG["hidden"], CFG["ffn"], CFG["top_k"]
+    nd = DOMAINS.get(world, 1)
+    local_e = E // world
+    n_slot = local_e + (CFG["extra_slots"] if world > 1 else 0)
+    topo = eplb.Topology.from_nvlink_rdma(nd, world // nd, 1, 8, device=dev)
+    main_rank = torch.arange(E, device=dev, dtype=torch.int64) // local_e
+    spec = eplb.ProblemSpec(E, main_rank, torch.full((E,), 3 * H * Fd * 2, dtype=torch.int64, device=dev), H * 2, n_slot)
+    reb = EPLBRebalancer(topo, spec, eplb.EPLBConfig(), ring_size=0)
+    g = torch.Generator(device="cpu").manual_seed(1234)
+    router = torch.nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(dev, torch.float32))
+    ge = torch.Generator(device="cpu")
+    weights_local, params = {}, [router]
+    for i in range(local_e):
+        e = rank * local_e + i
+        ge.manual_seed(10_000 + e)
+        w1 = torch.nn.Parameter((torch.randn(2 * Fd, H, generator=ge) * 0.02).to(dev, torch.bfloat16))
+        w2 = torch.nn.Parameter((torch.randn(H, Fd, generator=ge) * 0.02).to(dev, torch.bfloat16))
+        weights_local[e] = (w1, w2)
+        params += [w1, w2]
+    weight_shapes = [torch.Size((2 * Fd, H)), torch.Size((H, Fd))]
+    bias = router_bias_for_imbalance(E, K, CFG["router_std"] * H ** 0.5, CFG["imbalance_target"]).to(dev)
+    opt = torch.optim.AdamW(params, lr=1e-5, fused=True)
+    batched = make_batched_gated_mlp(True, F.silu)
+    grouped = make_grouped_gated_mlp(True, F.silu)
+    adapter = AllToAllAdapter()
+    batches = host_batches(args.tokens, H, rank)
+    dev_batches = [b.to(dev) for b in batches]
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    tok_idx = torch.arange(args.tokens, device=dev, dtype=torch.int64).view(-1, 1).expand(-1, K).reshape(-1).contiguous()
+    state = {"mb": 0}
+
+    def train_step(x):
+        logits = x.to(torch.float32) @ router.t() + bias
+        top_val, top_idx = torch.topk(logits, K, dim=-1)
+        prob = torch.softmax(top_val, dim=-1)
+        unit_expert = top_idx.reshape(-1).contiguous()
+        local_row = torch.bincount(unit_expert, minlength=E).to(torch.int64)
+        plan = reb.rebalance(local_row, 0, state["mb"], group=None).plan
+        state["mb"] += 1
+        out = sync_free_moe_forward(
+            tokens=x, unit_token_idx=tok_idx, unit_expert=unit_expert, unit_prob=prob.reshape(-1).to(x.dtype),
+            plan=plan, spec=spec, weights_local=weights_local, weight_shapes=weight_shapes,
+            batched_mlp_fn=batched, grouped_mlp_fn=grouped, group=None, adapter=adapter,
+            gated=True, act=F.silu, transpose_w=True)
+        loss = out.float().square().mean()
+        loss.backward()
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        return loss
+
+    def step_device(i):
+        train_step(dev_batches[i % len(dev_batches)].detach().requires_grad_(True))
+
+    def step_e2e(i):
+        x = batches[i % len(batches)].to(dev, non_blocking=True).requires_grad_(True)
+        loss = train_step(x)
+        loss_host.copy_(loss.detach().reshape(1), non_blocking=False)
+
+    try:
+        for i in range(args.warmup):
+            step_device(i)
+        torch.cuda.synchronize()
+    except Exception as exc:
+        print(json.dumps({"impl": "reference", "unavailable": f"reference step failed: {type(exc).__name__}: {exc}"[:400]}))
+        return
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_dev = timed_loop(step_device, args.steps, world)
+    for i in range(min(3, args.warmup)):
+        step_e2e(i)
+    ms_e2e = timed_loop(step_e2e, args.steps, world)
+    clocks = sampler.stop() if rank == 0 else {}
+    if rank == 0:
+        emit(args, world, "reference", ms_dev, ms_e2e, 0, clocks, batches[0].numel() * 2, 4,
+             {"path": "eplb.EPLBRebalancer.rebalance + eplb.integration.sync_free_moe_forward (AllToAllAdapter, "
+                      "dist.broadcast replicas, torch._grouped_mm), unmodified from baseline/_ref"})
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -104,3 +104,27 @@ class DriftingRouterSkew:
 
     def bias(self) -> torch.Tensor:
         return (self.scale * self.g).to(self.device)
+
+
+def router_bias_for_imbalance(num_experts: int, top_k: int, logit_std: float, target: float = 3.5,
+                              seed: int = 2024, samples: int = 32768, iters: int = 24) -> torch.Tensor:
+    """Per-expert additive logit bias ``beta * g`` (``g ~ N(0,1)`` seeded) such that top-k routing of
+    logits ``N(0, logit_std^2) + bias`` has expert max/mean load ~= ``target``.  Runs on the CPU and is
+    deterministic, so every rank and every implementation under comparison gets the same skew."""
+    g = torch.Generator().manual_seed(int(seed))
+    direction = torch.randn(num_experts, generator=g)
+    noise = torch.randn(samples, num_experts, generator=torch.Generator().manual_seed(int(seed) + 1)) * logit_std
+
+    def ratio(beta: float) -> float:
+        idx = (noise + beta * direction).topk(top_k, dim=-1).indices
+        c = torch.bincount(idx.flatten(), minlength=num_experts).double()
+        return float(c.max() / c.mean())
+
+    lo, hi = 0.0, 8.0
+    for _ in range(iters):
+        mid = 0.5 * (lo + hi)
+        if ratio(mid) < target:
+            lo = mid
+        else:
+            hi = mid
+    return (0.5 * (lo + hi)) * direction
