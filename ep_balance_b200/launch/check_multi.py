@@ -1,0 +1,106 @@
+"""Multi-GPU correctness check of the fused MoE layer (one process per GPU, NCCL for bootstrap).
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29517 -m ep_balance_b200.launch.check_multi [--steps 3]
+
+Every rank runs forward+backward through the native path, then recomputes its own tokens through
+the plain PyTorch oracle with the full set of expert weights (all-gathered).  Outputs, token
+gradients, gate gradients and the owners' weight gradients (sum over every rank's contribution,
+replicas included) must agree; the plan digest must be identical on all ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--tokens", type=int, default=512)
+    ap.add_argument("--hidden", type=int, default=256)
+    ap.add_argument("--ffn", type=int, default=256)
+    ap.add_argument("--experts", type=int, default=16)
+    ap.add_argument("--topk", type=int, default=2)
+    a = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+
+    from ..models.moe_layer import FusedMoE, MoEConfig, heap_layout
+    from ..models.reference_moe import moe_reference
+    from ..parallel.symm import SymmetricHeap
+
+    domains = 2 if world % 2 == 0 and world >= 4 else 1
+    cfg = MoEConfig(hidden=a.hidden, ffn=a.ffn, num_experts=a.experts, top_k=a.topk, max_tokens=a.tokens,
+                    extra_slots=2, num_domains=domains, capacity_factor=float(world))
+    heap = SymmetricHeap(heap_layout(cfg, world), dev)
+    layer = FusedMoE(cfg, heap, rank, world)
+    dist.broadcast(layer.router.data, src=0)
+    bias = torch.zeros(a.experts, device=dev)
+    bias[:3] = 3.0
+    layer.router_bias = bias
+    ok = True
+    for step in range(a.steps):
+        g = torch.Generator(device="cpu").manual_seed(100 * step + rank)
+        tokens = torch.randn(a.tokens, a.hidden, generator=g).to(dev, torch.bfloat16)
+        dout = torch.randn(a.tokens, a.hidden, generator=g).to(dev, torch.bfloat16)
+        idx, prob = layer.route_tokens(tokens)
+        prob = prob.detach()
+        out = torch.empty_like(tokens)
+        dtok = torch.empty_like(tokens)
+        dprob = torch.empty_like(prob)
+        layer.rt.forward(tokens.data_ptr(), idx.data_ptr(), prob.data_ptr(), out.data_ptr(), a.tokens)
+        layer.rt.backward(dout.data_ptr(), prob.data_ptr(), dtok.data_ptr(), dprob.data_ptr(), a.tokens)
+        torch.cuda.synchronize()
+        layer.check_status()
+        dist.barrier()
+
+        w1s = [torch.empty_like(layer.w1.data) for _ in range(world)]
+        w2s = [torch.empty_like(layer.w2.data) for _ in range(world)]
+        dist.all_gather(w1s, layer.w1.data.contiguous())
+        dist.all_gather(w2s, layer.w2.data.contiguous())
+        w1 = torch.cat(w1s).float().requires_grad_(True)
+        w2 = torch.cat(w2s).float().requires_grad_(True)
+        x = tokens.float().requires_grad_(True)
+        p = prob.clone().requires_grad_(True)
+        o = moe_reference(x, idx, p, w1, w2)
+        o.backward(dout.float())
+        gw1, gw2 = w1.grad.clone(), w2.grad.clone()
+        dist.all_reduce(gw1)
+        dist.all_reduce(gw2)
+        hc = layer.home_cap
+        errs = {
+            "out": rel(out, o.detach()), "dtokens": rel(dtok, x.grad), "dprob": rel(dprob, p.grad),
+            "dw1": rel(layer.w1.grad, gw1[rank * hc:(rank + 1) * hc]),
+            "dw2": rel(layer.w2.grad, gw2[rank * hc:(rank + 1) * hc]),
+        }
+        digests = [None] * world
+        dist.all_gather_object(digests, layer.last_plan().digest())
+        same_plan = len(set(digests)) == 1
+        replicas = int(layer.last_plan().x.sum()) - a.experts
+        good = all(v < 3e-2 for v in errs.values()) and same_plan
+        ok = ok and good
+        print(f"[rank {rank}] step {step} {'PASS' if good else 'FAIL'} plan_identical={same_plan} replicas={replicas} "
+              + " ".join(f"{k}={v:.2e}" for k, v in errs.items()), flush=True)
+    flag = torch.tensor([1 if ok else 0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("CHECK_MULTI " + ("PASS" if int(flag) else "FAIL"), flush=True)
+    return 0 if int(flag) else 1
+
+
+if __name__ == "__main__":
+    sys.exit(main())
