@@ -189,7 +189,9 @@ def run_ours(args):
     logit_std = CFG["router_std"] * CFG["hidden"] ** 0.5
     layer.router_bias = router_bias_for_imbalance(CFG["num_experts"], CFG["top_k"], logit_std,
                                                   CFG["imbalance_target"]).to(dev)
-    opt = torch.optim.AdamW(layer.parameters(), lr=1e-5, fused=True)
+    from ep_balance_b200.utils.optim import FusedAdamW
+
+    opt = FusedAdamW(layer.parameters(), lr=1e-5)
     batches = host_batches(args.tokens, CFG["hidden"], rank)
     dev_batches = [b.to(dev) for b in batches]
     loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
@@ -206,11 +208,33 @@ def run_ours(args):
         x = dev_batches[i % len(dev_batches)].detach().requires_grad_(True)
         train_step(x)
 
+    # End-to-end loop: the input of step i+1 is copied host->device on a side stream while step i
+    # computes (two device staging buffers); the loss of every step is read back to the host.
+    copy_stream = torch.cuda.Stream(device=dev)
+    staging = [torch.empty_like(dev_batches[0]) for _ in range(2)]
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+
+    def prefetch(i):
+        slot = i % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(consumed[slot])
+            staging[slot].copy_(batches[i % len(batches)], non_blocking=True)
+            ready[slot].record(copy_stream)
+
     def step_e2e(i):
-        x = batches[i % len(batches)].to(dev, non_blocking=True).requires_grad_(True)
+        slot = i % 2
+        if i == 0:
+            prefetch(0)
+        prefetch(i + 1)
+        torch.cuda.current_stream().wait_event(ready[slot])
+        x = staging[slot].detach().requires_grad_(True)
         loss = train_step(x)
+        consumed[slot].record()
         loss_host.copy_(loss.detach().reshape(1), non_blocking=False)  # device->host read of the step's loss
 
+    for ev in consumed:
+        ev.record()
     for i in range(args.warmup):
         step_device(i)
     torch.cuda.synchronize()

@@ -2,11 +2,14 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+#include <pybind11/stl.h>
 
+#include <cmath>
 #include <map>
 #include <string>
 
 #include "grouped_gemm.h"
+#include "optim.h"
 #include "route.h"
 #include "runtime.h"
 #include "solver.h"
@@ -162,6 +165,35 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
   cuda_check(epb::launch_grouped_gemm(tmA, tmB, g, (int)num_sms, current_stream()), "launch_grouped_gemm");
 }
 
+// In-place AdamW step on one tensor (param, grad and both moments share dtype and shape).
+void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, torch::Tensor exp_avg_sq, double lr,
+                double beta1, double beta2, double eps, double weight_decay, int64_t step) {
+  const c10::cuda::CUDAGuard guard(param.device());
+  TORCH_CHECK(param.is_contiguous() && grad.is_contiguous() && exp_avg.is_contiguous() && exp_avg_sq.is_contiguous(),
+              "adamw_step needs contiguous tensors");
+  TORCH_CHECK(param.scalar_type() == grad.scalar_type() && param.scalar_type() == exp_avg.scalar_type() &&
+                  param.scalar_type() == exp_avg_sq.scalar_type(),
+              "adamw_step needs one dtype");
+  TORCH_CHECK(param.scalar_type() == torch::kBFloat16 || param.scalar_type() == torch::kFloat32, "bf16 or fp32 only");
+  TORCH_CHECK(grad.numel() == param.numel() && exp_avg.numel() == param.numel() && exp_avg_sq.numel() == param.numel(),
+              "adamw_step size mismatch");
+  epb::AdamArgs a{};
+  a.param = param.data_ptr();
+  a.grad = grad.data_ptr();
+  a.exp_avg = exp_avg.data_ptr();
+  a.exp_avg_sq = exp_avg_sq.data_ptr();
+  a.numel = (size_t)param.numel();
+  a.lr = (float)lr;
+  a.beta1 = (float)beta1;
+  a.beta2 = (float)beta2;
+  a.eps = (float)eps;
+  a.weight_decay = (float)weight_decay;
+  a.bias_correction1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.bias_correction2_sqrt = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
+  a.is_bf16 = param.scalar_type() == torch::kBFloat16 ? 1 : 0;
+  cuda_check(epb::launch_adamw(a, current_stream()), "launch_adamw");
+}
+
 void wait_probe(torch::Tensor flag, int64_t target, int64_t budget_ns, torch::Tensor status) {
   const c10::cuda::CUDAGuard guard(flag.device());
   cuda_check(epb::launch_wait_probe(reinterpret_cast<const unsigned*>(dptr<int32_t>(flag, "flag", torch::kInt32)),
@@ -205,6 +237,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("solve_plan", &solve_plan);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("wait_probe", &wait_probe);
+  m.def("adamw_step", &adamw_step);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);
@@ -216,6 +249,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         return new MoeRuntime(config_from_dict(cfg), ptrs);
       }))
       .def("launches", &MoeRuntime::launches)
+      .def("enable_timing", &MoeRuntime::enable_timing)
+      .def("phase_times", &MoeRuntime::phase_times)
       .def("reset_launches", &MoeRuntime::reset_launches)
       .def("publish", [](MoeRuntime& r, uint64_t idx, int u) { r.publish((const int64_t*)cp(idx), u, current_stream()); })
       .def("solve", [](MoeRuntime& r) { r.solve(current_stream()); })

@@ -1,8 +1,8 @@
 // Ragged grouped GEMM for sm_100a: TMA-fed shared-memory tiles, tcgen05.mma issued by one thread,
 // accumulators in tensor memory, epilogue warps reading them back with tcgen05.ld.
 //
-// CTA = 6 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues MMAs, warps 2-5 run the
-// epilogue (each owns one 32-lane quarter of TMEM).  A 4-stage smem ring (A 16 KB + B 32 KB per
+// CTA = 10 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues MMAs, warps 2-9 run the
+// epilogue (two warps per 32-lane quarter of TMEM, each taking half of the tile's columns).  A 4-stage smem ring (A 16 KB + B 32 KB per
 // stage) feeds 128x256x16 UMMAs; two 256-column accumulators in TMEM let the epilogue of tile i
 // overlap the main loop of tile i+1.  The kernel is persistent: CTA c processes tiles
 // c, c+grid, ... of a tile list derived on device from the plan's group table.
@@ -27,8 +27,8 @@ constexpr int A_BYTES = BM * BK * 2;            // 16 KB
 constexpr int B_BYTES = BN * BK * 2;            // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
 constexpr int TMEM_COLS = 512;
-constexpr int NUM_THREADS = 192;
-constexpr int MAX_GROUPS = 320;
+constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
+constexpr int MAX_GROUPS = 320;  // barriers + flags + (MAX_GROUPS + 1) ints must fit in 2 KB
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -196,27 +196,52 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ float2 unpack_bf16(uint32_t v) {
   return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&v));
 }
-__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.f / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoidf_fast(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
-// Store 32 consecutive bf16 (64 B) given as 32 fp32 register values.
-__device__ __forceinline__ void store32(__nv_bfloat16* dst, const uint32_t (&r)[32]) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
+// ---------------------------------------------------------------- staged, row-contiguous stores
+// A warp's staging tile holds 32 rows x 64 B (4 pieces of 16 B per row).  Piece p of row r lives at
+// index r*4 + (p ^ ((r >> 1) & 3)), which makes both the row-wise writes (lane = row) and the
+// flush reads (8 rows x 4 pieces per instruction) free of bank conflicts.
+__device__ __forceinline__ int stage_index(int r, int p) { return r * 4 + (p ^ ((r >> 1) & 3)); }
+
+__device__ __forceinline__ void pack_row(const uint32_t (&r)[32], uint4 (&out)[4], bool keep) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    uint4 v;
-    v.x = pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1]));
-    v.y = pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3]));
-    v.z = pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5]));
-    v.w = pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7]));
-    d4[i] = v;
+    out[i].x = keep ? pack_bf16(__uint_as_float(r[8 * i + 0]), __uint_as_float(r[8 * i + 1])) : 0u;
+    out[i].y = keep ? pack_bf16(__uint_as_float(r[8 * i + 2]), __uint_as_float(r[8 * i + 3])) : 0u;
+    out[i].z = keep ? pack_bf16(__uint_as_float(r[8 * i + 4]), __uint_as_float(r[8 * i + 5])) : 0u;
+    out[i].w = keep ? pack_bf16(__uint_as_float(r[8 * i + 6]), __uint_as_float(r[8 * i + 7])) : 0u;
   }
 }
-__device__ __forceinline__ void store32_zero(__nv_bfloat16* dst) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
+// lane = row: write the lane's 64 B
+__device__ __forceinline__ void stage_store(uint4* tile, int lane, const uint4 (&p)[4]) {
+  __syncwarp();
 #pragma unroll
-  for (int i = 0; i < 4; ++i) d4[i] = make_uint4(0, 0, 0, 0);
+  for (int i = 0; i < 4; ++i) tile[stage_index(lane, i)] = p[i];
+  __syncwarp();
 }
-
+// Direct per-thread access to 64 B of the lane's own row (null row: zeros / skipped).
+__device__ __forceinline__ void row_load(const char* rowptr, int byte_off, uint4 (&regs)[4]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+    regs[i] = rowptr ? *reinterpret_cast<const uint4*>(rowptr + byte_off + i * 16) : make_uint4(0, 0, 0, 0);
+}
+__device__ __forceinline__ void row_store(char* rowptr, int byte_off, const uint4 (&regs)[4]) {
+  if (rowptr == nullptr) return;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(rowptr + byte_off + i * 16) = regs[i];
+}
+// Write the tile out: instruction `it` covers rows it*8 .. it*8+7, four lanes per row.  `rowptr`
+// is each lane's own row base (null: skip the row); the owner lane's pointer is fetched by shuffle.
+__device__ __forceinline__ void stage_flush(const uint4* tile, int lane, char* rowptr, int byte_off) {
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(rowptr);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int r = it * 8 + (lane >> 2), p = lane & 3;
+    const unsigned long long base = __shfl_sync(0xffffffffu, mine, r);
+    if (base != 0ull) *reinterpret_cast<uint4*>(base + byte_off + p * 16) = tile[stage_index(r, p)];
+  }
+}
 // ---------------------------------------------------------------- kernel
 template <int kMode>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -234,6 +259,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* tile_prefix = abort_flag + 1;  // [MAX_GROUPS + 1]
+  uint4* stage_tiles = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 2048);  // 8 warps x 2 KB
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Shape shape = make_shape<kMode>(args);
@@ -245,7 +271,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 4);
+      mbar_init(&acc_empty[b], 8);
     }
     *abort_flag = 0;
     int acc = 0;
@@ -355,13 +381,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     __syncwarp();
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
-    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    // ------------------------------------------------------------ epilogue (warps 2..9)
+    // Each warp owns 32 accumulator rows.  Columns are processed 32 at a time: the TMEM load of
+    // chunk c+1 is in flight while chunk c is converted, staged through a private 2 KB shared
+    // tile and written out with row-contiguous 16-byte stores (8 rows x 64 B per instruction).
+    const int quarter = warp & 3;      // TMEM lanes [32*quarter, 32*quarter + 32)
+    const int half = (warp - 2) >> 2;  // which half of the tile's column chunks this warp handles
+    uint4* stg = stage_tiles + (warp - 2) * 128;
     uint32_t acc_phase[2] = {0, 0};
     int local = 0;
     Tile t;
-    __nv_bfloat16* out0 = reinterpret_cast<__nv_bfloat16*>(args.out0);
-    __nv_bfloat16* out1 = reinterpret_cast<__nv_bfloat16*>(args.out1);
+    char* out0 = reinterpret_cast<char*>(args.out0);
+    char* out1 = reinterpret_cast<char*>(args.out1);
     for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x, ++local) {
       if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
       const int buf = local & 1;
@@ -370,7 +401,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
       const int r_in_tile = quarter * 32 + lane;
-      uint32_t v[32];
 
       if (kMode == kFwd1) {
         const int row_in_group = t.mt * BM + r_in_tile;
@@ -378,30 +408,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool in_buf = row < (size_t)args.row_capacity;
         const bool real = row_in_group < t.rows && in_buf;
         const int F = args.N;
-        __nv_bfloat16* hrow = out0 + row * (size_t)(2 * F) + t.nt * 128;
-        __nv_bfloat16* arow = out1 + row * (size_t)F + t.nt * 128;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t up[32];
-          tmem_ld32(taddr + c * 32, v);
-          tmem_ld32(taddr + 128 + c * 32, up);
-          tmem_ld_wait();
-          if (real) {
-            store32(hrow + c * 32, v);
-            store32(hrow + F + c * 32, up);
+        char* hrow = in_buf ? out0 + (row * (size_t)(2 * F) + t.nt * 128) * 2 : nullptr;
+        char* arow = in_buf ? out1 + (row * (size_t)F + t.nt * 128) * 2 : nullptr;
+        uint32_t g[2][32], u[2][32];
+        const int cb = half * 2;  // this warp's two 32-column chunks of the gate (and up) half
+        tmem_ld32(taddr + cb * 32, g[0]);
+        tmem_ld32(taddr + 128 + cb * 32, u[0]);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              // activation computed from the bf16-rounded pre-activations that backward will see
-              float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[i])));
-              float u = __bfloat162float(__float2bfloat16_rn(__uint_as_float(up[i])));
-              v[i] = __float_as_uint(g * sigmoidf_fast(g) * u);
-            }
-            store32(arow + c * 32, v);
-          } else if (in_buf) {
-            store32_zero(hrow + c * 32);
-            store32_zero(hrow + F + c * 32);
-            store32_zero(arow + c * 32);
+        for (int k = 0; k < 2; ++k) {
+          const int c = cb + k;
+          tmem_ld_wait();
+          if (k + 1 < 2) {
+            tmem_ld32(taddr + (c + 1) * 32, g[(k + 1) & 1]);
+            tmem_ld32(taddr + 128 + (c + 1) * 32, u[(k + 1) & 1]);
           }
+          uint32_t(&gv)[32] = g[k & 1];
+          uint32_t(&uv)[32] = u[k & 1];
+          uint4 pg[4], pu[4], pa[4];
+          pack_row(gv, pg, real);
+          pack_row(uv, pu, real);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            // activation from the bf16-rounded pre-activations, exactly what backward will read
+            float2 g2 = unpack_bf16((&pg[0].x)[i]), u2 = unpack_bf16((&pu[0].x)[i]);
+            (&pa[0].x)[i] = pack_bf16(g2.x * sigmoidf_fast(g2.x) * u2.x, g2.y * sigmoidf_fast(g2.y) * u2.y);
+          }
+          stage_store(stg, lane, pg);
+          stage_flush(stg, lane, hrow, c * 64);
+          stage_store(stg, lane, pu);
+          stage_flush(stg, lane, hrow, F * 2 + c * 64);
+          stage_store(stg, lane, pa);
+          stage_flush(stg, lane, arow, c * 64);
         }
       } else if (kMode == kDgrad2) {
         const int row_in_group = t.mt * BM + r_in_tile;
@@ -409,78 +446,90 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const bool in_buf = row < (size_t)args.row_capacity;
         const bool real = row_in_group < t.rows && in_buf;
         const int F = args.N;
-        __nv_bfloat16* hrow = out0 + row * (size_t)(2 * F);
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = t.nt * BN + c * 32;
-          if (col >= F) break;
-          tmem_ld32(taddr + c * 32, v);
-          tmem_ld_wait();
-          if (real) {
-            uint4* gp = reinterpret_cast<uint4*>(hrow + col);
-            uint4* up = reinterpret_cast<uint4*>(hrow + F + col);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 gv = gp[i], uv = up[i], dg, du;
-              uint32_t* gs = &gv.x;
-              uint32_t* us = &uv.x;
-              uint32_t* dgs = &dg.x;
-              uint32_t* dus = &du.x;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float2 g2 = unpack_bf16(gs[j]), u2 = unpack_bf16(us[j]);
-                float d0 = __uint_as_float(v[8 * i + 2 * j]), d1 = __uint_as_float(v[8 * i + 2 * j + 1]);
-                float s0 = sigmoidf_fast(g2.x), s1 = sigmoidf_fast(g2.y);
-                // d/dg [g*s(g)] = s + g*s*(1-s)
-                dgs[j] = pack_bf16(d0 * u2.x * (s0 + g2.x * s0 * (1.f - s0)), d1 * u2.y * (s1 + g2.y * s1 * (1.f - s1)));
-                dus[j] = pack_bf16(d0 * g2.x * s0, d1 * g2.y * s1);
-              }
-              gp[i] = dg;
-              up[i] = du;
-            }
-          } else if (in_buf) {
-            store32_zero(hrow + col);
-            store32_zero(hrow + F + col);
-          }
+        char* hrow = in_buf ? out0 + row * (size_t)(2 * F) * 2 : nullptr;
+        const int col0 = t.nt * BN;
+        const int nchunks = min(BN / 32, (F - col0) / 32);
+        uint32_t v[2][32];
+        uint4 lg[2][4], lu[2][4];  // this row's saved gate / up pre-activations, one chunk ahead
+        const int cb = half * 4;  // this warp's four 32-column chunks
+        if (cb < nchunks) {
+          tmem_ld32(taddr + cb * 32, v[0]);
+          row_load(hrow, (col0 + cb * 32) * 2, lg[0]);
+          row_load(hrow, (F + col0 + cb * 32) * 2, lu[0]);
         }
-      } else if (kMode == kWgrad) {
-        const int m = t.mt * BM + r_in_tile;
-        const bool real = m < args.M_out;
-        __nv_bfloat16* orow = out0 + ((size_t)t.wslot * args.M_out + (real ? m : 0)) * (size_t)args.N;
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = t.nt * BN + c * 32;
-          if (col >= args.N) break;
-          if (t.kblocks > 0) {
-            tmem_ld32(taddr + c * 32, v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = cb + k;
+          if (c < nchunks) {
             tmem_ld_wait();
-            if (real) store32(orow + col, v);
-          } else if (real) {
-            store32_zero(orow + col);  // an expert that received no rows has a zero gradient
+            if (k + 1 < 4 && c + 1 < nchunks) {
+              tmem_ld32(taddr + (c + 1) * 32, v[(k + 1) & 1]);
+              row_load(hrow, (col0 + (c + 1) * 32) * 2, lg[(k + 1) & 1]);
+              row_load(hrow, (F + col0 + (c + 1) * 32) * 2, lu[(k + 1) & 1]);
+            }
+            uint4 dg[4], du[4];
+            uint4(&pg)[4] = lg[k & 1];
+            uint4(&pu)[4] = lu[k & 1];
+            uint32_t(&dv)[32] = v[k & 1];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              float2 g2 = unpack_bf16((&pg[0].x)[i]), u2 = unpack_bf16((&pu[0].x)[i]);
+              float d0 = __uint_as_float(dv[2 * i]), d1 = __uint_as_float(dv[2 * i + 1]);
+              float s0 = sigmoidf_fast(g2.x), s1 = sigmoidf_fast(g2.y);
+              // d/dg [g*s(g)] = s + g*s*(1-s)
+              const uint32_t vg = pack_bf16(d0 * u2.x * (s0 + g2.x * s0 * (1.f - s0)), d1 * u2.y * (s1 + g2.y * s1 * (1.f - s1)));
+              const uint32_t vu = pack_bf16(d0 * g2.x * s0, d1 * g2.y * s1);
+              (&dg[0].x)[i] = real ? vg : 0u;  // padding rows are written as exact zeros
+              (&du[0].x)[i] = real ? vu : 0u;
+            }
+            row_store(hrow, (col0 + c * 32) * 2, dg);
+            row_store(hrow, (F + col0 + c * 32) * 2, du);
           }
         }
       } else {
-        // kFwd2 / kDgrad1 / kPlain: plain rows, optionally scattered to the unit's source rank
-        const int row_in_group = t.mt * BM + r_in_tile;
-        const size_t row = (size_t)t.row0 + row_in_group;
-        const bool real = row_in_group < t.rows && row < (size_t)args.row_capacity;
-        __nv_bfloat16* orow = nullptr;
-        if (real) {
-          if (args.meta != nullptr) {
-            const int2 mt = args.meta[row];
-            __nv_bfloat16* base = args.out_ptrs ? reinterpret_cast<__nv_bfloat16*>(args.out_ptrs[mt.x]) : out0;
-            orow = base + (size_t)mt.y * args.N;
-          } else {
-            orow = out0 + row * (size_t)args.N;
+        // kFwd2 / kDgrad1 / kPlain: plain rows, optionally scattered to the unit's source rank.
+        // kWgrad: rows of the weight gradient of this group's slot.
+        char* orow = nullptr;
+        int n_total = args.N;
+        bool have_acc = true;
+        if (kMode == kWgrad) {
+          const int m = t.mt * BM + r_in_tile;
+          if (m < args.M_out) orow = out0 + ((size_t)t.wslot * args.M_out + m) * (size_t)args.N * 2;
+          have_acc = t.kblocks > 0;  // an expert that received no rows has a zero gradient
+        } else {
+          const int row_in_group = t.mt * BM + r_in_tile;
+          const size_t row = (size_t)t.row0 + row_in_group;
+          if (row_in_group < t.rows && row < (size_t)args.row_capacity) {
+            if (args.meta != nullptr) {
+              const int2 mt = args.meta[row];
+              char* base = args.out_ptrs ? reinterpret_cast<char*>(args.out_ptrs[mt.x]) : out0;
+              orow = base + (size_t)mt.y * args.N * 2;
+            } else {
+              orow = out0 + row * (size_t)args.N * 2;
+            }
           }
         }
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          const int col = t.nt * BN + c * 32;
-          if (col >= args.N) break;
-          tmem_ld32(taddr + c * 32, v);
-          tmem_ld_wait();
-          if (real) store32(orow + col, v);
+        const int col0 = t.nt * BN;
+        const int nchunks = min(BN / 32, (n_total - col0) / 32);
+        uint32_t v[2][32];
+        const int cb = half * 4;  // this warp's four 32-column chunks
+        if (have_acc && cb < nchunks) tmem_ld32(taddr + cb * 32, v[0]);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int c = cb + k;
+          if (c < nchunks) {
+            uint4 pk[4];
+            if (have_acc) {
+              tmem_ld_wait();
+              if (k + 1 < 4 && c + 1 < nchunks) tmem_ld32(taddr + (c + 1) * 32, v[(k + 1) & 1]);
+              pack_row(v[k & 1], pk, true);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) pk[i] = make_uint4(0, 0, 0, 0);
+            }
+            stage_store(stg, lane, pk);
+            stage_flush(stg, lane, orow, (col0 + c * 32) * 2);
+          }
         }
       }
       tc_fence_before();
@@ -503,7 +552,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-constexpr size_t kSmemBytes = STAGES * STAGE_BYTES + 1024 /*align*/ + 16 * 8 /*barriers*/ + 16 + 4 * (MAX_GROUPS + 2);
+constexpr size_t kSmemBytes = STAGES * STAGE_BYTES + 1024 /*align*/ + 2048 /*barriers, flags, tile prefix*/ + 8 * 2048 /*staging*/;
 
 // ---------------------------------------------------------------- tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

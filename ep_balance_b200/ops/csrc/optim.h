@@ -1,0 +1,22 @@
+// Fused AdamW over one flat tensor (optim.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace epb {
+
+struct AdamArgs {
+  void* param;       // bf16 or fp32
+  const void* grad;  // same dtype as param
+  void* exp_avg;     // same dtype as param
+  void* exp_avg_sq;  // same dtype as param
+  size_t numel;
+  float lr, beta1, beta2, eps, weight_decay;
+  float bias_correction1, bias_correction2_sqrt;  // 1 - beta1^t, sqrt(1 - beta2^t)
+  int is_bf16;
+};
+
+cudaError_t launch_adamw(const AdamArgs& a, cudaStream_t stream);
+
+}  // namespace epb

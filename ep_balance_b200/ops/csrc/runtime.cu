@@ -254,34 +254,84 @@ void MoeRuntime::reduce_weight_grads(cudaStream_t stream) {
   check(launch_grad_reduce(a, stream), "grad_reduce(w2)");
 }
 
+// ------------------------------------------------------------------ timing
+void MoeRuntime::enable_timing(bool on) {
+  timing_ = on;
+  for (auto& m : marks_) cudaEventDestroy(m.second);
+  marks_.clear();
+}
+void MoeRuntime::mark(const char* name, cudaStream_t stream) {
+  if (!timing_) return;
+  cudaEvent_t ev;
+  if (cudaEventCreate(&ev) != cudaSuccess) return;
+  cudaEventRecord(ev, stream);
+  marks_.emplace_back(name, ev);
+}
+std::vector<std::pair<std::string, float>> MoeRuntime::phase_times() {
+  std::vector<std::pair<std::string, float>> out;
+  if (marks_.empty()) return out;
+  cudaEventSynchronize(marks_.back().second);
+  for (size_t i = 1; i < marks_.size(); ++i) {
+    float ms = 0.f;
+    if (marks_[i - 1].first == "fwd_end") continue;  // gap between forward and backward is not a phase
+    cudaEventElapsedTime(&ms, marks_[i - 1].second, marks_[i].second);
+    out.emplace_back(marks_[i].first, ms);
+  }
+  for (auto& m : marks_) cudaEventDestroy(m.second);
+  marks_.clear();
+  return out;
+}
+
 // ------------------------------------------------------------------ whole passes
 void MoeRuntime::forward(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out,
                          int num_tokens, cudaStream_t stream) {
   const int U = num_tokens * cfg_.topk;
+  mark("fwd_begin", stream);
   publish(topk_idx, U, stream);
+  mark("publish", stream);
   solve(stream);
+  mark("solve", stream);
   route(topk_idx, U, stream);
+  mark("route", stream);
   dispatch_tokens(tokens, U, stream);
+  mark("dispatch", stream);
   pull_weights(stream);
+  mark("pull_weights", stream);
   barrier(1, stream);
+  mark("barrier1", stream);
   gemm1(stream);
+  mark("gemm1", stream);
   gemm2(stream);
+  mark("gemm2", stream);
   barrier(2, stream);
+  mark("barrier2", stream);
   reduce_out(topk_prob, out, num_tokens, stream);
+  mark("reduce_out", stream);
+  mark("fwd_end", stream);
 }
 
 void MoeRuntime::backward(const void* dout, const float* topk_prob, void* dtokens, float* dprob, int num_tokens,
                           cudaStream_t stream) {
   const int U = num_tokens * cfg_.topk;
+  mark("bwd_begin", stream);
   dispatch_grads(dout, topk_prob, dprob, U, stream);
+  mark("dispatch_grads", stream);
   barrier(3, stream);
+  mark("barrier3", stream);
   wgrad2(stream);
+  mark("wgrad2", stream);
   dgrad2(stream);
+  mark("dgrad2", stream);
   wgrad1(stream);
+  mark("wgrad1", stream);
   dgrad1(stream);
+  mark("dgrad1", stream);
   barrier(4, stream);
+  mark("barrier4", stream);
   reduce_dtokens(dtokens, num_tokens, stream);
+  mark("reduce_dtokens", stream);
   reduce_weight_grads(stream);
+  mark("reduce_weight_grads", stream);
 }
 
 }  // namespace epb

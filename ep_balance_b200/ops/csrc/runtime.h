@@ -9,6 +9,8 @@
 
 #include <map>
 #include <string>
+#include <utility>
+#include <vector>
 
 #include "grouped_gemm.h"
 #include "route.h"
@@ -58,6 +60,11 @@ class MoeRuntime {
   void backward(const void* dout, const float* topk_prob, void* dtokens, float* dprob, int num_tokens,
                 cudaStream_t stream);
 
+  // Optional per-phase device timing: events are recorded around every phase of forward() and
+  // backward(); phase_times() synchronises and returns (name, ms) pairs of the last pass pair.
+  void enable_timing(bool on);
+  std::vector<std::pair<std::string, float>> phase_times();
+
   int launches() const { return launches_; }
   void reset_launches() { launches_ = 0; }
   const LayerConfig& config() const { return cfg_; }
@@ -76,6 +83,9 @@ class MoeRuntime {
   SolverParams sp_{};
   RankTables tables_{};
   int launches_ = 0;
+  bool timing_ = false;
+  std::vector<std::pair<std::string, cudaEvent_t>> marks_;
+  void mark(const char* name, cudaStream_t stream);
   // tensor maps (built once: every buffer has a fixed address)
   CUtensorMap tm_x_k_, tm_act_k_, tm_dy_k_, tm_dh_k_;           // K-major A operands
   CUtensorMap tm_w1_k_, tm_w2_k_, tm_w1_mn_, tm_w2_mn_;          // weights as B

@@ -20,7 +20,7 @@ NAME = "_epb_C"
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 BUILD_DIR = HERE / "_build"
-SOURCES = ["binding.cpp", "solver.cu", "route.cu", "grouped_gemm.cu", "runtime.cu"]
+SOURCES = ["binding.cpp", "solver.cu", "route.cu", "grouped_gemm.cu", "runtime.cu", "optim.cu"]
 CUDA_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
               "--expt-relaxed-constexpr"]
 

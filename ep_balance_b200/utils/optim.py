@@ -1,0 +1,40 @@
+"""AdamW whose update is one native kernel launch per parameter tensor.
+
+Expert weights of :class:`~ep_balance_b200.models.moe_layer.FusedMoE` are two flat bf16 tensors
+per layer, so the whole expert update is two launches.  Moments are kept in the parameter's dtype
+(the convention of ``torch.optim.AdamW(fused=True)``).  No host synchronisation: the step count
+lives on the host and enters the kernel as two bias-correction scalars.
+"""
+
+from __future__ import annotations
+
+from typing import Iterable
+
+import torch
+
+from ..ops.extension import load
+
+
+class FusedAdamW(torch.optim.Optimizer):
+    def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 1e-2) -> None:
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+        self._ext = load()
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = closure() if closure is not None else None
+        for group in self.param_groups:
+            b1, b2 = group["betas"]
+            for p in group["params"]:
+                if p.grad is None:
+                    continue
+                st = self.state[p]
+                if not st:
+                    st["step"] = 0
+                    st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                    st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
+                st["step"] += 1
+                self._ext.adamw_step(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
+                                     group["eps"], group["weight_decay"], st["step"])
+        return loss
