@@ -52,7 +52,7 @@ class _Bcast(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         root, group = ctx.meta
-        g = grad.detach().clone().contiguous()
+        g = grad.detach().clone(memory_format=torch.contiguous_format)
         dist.reduce(g, dst=root, op=dist.ReduceOp.SUM, group=group)
         return g, None, None
 
