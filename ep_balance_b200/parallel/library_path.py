@@ -284,6 +284,8 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     distributed = dist.is_available() and dist.is_initialized()
     my_rank = dist.get_rank(group) if distributed else 0
     adapter = adapter or (AllToAllAdapter() if distributed else LocalAdapter())
+    if not distributed and not isinstance(adapter, LocalAdapter):
+        adapter = LocalAdapter()  # no process group: every transport degenerates to the identity
     device, dtype = tokens.device, tokens.dtype
     n_slot = int(spec.n_slot)
     chunks = int(num_chunks if num_chunks is not None else (os.environ.get("EPLB_CHUNKS", "1") or "1"))
