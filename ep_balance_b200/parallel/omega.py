@@ -25,9 +25,9 @@ def all_gather_omega(local_row: torch.Tensor, group: Optional["dist.ProcessGroup
     if not is_distributed():
         return Loads(row[None])
     world = dist.get_world_size(group)
-    out = row.new_empty((world, row.numel()))
+    out = row.new_empty(world * row.numel())  # flat: the layout every backend accepts
     dist.all_gather_into_tensor(out, row, group=group)
-    return Loads(out)
+    return Loads(out.view(world, row.numel()))
 
 
 def local_counts_from_routing(expert_ids: torch.Tensor, num_experts: int) -> torch.Tensor:
