@@ -54,6 +54,7 @@ class MoEConfig:
     inter_cost: int = 8
     router_dtype: torch.dtype = torch.float32
     normalize_topk: bool = True
+    gemm_ctas: int = 2  # 2: CTA-pair grouped GEMM (256-row tiles); 1: single-CTA kernel (128-row tiles)
 
 
 def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
@@ -82,8 +83,9 @@ def row_capacity(cfg: MoEConfig, world: int) -> int:
     U = cfg.max_tokens * cfg.top_k
     home_cap = -(-cfg.num_experts // world)
     w_slots = home_cap + (cfg.extra_slots if world > 1 else 0)
-    rows = int(U * (cfg.capacity_factor if world > 1 else 1.0)) + 128 * w_slots
-    return (rows + 127) // 128 * 128
+    tile = 128 * cfg.gemm_ctas  # every group starts on a GEMM M-tile boundary
+    rows = int(U * (cfg.capacity_factor if world > 1 else 1.0)) + tile * w_slots
+    return (rows + tile - 1) // tile * tile
 
 
 class _FusedMoEFunction(torch.autograd.Function):
@@ -192,7 +194,8 @@ class FusedMoE(nn.Module):
                       D=cfg.num_domains, u_min=sc.u_min, iters=iters, patience=sc.stage2_stagnation_patience,
                       allow_cross=int(sc.allow_cross_domain),
                       probe=int(sc.stage2_patience_all_scales and iters > sc.stage2_stagnation_patience + 1),
-                      s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync))
+                      s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync),
+                      gemm_ctas=cfg.gemm_ctas)
         self.rt = load().MoeRuntime(rt_cfg, ptrs)
         self.bind_grads()
 

@@ -60,6 +60,7 @@ LayerConfig config_from_dict(const py::dict& d) {
   c.s_tok = d.contains("s_tok") ? d["s_tok"].cast<int64_t>() : 0;
   c.num_sms = get_int(d, "num_sms", 148);
   c.multi_rank_sync = get_int(d, "multi_rank_sync", 1);
+  c.gemm_ctas = get_int(d, "gemm_ctas", 2);
   return c;
 }
 
@@ -113,12 +114,14 @@ void solve_plan(torch::Tensor omega, torch::Tensor dom, torch::Tensor cost, torc
 //   mode kWgrad:       out[S, M_out, N] = P[T, M_out]^T Q[T, N] per group
 void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor out0, c10::optional<torch::Tensor> out1,
                   torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor group_wslot, torch::Tensor totals,
-                  torch::Tensor status, int64_t num_sms) {
+                  torch::Tensor status, int64_t num_sms, int64_t ctas) {
   const c10::cuda::CUDAGuard guard(a.device());
+  TORCH_CHECK(ctas == 1 || ctas == 2, "ctas must be 1 or 2");
   TORCH_CHECK(a.scalar_type() == torch::kBFloat16 && b.scalar_type() == torch::kBFloat16, "bf16 operands only");
   TORCH_CHECK(a.is_contiguous() && b.is_contiguous() && out0.is_contiguous(), "operands must be contiguous");
   epb::GemmArgs g{};
   g.mode = (int)mode;
+  g.ctas = (int)ctas;
   g.group_off = dptr<const int32_t>(group_off, "group_off", torch::kInt32);
   g.group_rows = dptr<const int32_t>(group_rows, "group_rows", torch::kInt32);
   g.group_wslot = dptr<const int32_t>(group_wslot, "group_wslot", torch::kInt32);

@@ -22,11 +22,22 @@
 namespace epb {
 namespace {
 
-constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2;            // 16 KB
-constexpr int B_BYTES = BN * BK * 2;            // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;  // 48 KB
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2;  // 16 KB: this CTA's 128 rows of the A tile
 constexpr int TMEM_COLS = 512;
+
+// kCtas = 1: one CTA computes a 128 x 256 tile.  kCtas = 2: a CTA pair (thread-block cluster of
+// two SMs) computes a 256 x 256 tile with tcgen05.mma.cta_group::2; each CTA stages its own 128
+// rows of A and its own 128 columns of B, so per-SM operand traffic drops from 48 KB to 32 KB per
+// k-block and the shared-memory ring deepens from 4 to 6 stages.
+template <int kCtas>
+struct Geometry {
+  static constexpr int STAGES = kCtas == 2 ? 6 : 4;
+  static constexpr int B_BYTES = BN * BK * 2 / kCtas;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TILE_M = BM * kCtas;
+};
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
 constexpr int MAX_GROUPS = 320;  // barriers + flags + (MAX_GROUPS + 1) ints must fit in 2 KB
 
@@ -85,6 +96,71 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, u
       : "memory");
 }
 
+// ---- CTA-pair variants (thread-block cluster of 2; no multicast anywhere)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(saddr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Loads of a CTA pair complete on the barrier of the pair's even-ranked CTA (rank bit cleared).
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+template <int kCtas>
+__device__ __forceinline__ void tma2(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  if (kCtas == 2) tma_load_2d_pair(dst, map, bar, c0, c1);
+  else tma_load_2d(dst, map, bar, c0, c1);
+}
+template <int kCtas>
+__device__ __forceinline__ void tma3(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  if (kCtas == 2) tma_load_3d_pair(dst, map, bar, c0, c1, c2);
+  else tma_load_3d(dst, map, bar, c0, c1, c2);
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on ONE barrier (own or the peer's, given as a shared::cluster address) once every MMA
+// issued so far by the pair has completed.  Both CTAs are told with two of these.
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -141,10 +217,10 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes
   d |= (uint64_t)2 << 61;
   return d;
 }
-// Instruction descriptor for kind::f16: bf16 x bf16 -> fp32, M = 128.
-__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n) {
+// Instruction descriptor for kind::f16: bf16 x bf16 -> fp32; M = 128 (one CTA) or 256 (CTA pair).
+__host__ __device__ constexpr uint32_t make_idesc(bool a_mn, bool b_mn, int n, int m) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
-         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // ---------------------------------------------------------------- tiles
@@ -160,14 +236,14 @@ struct Shape {
   int n_groups, n_tiles_n, tile_n, m_tiles_fixed, kblocks_fixed;
 };
 
-template <int kMode>
+template <int kMode, int kCtas>
 __device__ __forceinline__ Shape make_shape(const GemmArgs& a) {
   Shape s;
   int ng = a.totals[1];
   s.n_groups = ng < a.n_groups_cap ? ng : a.n_groups_cap;
   s.tile_n = kMode == kFwd1 ? 128 : BN;
   s.n_tiles_n = ceil_div(a.N, s.tile_n);
-  s.m_tiles_fixed = kMode == kWgrad ? ceil_div(a.M_out, BM) : 0;
+  s.m_tiles_fixed = kMode == kWgrad ? ceil_div(a.M_out, Geometry<kCtas>::TILE_M) : 0;
   s.kblocks_fixed = kMode == kWgrad ? 0 : ceil_div(a.K, BK);
   return s;
 }
@@ -243,16 +319,18 @@ __device__ __forceinline__ void stage_flush(const uint4* tile, int lane, char* r
   }
 }
 // ---------------------------------------------------------------- kernel
-template <int kMode>
+template <int kMode, int kCtas>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs args) {
+  using G = Geometry<kCtas>;
+  constexpr int STAGES = G::STAGES, STAGE_BYTES = G::STAGE_BYTES, TILE_M = G::TILE_M;
   constexpr bool kAMn = kMode == kWgrad;
   constexpr bool kBMn = kMode == kWgrad || kMode == kDgrad2 || kMode == kDgrad1;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles = smem;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);  // barriers start 8-byte aligned
   uint64_t* empty_bar = full_bar + STAGES;
   uint64_t* acc_full = empty_bar + STAGES;  // [2]
   uint64_t* acc_empty = acc_full + 2;       // [2]
@@ -262,7 +340,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint4* stage_tiles = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 2048);  // 8 warps x 2 KB
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const Shape shape = make_shape<kMode>(args);
+  const Shape shape = make_shape<kMode, kCtas>(args);
+  const int cta_rank = kCtas == 2 ? (int)cluster_ctarank() : 0;  // rank 0 of a pair issues the MMAs
+  const int tile_first = blockIdx.x / kCtas, tile_stride = gridDim.x / kCtas;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -271,22 +351,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);
+      mbar_init(&acc_empty[b], 8 * kCtas);
     }
     *abort_flag = 0;
     int acc = 0;
     tile_prefix[0] = 0;
     for (int g = 0; g < shape.n_groups; ++g) {
-      int mt = kMode == kWgrad ? shape.m_tiles_fixed : ceil_div(args.group_rows[g], BM);
+      int mt = kMode == kWgrad ? shape.m_tiles_fixed : ceil_div(args.group_rows[g], TILE_M);
       acc += mt * shape.n_tiles_n;
       tile_prefix[g + 1] = acc;
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(tmem_slot, TMEM_COLS);
+  if (warp == 1) {
+    if (kCtas == 2) tmem_alloc_pair(tmem_slot, TMEM_COLS);
+    else tmem_alloc(tmem_slot, TMEM_COLS);
+  }
   tc_fence_before();
   __syncthreads();
+  if (kCtas == 2) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int total_tiles = tile_prefix[shape.n_groups];
@@ -294,65 +378,81 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      Tile t;
-      for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x) {
-        if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
-        const int arow = t.row0 + t.mt * BM;
-        for (int kb = 0; kb < t.kblocks; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v, args.status, 1)) break;
-          uint8_t* sA = tiles + stage * STAGE_BYTES;
-          uint8_t* sB = sA + A_BYTES;
-          mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-          if (kMode == kWgrad) {
-            const int krow = t.row0 + kb * BK;
-            for (int i = 0; i < 2; ++i) tma_load_2d(sA + i * 8192, &tmA, &full_bar[stage], t.mt * BM + 64 * i, krow);
-            for (int j = 0; j < 4; ++j) tma_load_2d(sB + j * 8192, &tmB, &full_bar[stage], t.nt * BN + 64 * j, krow);
-          } else {
-            tma_load_2d(sA, &tmA, &full_bar[stage], kb * BK, arow);
-            if (kMode == kFwd1) {
-              tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, t.nt * 128, t.wslot);
-              tma_load_3d(sB + 16384, &tmB, &full_bar[stage], kb * BK, args.N + t.nt * 128, t.wslot);
-            } else if (kBMn) {
-              for (int j = 0; j < 4; ++j)
-                tma_load_3d(sB + j * 8192, &tmB, &full_bar[stage], t.nt * BN + 64 * j, kb * BK, t.wslot);
-            } else {
-              tma_load_3d(sB, &tmB, &full_bar[stage], kb * BK, t.nt * BN, t.wslot);
-              tma_load_3d(sB + 16384, &tmB, &full_bar[stage], kb * BK, t.nt * BN + 128, t.wslot);
+    // The warp walks the tile list together; lane 0 issues the TMA loads.
+    int stage = 0;
+    uint32_t phase = 0;
+    Tile t;
+    for (int ti = tile_first; ti < total_tiles; ti += tile_stride) {
+      int go = 1;
+      if (lane == 0) {
+        if (*abort_v || !find_tile<kMode>(args, shape, tile_prefix, ti, t)) go = 0;
+        if (go) {
+          const int m_off = t.mt * TILE_M + cta_rank * BM;            // this CTA's rows of the tile
+          const int n_off = t.nt * BN + cta_rank * (BN / 2) * (kCtas - 1);  // this CTA's columns of B
+          constexpr int kBoxesB = 4 / kCtas;                          // 64-wide MN-major boxes of B
+          for (int kb = 0; kb < t.kblocks; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v, args.status, 1)) {
+              go = 0;
+              break;
             }
-          }
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+            uint8_t* sA = tiles + stage * STAGE_BYTES;
+            uint8_t* sB = sA + A_BYTES;
+            uint64_t* fb = &full_bar[stage];
+            if (cta_rank == 0) mbar_expect_tx(fb, STAGE_BYTES * kCtas);  // both CTAs' bytes land on the leader's barrier
+            if (kMode == kWgrad) {
+              const int krow = t.row0 + kb * BK;
+              for (int i = 0; i < 2; ++i) tma2<kCtas>(sA + i * 8192, &tmA, fb, m_off + 64 * i, krow);
+              for (int j = 0; j < kBoxesB; ++j) tma2<kCtas>(sB + j * 8192, &tmB, fb, n_off + 64 * j, krow);
+            } else {
+              tma2<kCtas>(sA, &tmA, fb, kb * BK, t.row0 + m_off);
+              if (kMode == kFwd1) {
+                // gate rows [nt*128, +128) and up rows [F + nt*128, +128): one half per CTA of a pair
+                if (kCtas == 2) {
+                  tma3<kCtas>(sB, &tmB, fb, kb * BK, cta_rank * args.N + t.nt * 128, t.wslot);
+                } else {
+                  tma3<kCtas>(sB, &tmB, fb, kb * BK, t.nt * 128, t.wslot);
+                  tma3<kCtas>(sB + 16384, &tmB, fb, kb * BK, args.N + t.nt * 128, t.wslot);
+                }
+              } else if (kBMn) {
+                for (int j = 0; j < kBoxesB; ++j) tma3<kCtas>(sB + j * 8192, &tmB, fb, n_off + 64 * j, kb * BK, t.wslot);
+              } else {
+                tma3<kCtas>(sB, &tmB, fb, kb * BK, n_off, t.wslot);
+                if (kCtas == 1) tma3<kCtas>(sB + 16384, &tmB, fb, kb * BK, n_off + 128, t.wslot);
+              }
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) break;
     }
-    __syncwarp();
   } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (lane == 0 && cta_rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       uint32_t acc_phase[2] = {0, 0};
       int local = 0;
       Tile t;
-      for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x, ++local) {
+      for (int ti = tile_first; ti < total_tiles && !*abort_v; ti += tile_stride, ++local) {
         if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
         const int buf = local & 1;
         if (!mbar_wait(&acc_empty[buf], acc_phase[buf] ^ 1u, abort_v, args.status, 2)) break;
         acc_phase[buf] ^= 1u;
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
-        // columns the MMA must produce for this tile (multiple of 16, at most 256)
+        // columns the MMA must produce for this tile (multiple of 16, at most 256); a CTA pair
+        // always produces all 256 because each CTA holds a fixed half of them
         int ncols = BN;
-        if (kMode != kFwd1) {
+        if (kMode != kFwd1 && kCtas == 1) {
           int left = args.N - t.nt * BN;
           if (left < BN) ncols = round_up(left, 16);
         }
-        const uint32_t idesc = make_idesc(kAMn, kBMn, ncols);
+        const uint32_t idesc = make_idesc(kAMn, kBMn, ncols, TILE_M);
         bool failed = false;
         for (int kb = 0; kb < t.kblocks; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_v, args.status, 3)) {
@@ -367,16 +467,34 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           constexpr uint32_t a_step = kAMn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
           constexpr uint32_t b_step = kBMn ? (UMMA_K * 128) >> 4 : (UMMA_K * 2) >> 4;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_bf16(tmem_d, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), idesc, (kb | k) ? 1u : 0u);
-          umma_commit(&empty_bar[stage]);  // frees the smem stage once these MMAs have read it
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            if (kCtas == 2)
+              umma_bf16_pair(tmem_d, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), idesc, (kb | k) ? 1u : 0u);
+            else
+              umma_bf16(tmem_d, da + (uint64_t)(k * a_step), db + (uint64_t)(k * b_step), idesc, (kb | k) ? 1u : 0u);
+          }
+          // frees the smem stage (in both CTAs of a pair) once these MMAs have read it
+          if (kCtas == 2) {
+            const uint32_t eb = smem_u32(&empty_bar[stage]);
+            umma_commit_pair(eb);
+            umma_commit_pair(map_to_cta(eb, 1));
+          } else {
+            umma_commit(&empty_bar[stage]);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
         if (failed) break;
-        umma_commit(&acc_full[buf]);  // accumulator ready for the epilogue
+        // accumulator ready for the epilogue warps (of both CTAs)
+        if (kCtas == 2) {
+          const uint32_t ab = smem_u32(&acc_full[buf]);
+          umma_commit_pair(ab);
+          umma_commit_pair(map_to_cta(ab, 1));
+        } else {
+          umma_commit(&acc_full[buf]);
+        }
       }
     }
     __syncwarp();
@@ -393,17 +511,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     Tile t;
     char* out0 = reinterpret_cast<char*>(args.out0);
     char* out1 = reinterpret_cast<char*>(args.out1);
-    for (int ti = blockIdx.x; ti < total_tiles && !*abort_v; ti += gridDim.x, ++local) {
+    for (int ti = tile_first; ti < total_tiles && !*abort_v; ti += tile_stride, ++local) {
       if (!find_tile<kMode>(args, shape, tile_prefix, ti, t)) break;
       const int buf = local & 1;
       if (!mbar_wait(&acc_full[buf], acc_phase[buf], abort_v, args.status, 4)) break;
       acc_phase[buf] ^= 1u;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
-      const int r_in_tile = quarter * 32 + lane;
+      const int r_in_tile = cta_rank * BM + quarter * 32 + lane;  // row inside the (pair's) M tile
 
       if (kMode == kFwd1) {
-        const int row_in_group = t.mt * BM + r_in_tile;
+        const int row_in_group = t.mt * TILE_M + r_in_tile;
         const size_t row = (size_t)t.row0 + row_in_group;  // rows up to the padded end exist in the buffers
         const bool in_buf = row < (size_t)args.row_capacity;
         const bool real = row_in_group < t.rows && in_buf;
@@ -441,7 +559,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           stage_flush(stg, lane, arow, c * 64);
         }
       } else if (kMode == kDgrad2) {
-        const int row_in_group = t.mt * BM + r_in_tile;
+        const int row_in_group = t.mt * TILE_M + r_in_tile;
         const size_t row = (size_t)t.row0 + row_in_group;
         const bool in_buf = row < (size_t)args.row_capacity;
         const bool real = row_in_group < t.rows && in_buf;
@@ -493,11 +611,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         int n_total = args.N;
         bool have_acc = true;
         if (kMode == kWgrad) {
-          const int m = t.mt * BM + r_in_tile;
+          const int m = t.mt * TILE_M + r_in_tile;
           if (m < args.M_out) orow = out0 + ((size_t)t.wslot * args.M_out + m) * (size_t)args.N * 2;
           have_acc = t.kblocks > 0;  // an expert that received no rows has a zero gradient
         } else {
-          const int row_in_group = t.mt * BM + r_in_tile;
+          const int row_in_group = t.mt * TILE_M + r_in_tile;
           const size_t row = (size_t)t.row0 + row_in_group;
           if (row_in_group < t.rows && row < (size_t)args.row_capacity) {
             if (args.meta != nullptr) {
@@ -534,7 +652,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) {  // the accumulator buffer is free again: tell the MMA issuer (leader CTA)
+        if (kCtas == 2) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+        else mbar_arrive(&acc_empty[buf]);
+      }
     }
   }
 
@@ -546,13 +667,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
   }
   __syncthreads();
+  if (kCtas == 2) cluster_sync_all();  // neither CTA leaves while the other may still signal it
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (kCtas == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
-constexpr size_t kSmemBytes = STAGES * STAGE_BYTES + 1024 /*align*/ + 2048 /*barriers, flags, tile prefix*/ + 8 * 2048 /*staging*/;
+template <int kCtas>
+constexpr size_t smem_bytes() {
+  return Geometry<kCtas>::STAGES * Geometry<kCtas>::STAGE_BYTES + 1024 /*align*/ + 2048 /*barriers, flags, tile prefix*/ +
+         8 * 2048 /*staging*/;
+}
 
 // ---------------------------------------------------------------- tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -599,18 +726,44 @@ bool make_tmap_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t r
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int kMode>
+template <int kMode, int kCtas>
 static cudaError_t launch_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
                                cudaStream_t stream) {
   static bool configured = false;
+  constexpr size_t smem = smem_bytes<kCtas>();
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  grouped_gemm_kernel<kMode><<<num_sms, NUM_THREADS, kSmemBytes, stream>>>(tmA, tmB, args);
-  return cudaGetLastError();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(num_sms / kCtas * kCtas));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kCtas;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<kMode, kCtas>, tmA, tmB, args);
+}
+
+template <int kCtas>
+static cudaError_t launch_ctas(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
+                               cudaStream_t stream) {
+  switch (args.mode) {
+    case kFwd1: return launch_mode<kFwd1, kCtas>(tmA, tmB, args, num_sms, stream);
+    case kFwd2: return launch_mode<kFwd2, kCtas>(tmA, tmB, args, num_sms, stream);
+    case kDgrad2: return launch_mode<kDgrad2, kCtas>(tmA, tmB, args, num_sms, stream);
+    case kDgrad1: return launch_mode<kDgrad1, kCtas>(tmA, tmB, args, num_sms, stream);
+    case kWgrad: return launch_mode<kWgrad, kCtas>(tmA, tmB, args, num_sms, stream);
+    case kPlain: return launch_mode<kPlain, kCtas>(tmA, tmB, args, num_sms, stream);
+    default: return cudaErrorInvalidValue;
+  }
 }
 
 cudaError_t launch_grouped_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
@@ -618,15 +771,8 @@ cudaError_t launch_grouped_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, 
   if (args.n_groups_cap > MAX_GROUPS) return cudaErrorInvalidValue;
   if (args.mode == kFwd1 && args.N % 128 != 0) return cudaErrorInvalidValue;
   if (args.N % 32 != 0) return cudaErrorInvalidValue;
-  switch (args.mode) {
-    case kFwd1: return launch_mode<kFwd1>(tmA, tmB, args, num_sms, stream);
-    case kFwd2: return launch_mode<kFwd2>(tmA, tmB, args, num_sms, stream);
-    case kDgrad2: return launch_mode<kDgrad2>(tmA, tmB, args, num_sms, stream);
-    case kDgrad1: return launch_mode<kDgrad1>(tmA, tmB, args, num_sms, stream);
-    case kWgrad: return launch_mode<kWgrad>(tmA, tmB, args, num_sms, stream);
-    case kPlain: return launch_mode<kPlain>(tmA, tmB, args, num_sms, stream);
-    default: return cudaErrorInvalidValue;
-  }
+  if (args.ctas == 2) return launch_ctas<2>(tmA, tmB, args, num_sms, stream);
+  return launch_ctas<1>(tmA, tmB, args, num_sms, stream);
 }
 
 }  // namespace epb

@@ -21,8 +21,10 @@ enum GemmMode : int { kFwd1 = 0, kFwd2 = 1, kDgrad2 = 2, kDgrad1 = 3, kWgrad = 4
 
 struct GemmArgs {
   int mode;
+  int ctas;                    // 1: one CTA per 128-row tile; 2: CTA pair (cta_group::2) per 256-row tile.
+                               // Groups must start on multiples of 128 * ctas rows.
   // group geometry (device)
-  const int32_t* group_off;    // [n_groups_cap + 1] first row of each group (multiple of 128)
+  const int32_t* group_off;    // [n_groups_cap + 1] first row of each group (multiple of 128 * ctas)
   const int32_t* group_rows;   // [n_groups_cap]
   const int32_t* group_wslot;  // [n_groups_cap]
   const int32_t* totals;       // [2]: padded rows, number of groups

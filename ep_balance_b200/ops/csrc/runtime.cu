@@ -38,7 +38,8 @@ void MoeRuntime::tmap3(CUtensorMap* m, const void* base, uint64_t slots, uint64_
 MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint64_t>& ptrs) : cfg_(cfg), ptrs_(ptrs) {
   const LayerConfig& c = cfg_;
   if (c.H % 64 || c.F % 128) throw std::runtime_error("MoeRuntime: need H % 64 == 0 and F % 128 == 0");
-  if (c.row_capacity % 128) throw std::runtime_error("MoeRuntime: row_capacity must be a multiple of 128");
+  if (c.gemm_ctas != 1 && c.gemm_ctas != 2) throw std::runtime_error("MoeRuntime: gemm_ctas must be 1 or 2");
+  if (c.row_capacity % (128 * c.gemm_ctas)) throw std::runtime_error("MoeRuntime: row_capacity must be a multiple of the GEMM M tile");
 
   sp_.omega = ptr<const int32_t>("omega");
   sp_.dom = ptr<const int32_t>("dom");
@@ -70,7 +71,7 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
 
   tables_.me = c.me;
   tables_.n_slot = c.w_slots;
-  tables_.row_align = 128;
+  tables_.row_align = 128 * c.gemm_ctas;
   tables_.row_capacity = c.row_capacity;
   tables_.home_cap = c.home_cap;
   tables_.home_index = ptr<const int32_t>("home_index");
@@ -168,6 +169,7 @@ void MoeRuntime::gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int 
                       void* out1, void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
   GemmArgs g{};
   g.mode = mode;
+  g.ctas = cfg_.gemm_ctas;
   g.group_off = tables_.group_off;
   g.group_rows = tables_.group_rows;
   g.group_wslot = tables_.group_wslot;

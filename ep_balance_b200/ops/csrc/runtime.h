@@ -28,6 +28,7 @@ struct LayerConfig {
   int D = 1, u_min = 1, iters = 64, patience = 8, allow_cross = 1, probe = 0;
   int64_t s_tok = 0;
   int num_sms = 148;
+  int gemm_ctas = 2;        // 2: grouped GEMMs run on CTA pairs (256-row tiles); 1: single CTAs (128-row tiles)
   int multi_rank_sync = 1;  // 0: one process emulates all ranks, kernels are ordered by the stream
 };
 

@@ -26,12 +26,14 @@ def main() -> None:
     ap.add_argument("--ffn", type=int, default=1408)
     ap.add_argument("--modes", default="fwd1,fwd2,dgrad2,dgrad1,wgrad")
     ap.add_argument("--iters", type=int, default=1)
+    ap.add_argument("--ctas", type=int, default=2, choices=[1, 2])
     a = ap.parse_args()
     ext = load()
     dev = torch.device("cuda")
     G, H, Fd = a.groups, a.hidden, a.ffn
     rows = [a.rows] * G
-    off = [i * ((a.rows + 127) // 128 * 128) for i in range(G + 1)]
+    tile = 128 * a.ctas
+    off = [i * ((a.rows + tile - 1) // tile * tile) for i in range(G + 1)]
     T = off[-1]
     i32 = dict(dtype=torch.int32, device=dev)
     goff, grows = torch.tensor(off, **i32), torch.tensor(rows, **i32)
@@ -55,7 +57,7 @@ def main() -> None:
     }
     for name in a.modes.split(","):
         A, B, o0, o1, flops = jobs[name]
-        run = lambda: ext.grouped_gemm(MODE[name], A, B, o0, o1, goff, grows, gws, totals, status, sms)
+        run = lambda: ext.grouped_gemm(MODE[name], A, B, o0, o1, goff, grows, gws, totals, status, sms, a.ctas)
         run()
         torch.cuda.synchronize()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

@@ -26,12 +26,13 @@ def _oracle(tokens, idx, prob, w1, w2, dout):
     return out.detach(), x.grad, p.grad, a.grad, b.grad
 
 
-def test_single_rank_forward_backward():
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_single_rank_forward_backward(ctas):
     from ep_balance_b200.models.emulated import EmulatedCluster
     from ep_balance_b200.models.moe_layer import MoEConfig
 
     torch.manual_seed(0)
-    cfg = MoEConfig(hidden=256, ffn=384, num_experts=8, top_k=2, max_tokens=512)
+    cfg = MoEConfig(hidden=256, ffn=384, num_experts=8, top_k=2, max_tokens=512, gemm_ctas=ctas)
     cl = EmulatedCluster(cfg, world=1)
     layer = cl.layers[0]
     tokens = torch.randn(512, 256, device="cuda").bfloat16()
