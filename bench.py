@@ -40,6 +40,7 @@ def parse():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--tokens", type=int, default=CFG["tokens_per_rank"])
+    p.add_argument("--gemm-ctas", type=int, default=2, choices=[1, 2], help="grouped GEMM: CTA pairs (2) or single CTAs (1)")
     p.add_argument("--phases", action="store_true", help="also print a per-phase device-time table (stderr)")
     return p.parse_args()
 
@@ -180,7 +181,8 @@ def run_ours(args):
 
     dev = torch.device("cuda", local)
     cfg = MoEConfig(hidden=CFG["hidden"], ffn=CFG["ffn"], num_experts=CFG["num_experts"], top_k=CFG["top_k"],
-                    max_tokens=args.tokens, extra_slots=CFG["extra_slots"], num_domains=DOMAINS.get(world, 1))
+                    max_tokens=args.tokens, extra_slots=CFG["extra_slots"], num_domains=DOMAINS.get(world, 1),
+                    gemm_ctas=args.gemm_ctas)
     heap = SymmetricHeap(heap_layout(cfg, world), dev)
     layer = FusedMoE(cfg, heap, rank, world)
     # same router on every rank
@@ -256,7 +258,8 @@ def run_ours(args):
     plan = layer.last_plan()
     loads = layer.rank_loads().float()
     extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],
-             "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return"}
+             "gemm_ctas": args.gemm_ctas,
+             "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return, fused AdamW"}
     if rank == 0:
         emit(args, world, "ours", ms_dev, ms_e2e, launches, clocks, batches[0].numel() * 2, 4, extra)
     if world > 1:
