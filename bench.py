@@ -253,8 +253,25 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else {}
     layer.check_status()
 
-    if args.phases and rank == 0:
-        phase_table(layer, dev_batches[0])
+    if args.phases:
+        if world == 1:
+            phase_table(layer, dev_batches[0])
+        else:
+            # multi-rank: events around every phase of whole steps (barrier waits included)
+            layer.rt.enable_timing(True)
+            acc = {}
+            for i in range(5):
+                step_device(i)
+                for name, ms in layer.rt.phase_times():
+                    acc.setdefault(name, []).append(ms)
+            layer.rt.enable_timing(False)
+            table = torch.tensor([[sum(v) / len(v)] for v in acc.values()], device=dev)
+            worst = table.clone()
+            dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+            dist.all_reduce(table, op=dist.ReduceOp.SUM)
+            if rank == 0:
+                for (name, _), mean, mx in zip(acc.items(), (table / world).flatten().tolist(), worst.flatten().tolist()):
+                    print(f"[phase] {name:<20} mean {mean:8.3f} ms   max over ranks {mx:8.3f} ms", file=sys.stderr)
     plan = layer.last_plan()
     loads = layer.rank_loads().float()
     extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],

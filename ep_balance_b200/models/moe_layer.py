@@ -153,6 +153,7 @@ class FusedMoE(nn.Module):
         self._gw1 = heap.tensor("gw1", rank)[: self.home_cap]
         self._gw2 = heap.tensor("gw2", rank)[: self.home_cap]
         self.router_bias: Optional[torch.Tensor] = None  # additive logit skew (synthetic workloads)
+        self.route_fn = None  # optional ``logits [N, E] -> (top_idx int64 [N, K], prob fp32 [N, K])``
 
         # ---- local state
         i32 = dict(dtype=torch.int32, device=dev)
@@ -214,6 +215,9 @@ class FusedMoE(nn.Module):
             logits = tokens.to(self.router.dtype) @ self.router.t()
             if self.router_bias is not None:
                 logits = logits + self.router_bias
+            if self.route_fn is not None:
+                top_idx, prob = self.route_fn(logits)
+                return top_idx.contiguous(), prob.float().contiguous()
             top_val, top_idx = torch.topk(logits, self.cfg.top_k, dim=-1)
             prob = torch.softmax(top_val.float(), dim=-1) if self.cfg.normalize_topk else torch.sigmoid(top_val.float())
         return top_idx.contiguous(), prob.contiguous()
