@@ -4,8 +4,9 @@
     python -m ep_balance_b200.launch.solver_scaling --ranks 8 --experts 64 --domains 2 --extra-slots 2
 
 All logical ranks are simulated on one GPU (the solver is replicated, not distributed).  Timing is
-kernel-only: CUDA events around ``iters`` back-to-back solves after ``warmup`` solves; ``min_us`` is
-the smallest single-solve time over ``repeats`` such batches.  ``--impl reference`` times the
+reported twice: ``min_us`` / ``median_us`` are API-level (CUDA events around ``iters`` back-to-back
+``solve()`` calls, so tensor allocation, dtype casts and Python dispatch count), ``kernel_min_us`` /
+``kernel_median_us`` are the solver kernels alone, one event pair per call.  ``--impl reference`` times the
 upstream CUDA solver from ``baseline/_ref`` the same way.  Reference driver:
 tests/test_gpu_solver.py:287-679, scripts/run_solver_scaling.sh:10-22.
 """
@@ -36,6 +37,89 @@ def _time(fn, warmup: int, iters: int, repeats: int) -> Dict[str, float]:
         per.append(a.elapsed_time(b) * 1e3 / iters)
     per.sort()
     return {"min_us": per[0], "median_us": per[len(per) // 2]}
+
+
+def _time_each(fn, before, warmup: int, iters: int) -> Dict[str, float]:
+    """Per-launch device time: an event pair around every call, state reset outside the pair."""
+    for _ in range(warmup):
+        before()
+        fn()
+    torch.cuda.synchronize()
+    pairs = []
+    for _ in range(iters):
+        before()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        pairs.append((a, b))
+    torch.cuda.synchronize()
+    us = sorted(a.elapsed_time(b) * 1e3 for a, b in pairs)
+    return {"kernel_min_us": us[0], "kernel_median_us": us[len(us) // 2]}
+
+
+def kernel_only(ranks: int, experts: int, domains: int, extra: int, skew: float, impl: str, warmup: int,
+                iters: int) -> Dict[str, float]:
+    """Solver kernels alone (no tensor allocation, casts or Python-side preparation in the timed span).
+
+    Ours: the single cooperative launch behind ``ext.solve_plan``.  Reference: its three-kernel
+    ``backend.fast_solve`` call on candidate arrays prepared beforehand, with its accumulators and
+    placement reset before every call outside the timed span (the method of its own perf driver,
+    tests/test_gpu_solver.py:407-435)."""
+    from ..utils.workload import make_loads
+
+    dev = torch.device("cuda")
+    omega = make_loads(ranks, experts, 4096, 8, skew, 0.25, 0).omega.to(dev)
+    n_slot = -(-experts // ranks) + extra
+    wb, s_tok = 3 * 7168 * 2048 * 2, 7168 * 2
+    if impl == "reference":
+        import eplb
+        from eplb import cuda_solve as cs
+
+        topo = eplb.Topology.from_nvlink_rdma(domains, ranks // domains, device=dev)
+        spec = eplb.ProblemSpec.uniform_main_placement(experts, ranks, wb, s_tok, n_slot, device=dev)
+        loads, cfg = eplb.Loads(omega), eplb.EPLBConfig()
+        backend = cs._get_backend()
+        om = loads.omega.to(torch.int64).contiguous()
+        dom = topo.domain_of_rank.to(torch.int64).contiguous()
+        cost = topo.cost.to(torch.int64).contiguous()
+        x0 = torch.zeros((experts, ranks), dtype=torch.int8, device=dev)
+        x0.scatter_(1, spec.main_rank.view(experts, 1), 1)
+        su0 = x0.sum(0).to(torch.int64)
+        ce, cd, cv = cs._stage1_candidates(loads, topo, spec)
+        x, su = x0.clone(), su0.clone()
+        q = torch.zeros((ranks, experts, ranks), dtype=torch.int64, device=dev)
+        erl = torch.zeros((experts, ranks), dtype=torch.int64, device=dev)
+        rl = torch.zeros(ranks, dtype=torch.int64, device=dev)
+        stuck = torch.zeros(ranks, dtype=torch.uint8, device=dev)
+        ctl = torch.zeros(3, dtype=torch.int64, device=dev)
+
+        def before():
+            x.copy_(x0)
+            su.copy_(su0)
+            erl.zero_()
+            rl.zero_()
+            stuck.zero_()
+
+        fn = lambda: backend.fast_solve(om, x, cost, dom, q, erl, ce, cd, cv, su, rl, stuck, ctl, int(domains),
+                                        int(n_slot), 64, 8, False, 1, True)
+        return _time_each(fn, before, warmup, iters)
+    from .. import EPLBConfig, ProblemSpec, Topology
+    from ..ops.extension import load
+    from ..ops.solver_op import _static_inputs, workspace
+
+    ext = load()
+    topo = Topology.from_nvlink_rdma(domains, ranks // domains)
+    spec = ProblemSpec.uniform_main_placement(experts, ranks, wb, s_tok, n_slot)
+    d, c, m, w = _static_inputs(topo, spec, dev)
+    ws = workspace(ranks, experts, dev)
+    om = omega.to(torch.int32).contiguous()
+    x = torch.empty((experts, ranks), dtype=torch.int8, device=dev)
+    q = torch.empty((ranks, experts, ranks), dtype=torch.int32, device=dev)
+    theta = torch.empty(1, dtype=torch.int64, device=dev)
+    fn = lambda: ext.solve_plan(om, d, c, m, w, s_tok, domains, n_slot, 1, 64, 8, True, False, x, q, ws.erl,
+                                ws.rank_load, ws.slot_used, ws.stuck, theta, ws.control, ws.sync, ws.status)
+    return _time_each(fn, lambda: None, warmup, iters)
 
 
 def measure(ranks: int, experts: int, domains: int, extra: int, skew: float, impl: str, warmup: int, iters: int,
@@ -69,6 +153,7 @@ def measure(ranks: int, experts: int, domains: int, extra: int, skew: float, imp
         fn = lambda: solve(loads, topo, spec, cfg, validate=False)
         plan = fn()
     t = _time(fn, warmup, iters, repeats)
+    t.update(kernel_only(ranks, experts, domains, extra, skew, impl, warmup, iters))
     load = plan.q.sum((0, 1)).double()
     return {"impl": impl, "ranks": ranks, "experts": experts, "domains": domains, "extra_slots": extra, "skew": skew,
             "imbalance": float(load.max() / load.mean()), "replicas": int(plan.x.sum()) - experts, **t}

@@ -63,7 +63,7 @@ __device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, unsi
       if (t0 == 0) t0 = now;
       else if (now - t0 > budget_ns) return false;
     }
-    __nanosleep(64);
+    if (spin > 64u) __nanosleep(32);  // back off only after a burst of immediate polls
   }
 }
 

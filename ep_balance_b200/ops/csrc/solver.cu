@@ -81,6 +81,9 @@ struct Smem {
   int* slot;        // [R]
   int* stuck;       // [R]
   Cand* wcand;      // [32]
+  int* erl_c;       // [E * n] cached erl[e, domain rank] of the domain being repaired (or null)
+  signed char* x_c; // [E * n] cached x[e, domain rank]
+  int* q_c;         // [R * E * n] cached q[s, e, domain rank] (or unused)
 };
 
 __device__ Smem carve(unsigned char* base, int R, int E) {
@@ -100,6 +103,10 @@ __device__ Smem carve(unsigned char* base, int R, int E) {
   s.stuck = reinterpret_cast<int*>(base);
   base += sizeof(int) * R;
   s.wcand = reinterpret_cast<Cand*>(base);
+  base += sizeof(Cand) * 32;
+  s.erl_c = reinterpret_cast<int*>(base);
+  s.x_c = reinterpret_cast<signed char*>(base + sizeof(int) * (size_t)E * R);
+  s.q_c = reinterpret_cast<int*>(base + (((size_t)E * R * 5 + 15) / 16) * 16);
   return s;
 }
 
@@ -128,6 +135,9 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
   const int R = p.R, E = p.E;
   const int n = collect_domain(p, s, d);
   if (n == 0) return;
+  // With the cache region available the domain's placement columns live in shared memory while
+  // candidates are admitted (one global round trip per candidate otherwise) and are stored once.
+  signed char* xc = p.cache_stage2 ? s.x_c : nullptr;
   if (tid == 0) n_valid = 0;
   for (int i = tid; i < n; i += nt) s.slot[i] = 0;
   __syncthreads();
@@ -136,7 +146,8 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
     int e = idx / n, i = idx - e * n;
     int r = s.dom_ranks[i];
     bool own = p.main_rank[e] == r;
-    p.x[(size_t)e * R + r] = own ? 1 : 0;
+    if (xc) xc[idx] = own ? 1 : 0;
+    else p.x[(size_t)e * R + r] = own ? 1 : 0;
     if (own) atomicAdd(&s.slot[i], 1);
   }
   // gate and benefit
@@ -170,7 +181,8 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
         bool present = false;
         long long key = LLONG_MAX;  // (slots used, domain-local index) of the best free rank
         for (int i = lane; i < n; i += kWarp) {
-          if (p.x[(size_t)e * R + s.dom_ranks[i]] != 0) present = true;
+          const bool here = xc ? xc[e * n + i] != 0 : p.x[(size_t)e * R + s.dom_ranks[i]] != 0;
+          if (here) present = true;
           int used = s.slot[i];
           if (used < p.n_slot) key = min(key, ((long long)used << 32) | (unsigned)i);
         }
@@ -178,7 +190,8 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
         for (int off = kWarp / 2; off > 0; off >>= 1) key = min(key, __shfl_down_sync(kFull, key, off));
         if (lane == 0 && any == 0 && key != LLONG_MAX) {
           int i = (int)(key & 0xffffffffll);
-          p.x[(size_t)e * R + s.dom_ranks[i]] = 1;
+          if (xc) xc[e * n + i] = 1;
+          else p.x[(size_t)e * R + s.dom_ranks[i]] = 1;
           s.slot[i] += 1;
         }
         __syncwarp(kFull);
@@ -186,10 +199,71 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
     }
   }
   __syncthreads();
+  if (xc)
+    for (int idx = tid; idx < E * n; idx += nt) {
+      int e = idx / n, i = idx - e * n;
+      p.x[(size_t)e * R + s.dom_ranks[i]] = xc[idx];
+    }
   for (int i = tid; i < n; i += nt) p.slot_used[s.dom_ranks[i]] = s.slot[i];
 }
 
 // ------------------------------------------------------------------ phase 1
+// Units a destination gets from one (src, e) pair under the even split: `act` is the set of active
+// hosts (bit per rank), `dst` one of them.
+__device__ __forceinline__ int even_share(int need, unsigned long long act, int dst, int u_min) {
+  const int count = __popcll(act);
+  if (need <= 0 || count == 0) return 0;
+  int n = count;
+  if (u_min > 1 && need >= u_min) n = min(count, need / u_min);
+  else if (need < u_min) n = 1;
+  const int pos = __popcll(act & ((1ull << dst) - 1ull));
+  return pos < n ? need / n + (pos < need % n ? 1 : 0) : 0;
+}
+
+// R <= 64: one thread per (src, e) pair writes its row of q, one thread per (e, dst) pair sums
+// erl; host sets are 64-bit masks held in shared memory.  Every pair is independent, so the whole
+// grid works on them at once instead of one warp walking an expert's sources serially.
+__device__ void phase1_routing_masks(const SolverParams& p, Smem& s) {
+  __shared__ unsigned long long dom_mask[64];
+  const int R = p.R, E = p.E, u_min = p.u_min;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  unsigned long long* host = reinterpret_cast<unsigned long long*>(s.prio);  // [E]
+  __syncthreads();
+  for (int e = tid; e < E; e += nt) {
+    unsigned long long m = 0;
+    for (int dst = 0; dst < R; ++dst) m |= (unsigned long long)(p.x[(size_t)e * R + dst] != 0) << dst;
+    host[e] = m;
+  }
+  for (int r = tid; r < R; r += nt) {
+    unsigned long long m = 0;
+    const int dr = p.dom[r];
+    for (int o = 0; o < R; ++o) m |= (unsigned long long)(p.dom[o] == dr) << o;
+    dom_mask[r] = m;
+  }
+  __syncthreads();
+  const int gtid = blockIdx.x * nt + tid, gthreads = gridDim.x * nt;
+  for (int pair = gtid; pair < R * E; pair += gthreads) {
+    const int src = pair / E, e = pair - src * E;
+    const int need = p.omega[pair];
+    const unsigned long long loc = host[e] & dom_mask[src];
+    const unsigned long long act = loc ? loc : host[e];
+    int* qrow = p.q + (size_t)pair * R;
+    for (int dst = 0; dst < R; ++dst) qrow[dst] = ((act >> dst) & 1ull) ? even_share(need, act, dst, u_min) : 0;
+  }
+  for (int cell = gtid; cell < E * R; cell += gthreads) {
+    const int e = cell / R, dst = cell - e * R;
+    int acc = 0;
+    if ((host[e] >> dst) & 1ull) {
+      for (int src = 0; src < R; ++src) {
+        const unsigned long long loc = host[e] & dom_mask[src];
+        const unsigned long long act = loc ? loc : host[e];
+        if ((act >> dst) & 1ull) acc += even_share(p.omega[(size_t)src * E + e], act, dst, u_min);
+      }
+    }
+    p.erl[cell] = acc;
+  }
+}
+
 __device__ void phase1_routing(const SolverParams& p) {
   const int R = p.R, E = p.E, u_min = p.u_min;
   const int lane = threadIdx.x & 31;
@@ -244,7 +318,7 @@ struct ProbeState {
   int patience;
 };
 
-__device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, ProbeState probe) {
+__device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, ProbeState probe, bool fresh) {
   __shared__ int busy_idx, busy_rank, busy_load, finished, sel_idx, apply_move;
   __shared__ int best_theta, stagnant;
   __shared__ Cand best_sh;
@@ -253,11 +327,46 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
   const int R = p.R, E = p.E, u_min = p.u_min;
   const int n = collect_domain(p, s, d);
   if (n == 0) return;
-  for (int i = tid; i < n; i += nt) {
-    int r = s.dom_ranks[i];
-    s.load[i] = p.rank_load[r];
-    s.slot[i] = p.slot_used[r];
-    s.stuck[i] = probe.on ? p.stuck[r] : 0;
+  if (fresh) {
+    // first repair pass after routing: this domain's rank loads are column sums of erl
+    const int lane_ = tid & 31, warp_ = tid >> 5, nwarps_ = nt >> 5;
+    for (int i = warp_; i < n; i += nwarps_) {
+      const int r = s.dom_ranks[i];
+      int acc = 0;
+      for (int e = lane_; e < E; e += kWarp) acc += p.erl[(size_t)e * R + r];
+      for (int off = kWarp / 2; off > 0; off >>= 1) acc += __shfl_down_sync(kFull, acc, off);
+      if (lane_ == 0) {
+        s.load[i] = acc;
+        s.slot[i] = p.slot_used[r];
+        s.stuck[i] = 0;
+      }
+    }
+  } else {
+    for (int i = tid; i < n; i += nt) {
+      int r = s.dom_ranks[i];
+      s.load[i] = p.rank_load[r];
+      s.slot[i] = p.slot_used[r];
+      s.stuck[i] = probe.on ? p.stuck[r] : 0;
+    }
+  }
+  // The repair loop re-reads erl[e, r] and x[e, r] of this domain's ranks on every iteration;
+  // keep them in shared memory (when they fit) so an iteration costs no global round trips
+  // beyond the quota move itself.  Global copies are kept up to date for the later phases.
+  const bool cached = p.cache_stage2 != 0;
+  const bool qcached = p.cache_q != 0 && u_min == 1;  // the quota columns of this domain's ranks too
+  if (qcached) {
+    for (int idx = tid; idx < R * E * n; idx += nt) {
+      const int se = idx / n, i = idx - se * n;
+      s.q_c[idx] = p.q[(size_t)se * R + s.dom_ranks[i]];
+    }
+  }
+  if (cached) {
+    for (int idx = tid; idx < E * n; idx += nt) {
+      const int e = idx / n, i = idx - e * n;
+      const int r = s.dom_ranks[i];
+      s.erl_c[idx] = p.erl[(size_t)e * R + r];
+      s.x_c[idx] = p.x[(size_t)e * R + r];
+    }
   }
   __syncthreads();
 
@@ -294,12 +403,13 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
 
     Cand mine = no_cand();
     for (int e = tid; e < E; e += nt) {
-      const int avail = p.erl[(size_t)e * R + src];
+      const int avail = cached ? s.erl_c[e * n + busy_idx] : p.erl[(size_t)e * R + src];
       if (avail <= 0) continue;
       for (int ti = 0; ti < n; ++ti) {
         const int t = s.dom_ranks[ti], tl = s.load[ti];
         if (t == src || tl >= top) continue;
-        if (p.x[(size_t)e * R + t] == 0 && s.slot[ti] >= p.n_slot) continue;
+        const bool host = cached ? s.x_c[e * n + ti] != 0 : p.x[(size_t)e * R + t] != 0;
+        if (!host && s.slot[ti] >= p.n_slot) continue;
         const int delta = min(avail, (top - tl) / 2);
         if (delta < u_min) continue;
         Cand c{delta, tl, p.cost[(size_t)src * R + t], e, t};
@@ -325,8 +435,10 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
           s.stuck[busy_idx] = 1;
         } else {
           signed char* cell = p.x + (size_t)best.expert * R + best.target;
-          if (*cell == 0) {
+          const bool hosted = cached ? s.x_c[best.expert * n + sel_idx] != 0 : *cell != 0;
+          if (!hosted) {
             *cell = 1;
+            if (cached) s.x_c[best.expert * n + sel_idx] = 1;
             s.slot[sel_idx] += 1;
           }
         }
@@ -340,7 +452,9 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
             const int sr = base + lane;
             int* from = p.q + ((size_t)sr * E + best.expert) * R + src;
             int* to = p.q + ((size_t)sr * E + best.expert) * R + best.target;
-            const int have = sr < R ? *from : 0;
+            int* cfrom = qcached && sr < R ? s.q_c + ((size_t)sr * E + best.expert) * n + busy_idx : nullptr;
+            int* cto = qcached && sr < R ? s.q_c + ((size_t)sr * E + best.expert) * n + sel_idx : nullptr;
+            const int have = sr < R ? (cfrom ? *cfrom : *from) : 0;
             int incl = have;
             for (int off = 1; off < kWarp; off <<= 1) {
               int o = __shfl_up_sync(kFull, incl, off);
@@ -350,14 +464,26 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
             const int mv = min(have, max(best.delta - before, 0));
             if (sr < R && mv > 0) {
               *from = have - mv;
-              *to += mv;
+              if (cfrom) {
+                *cfrom = have - mv;
+                *to = (*cto += mv);
+              } else {
+                *to += mv;
+              }
             }
             carry += __shfl_sync(kFull, incl, kWarp - 1);
           }
         }
         if (tid == 0) {
-          p.erl[(size_t)best.expert * R + src] -= best.delta;
-          p.erl[(size_t)best.expert * R + best.target] += best.delta;
+          if (cached) {
+            const int a = (s.erl_c[best.expert * n + busy_idx] -= best.delta);
+            const int b = (s.erl_c[best.expert * n + sel_idx] += best.delta);
+            p.erl[(size_t)best.expert * R + src] = a;
+            p.erl[(size_t)best.expert * R + best.target] = b;
+          } else {
+            p.erl[(size_t)best.expert * R + src] -= best.delta;
+            p.erl[(size_t)best.expert * R + best.target] += best.delta;
+          }
           s.load[busy_idx] -= best.delta;
           s.load[sel_idx] += best.delta;
           for (int i = 0; i < n; ++i) s.stuck[i] = 0;
@@ -390,6 +516,7 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
           signed char* cell = p.x + (size_t)best.expert * R + best.target;
           if (*cell == 0) {
             *cell = 1;
+            if (cached) s.x_c[best.expert * n + ti] = 1;
             s.slot[ti] += 1;
           }
           int left = limit;
@@ -402,6 +529,10 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
           }
           p.erl[(size_t)best.expert * R + src] -= actual;
           p.erl[(size_t)best.expert * R + best.target] += actual;
+          if (cached) {
+            s.erl_c[best.expert * n + busy_idx] -= actual;
+            s.erl_c[best.expert * n + ti] += actual;
+          }
           s.load[busy_idx] -= actual;
           s.load[ti] += actual;
           for (int i = 0; i < n; ++i) s.stuck[i] = 0;
@@ -418,22 +549,6 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
     p.stuck[r] = (unsigned char)s.stuck[i];
   }
   __syncthreads();
-}
-
-__device__ void rank_loads_from_erl(const SolverParams& p) {
-  // rank_load[r] = sum_e erl[e, r]; ranks are spread over all warps of the grid
-  const int lane = threadIdx.x & 31;
-  const int wpb = blockDim.x >> 5;
-  const int gwarp = blockIdx.x * wpb + (threadIdx.x >> 5);
-  for (int r = gwarp; r < p.R; r += gridDim.x * wpb) {
-    int acc = 0;
-    for (int e = lane; e < p.E; e += kWarp) acc += p.erl[(size_t)e * p.R + r];
-    for (int off = kWarp / 2; off > 0; off >>= 1) acc += __shfl_down_sync(kFull, acc, off);
-    if (lane == 0) {
-      p.rank_load[r] = acc;
-      p.stuck[r] = 0;
-    }
-  }
 }
 
 __device__ int global_theta(const SolverParams& p) {
@@ -522,26 +637,27 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
   bool ok = true;
   for (int d = blockIdx.x; d < p.D; d += gridDim.x) phase0_domain(p, s, d);
   ok = ok && grid_barrier(p, 11);
-  if (ok) phase1_routing(p);
+  if (ok) {
+    if (p.R <= 64) phase1_routing_masks(p, s);
+    else phase1_routing(p);
+  }
   ok = ok && grid_barrier(p, 12);
-  if (ok) rank_loads_from_erl(p);
-  ok = ok && grid_barrier(p, 13);
 
   if (ok) {
     if (!p.probe) {
-      for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, p.iters, ProbeState{false, 0});
+      for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, p.iters, ProbeState{false, 0}, true);
     } else {
       // Stagnation probe: 1 repair round, then `patience` rounds, then the remainder unless the
       // global max load stopped improving.  Every CTA evaluates the same control values.
       ProbeState pr{true, p.patience};
-      for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, 1, pr);
+      for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, 1, pr, true);
       ok = ok && grid_barrier(p, 14);
       long long best = global_theta(p);
       long long stagnant = 0, stop = 0;
       int left = p.iters - 1;
       const int probe_iters = min(p.patience, left);
       if (ok && probe_iters > 0)
-        for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, probe_iters, pr);
+        for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, probe_iters, pr, false);
       left -= probe_iters;
       ok = ok && grid_barrier(p, 15);
       if (ok && left > 0) {
@@ -554,7 +670,7 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
           if (stagnant >= p.patience) stop = 1;
         }
         if (!stop)
-          for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, left, pr);
+          for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, left, pr, false);
       }
       if (blockIdx.x == 0 && threadIdx.x == 0 && p.control) {
         p.control[0] = best;
@@ -586,13 +702,16 @@ __global__ void __launch_bounds__(1024) tables_kernel(SolverParams p, RankTables
   build_tables(p, tables, tables.me);
 }
 
-size_t solver_smem_bytes(int R, int E) {
+size_t solver_base_smem(int R, int E) {
   return sizeof(long long) * E + sizeof(int) * E + sizeof(int) * 5 * R + sizeof(Cand) * 32 + 64;
 }
+size_t solver_cache_smem(int R, int E) { return (((size_t)E * R * 5 + 15) / 16) * 16; }  // erl (int) + x (byte) per (e, rank)
+size_t solver_qcache_smem(int R, int E) { return (size_t)R * E * R * 4; }
+constexpr size_t kCacheBudget = 200 * 1024;
 
 int pow2_threads(int R, int E) {
   int want = E > R ? E : R;
-  int t = 128;
+  int t = 256;
   while (t < want && t < 1024) t <<= 1;
   return t;
 }
@@ -605,15 +724,20 @@ cudaError_t launch_solver(const SolverParams& p, const RankTables& tables, cudaS
   if (err != cudaSuccess) return err;
   err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (err != cudaSuccess) return err;
-  const size_t smem = solver_smem_bytes(p.R, p.E);
-  if (smem > 48 * 1024) {
+  SolverParams pc = p;
+  const size_t base = solver_base_smem(p.R, p.E);
+  pc.cache_stage2 = base + solver_cache_smem(p.R, p.E) <= kCacheBudget ? 1 : 0;
+  pc.cache_q = pc.cache_stage2 && base + solver_cache_smem(p.R, p.E) + solver_qcache_smem(p.R, p.E) <= kCacheBudget ? 1 : 0;
+  const size_t smem = base + (pc.cache_stage2 ? solver_cache_smem(p.R, p.E) : 0) + (pc.cache_q ? solver_qcache_smem(p.R, p.E) : 0);
+  static size_t configured_smem = 48 * 1024;  // raise the kernel's dynamic shared memory limit only when needed
+  if (smem > configured_smem) {
     err = cudaFuncSetAttribute(solver_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
+    configured_smem = smem;
   }
   int grid = p.D < sms ? p.D : sms;
   if (grid < 1) grid = 1;
   const int threads = pow2_threads(p.R, p.E);
-  SolverParams pc = p;
   RankTables tc = tables;
   void* args[] = {&pc, &tc};
   if (grid > 1) return cudaLaunchCooperativeKernel((void*)solver_kernel, dim3(grid), dim3(threads), args, smem, stream);

@@ -15,6 +15,8 @@ struct SolverParams {
   const int64_t* weight_bytes;  // [E]
   int64_t s_tok;
   int R, E, D, n_slot, u_min, iters, patience, allow_cross, probe;
+  int cache_q;                  // set by launch_solver: ... and the quota columns it moves
+  int cache_stage2;             // set by launch_solver: repair loop keeps erl/x of its domain in shared memory
   // outputs
   int8_t* x;              // [E, R]
   int32_t* q;             // [R, E, R]; every element is written, no pre-zeroing needed
