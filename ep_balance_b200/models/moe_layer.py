@@ -55,6 +55,11 @@ class MoEConfig:
     router_dtype: torch.dtype = torch.float32
     normalize_topk: bool = True
     gemm_ctas: int = 2  # 2: CTA-pair grouped GEMM (256-row tiles); 1: single-CTA kernel (128-row tiles)
+    # None: every backward overwrites ``param.grad``.  torch.bfloat16 / torch.float32: every backward ADDS the
+    # expert weight gradients into an accumulation buffer of that dtype (``param.grad`` for bf16,
+    # ``param.main_grad`` for fp32), for steps made of several micro-batches; clear it with
+    # ``FusedMoE.zero_grad_accum()`` (or ``optimizer.zero_grad(set_to_none=False)`` in the bf16 case).
+    grad_accum_dtype: Optional[torch.dtype] = None
 
 
 def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
@@ -177,6 +182,13 @@ class FusedMoE(nn.Module):
             "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
         }
         ptrs = {k: v.data_ptr() for k, v in self.loc.items()}
+        self._acc_gw1 = self._acc_gw2 = None
+        if cfg.grad_accum_dtype is not None:
+            if cfg.grad_accum_dtype not in (torch.bfloat16, torch.float32):
+                raise ValueError("grad_accum_dtype must be None, torch.bfloat16 or torch.float32")
+            self._acc_gw1 = torch.zeros((self.home_cap, 2 * F, H), dtype=cfg.grad_accum_dtype, device=dev)
+            self._acc_gw2 = torch.zeros((self.home_cap, H, F), dtype=cfg.grad_accum_dtype, device=dev)
+            ptrs["acc_gw1"], ptrs["acc_gw2"] = self._acc_gw1.data_ptr(), self._acc_gw2.data_ptr()
         for name in ("omega", "signals", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"):
             ptrs[name] = heap.address(name, rank)
         self._tables: List[torch.Tensor] = []
@@ -196,17 +208,33 @@ class FusedMoE(nn.Module):
                       allow_cross=int(sc.allow_cross_domain),
                       probe=int(sc.stage2_patience_all_scales and iters > sc.stage2_stagnation_patience + 1),
                       s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync),
-                      gemm_ctas=cfg.gemm_ctas)
+                      gemm_ctas=cfg.gemm_ctas, accum_fp32=int(cfg.grad_accum_dtype == torch.float32))
         self.rt = load().MoeRuntime(rt_cfg, ptrs)
         self.bind_grads()
 
     # ---- gradients ---------------------------------------------------------
     def bind_grads(self) -> None:
-        """Point ``.grad`` of the expert parameters at the symmetric gradient slots."""
+        """Point ``.grad`` of the expert parameters at the symmetric gradient slots, or at the
+        accumulation buffers when ``grad_accum_dtype`` is set (fp32: ``.main_grad``, ``.grad`` stays None)."""
+        if self._acc_gw1 is not None:
+            if self._acc_gw1.dtype == torch.float32:
+                self.w1.main_grad, self.w2.main_grad = self._acc_gw1, self._acc_gw2
+                return
+            if self.w1.grad is None or self.w1.grad.data_ptr() != self._acc_gw1.data_ptr():
+                self.w1.grad = self._acc_gw1
+            if self.w2.grad is None or self.w2.grad.data_ptr() != self._acc_gw2.data_ptr():
+                self.w2.grad = self._acc_gw2
+            return
         if self.w1.grad is None or self.w1.grad.data_ptr() != self._gw1.data_ptr():
             self.w1.grad = self._gw1
         if self.w2.grad is None or self.w2.grad.data_ptr() != self._gw2.data_ptr():
             self.w2.grad = self._gw2
+
+    def zero_grad_accum(self) -> None:
+        """Clear the gradient accumulation buffers (start of a step made of several micro-batches)."""
+        if self._acc_gw1 is not None:
+            self._acc_gw1.zero_()
+            self._acc_gw2.zero_()
 
     # ---- routing -----------------------------------------------------------
     def route_tokens(self, tokens: torch.Tensor):

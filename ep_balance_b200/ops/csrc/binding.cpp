@@ -9,6 +9,7 @@
 #include <string>
 
 #include "grouped_gemm.h"
+#include "onesided.h"
 #include "optim.h"
 #include "route.h"
 #include "runtime.h"
@@ -57,6 +58,7 @@ LayerConfig config_from_dict(const py::dict& d) {
   c.patience = get_int(d, "patience", 8);
   c.allow_cross = get_int(d, "allow_cross", 1);
   c.probe = get_int(d, "probe", 0);
+  c.accum_fp32 = get_int(d, "accum_fp32", 0);
   c.s_tok = d.contains("s_tok") ? d["s_tok"].cast<int64_t>() : 0;
   c.num_sms = get_int(d, "num_sms", 148);
   c.multi_rank_sync = get_int(d, "multi_rank_sync", 1);
@@ -174,9 +176,10 @@ void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, 
   const c10::cuda::CUDAGuard guard(param.device());
   TORCH_CHECK(param.is_contiguous() && grad.is_contiguous() && exp_avg.is_contiguous() && exp_avg_sq.is_contiguous(),
               "adamw_step needs contiguous tensors");
-  TORCH_CHECK(param.scalar_type() == grad.scalar_type() && param.scalar_type() == exp_avg.scalar_type() &&
+  const bool grad_f32 = param.scalar_type() == torch::kBFloat16 && grad.scalar_type() == torch::kFloat32;
+  TORCH_CHECK((param.scalar_type() == grad.scalar_type() || grad_f32) && param.scalar_type() == exp_avg.scalar_type() &&
                   param.scalar_type() == exp_avg_sq.scalar_type(),
-              "adamw_step needs one dtype");
+              "adamw_step: moments share the parameter dtype; the gradient does too, or is fp32 for a bf16 parameter");
   TORCH_CHECK(param.scalar_type() == torch::kBFloat16 || param.scalar_type() == torch::kFloat32, "bf16 or fp32 only");
   TORCH_CHECK(grad.numel() == param.numel() && exp_avg.numel() == param.numel() && exp_avg_sq.numel() == param.numel(),
               "adamw_step size mismatch");
@@ -194,6 +197,7 @@ void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, 
   a.bias_correction1 = (float)(1.0 - std::pow(beta1, (double)step));
   a.bias_correction2_sqrt = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
   a.is_bf16 = param.scalar_type() == torch::kBFloat16 ? 1 : 0;
+  a.grad_f32 = grad_f32 ? 1 : 0;
   cuda_check(epb::launch_adamw(a, current_stream()), "launch_adamw");
 }
 
@@ -203,6 +207,53 @@ void wait_probe(torch::Tensor flag, int64_t target, int64_t budget_ns, torch::Te
                                     (unsigned)target, (unsigned long long)budget_ns,
                                     dptr<int>(status, "status", torch::kInt32), current_stream()),
              "launch_wait_probe");
+}
+
+// ---- one-sided transfers over peer-mapped windows (descriptors: int64 [K, 4] on the device)
+void copy_batched(bool is_put, torch::Tensor desc, torch::Tensor window_ptrs, uint64_t local_base, bool use_bulk,
+                  int64_t blocks_per_desc, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(desc.device());
+  TORCH_CHECK(desc.dim() == 2 && desc.size(1) == 4, "descriptors must be int64 [K, 4]");
+  epb::BatchedCopyArgs a{};
+  a.desc = reinterpret_cast<const epb::CopyDesc*>(dptr<int64_t>(desc, "desc", torch::kInt64));
+  a.K = (int)desc.size(0);
+  a.window_ptrs = reinterpret_cast<uint8_t* const*>(dptr<int64_t>(window_ptrs, "window_ptrs", torch::kInt64));
+  a.R = (int)window_ptrs.numel();
+  a.local_base = reinterpret_cast<uint8_t*>(static_cast<uintptr_t>(local_base));
+  a.use_bulk = use_bulk ? 1 : 0;
+  a.status = dptr<int>(status, "status", torch::kInt32);
+  cuda_check(is_put ? epb::launch_put_batched(a, (int)blocks_per_desc, current_stream())
+                    : epb::launch_get_batched(a, (int)blocks_per_desc, current_stream()),
+             is_put ? "launch_put_batched" : "launch_get_batched");
+}
+void get_batched(torch::Tensor desc, torch::Tensor window_ptrs, uint64_t local_base, bool use_bulk,
+                 int64_t blocks_per_desc, torch::Tensor status) {
+  copy_batched(false, desc, window_ptrs, local_base, use_bulk, blocks_per_desc, status);
+}
+void put_batched(torch::Tensor desc, torch::Tensor window_ptrs, uint64_t local_base, bool use_bulk,
+                 int64_t blocks_per_desc, torch::Tensor status) {
+  copy_batched(true, desc, window_ptrs, local_base, use_bulk, blocks_per_desc, status);
+}
+void signal_peers(torch::Tensor signal_ptrs, int64_t peer, int64_t idx, int64_t value) {
+  const c10::cuda::CUDAGuard guard(signal_ptrs.device());
+  cuda_check(epb::launch_signal(reinterpret_cast<unsigned* const*>(dptr<int64_t>(signal_ptrs, "signal_ptrs", torch::kInt64)),
+                                (int)signal_ptrs.numel(), (int)peer, (int)idx, (unsigned)value, current_stream()),
+             "launch_signal");
+}
+void wait_signal(uint64_t word, int64_t expected, int64_t idx, int64_t budget_ns, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(status.device());
+  cuda_check(epb::launch_wait_signal(reinterpret_cast<const unsigned*>(static_cast<uintptr_t>(word)), (unsigned)expected,
+                                     (int)idx, (unsigned long long)budget_ns, dptr<int>(status, "status", torch::kInt32),
+                                     current_stream()),
+             "launch_wait_signal");
+}
+void symm_barrier(torch::Tensor signal_ptrs, int64_t slot, int64_t me, torch::Tensor epoch_word, torch::Tensor status) {
+  const c10::cuda::CUDAGuard guard(signal_ptrs.device());
+  cuda_check(epb::launch_symm_barrier(reinterpret_cast<unsigned* const*>(dptr<int64_t>(signal_ptrs, "signal_ptrs", torch::kInt64)),
+                                      (int)slot, (int)signal_ptrs.numel(), (int)me,
+                                      reinterpret_cast<unsigned*>(dptr<int32_t>(epoch_word, "epoch_word", torch::kInt32)),
+                                      dptr<int>(status, "status", torch::kInt32), current_stream()),
+             "launch_symm_barrier");
 }
 
 // ---- symmetric heap over CUDA IPC: one cudaMalloc per rank, mapped into every peer process
@@ -241,6 +292,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("grouped_gemm", &grouped_gemm);
   m.def("wait_probe", &wait_probe);
   m.def("adamw_step", &adamw_step);
+  m.def("get_batched", &get_batched);
+  m.def("put_batched", &put_batched);
+  m.def("signal_peers", &signal_peers);
+  m.def("wait_signal", &wait_signal);
+  m.def("symm_barrier", &symm_barrier);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);

@@ -24,17 +24,32 @@ __global__ void __launch_bounds__(256) adamw_bf16_kernel(AdamArgs a) {
   uint4* v4 = reinterpret_cast<uint4*>(a.exp_avg_sq);
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    uint4 pv = p4[i], gv = g4[i], mv = m4[i], vv = v4[i];
+    uint4 pv = p4[i], mv = m4[i], vv = v4[i];
+    float gf[8];
+    if (a.grad_f32) {
+      const float4* gq = reinterpret_cast<const float4*>(a.grad) + i * 2;
+      const float4 lo = gq[0], hi = gq[1];
+      gf[0] = lo.x; gf[1] = lo.y; gf[2] = lo.z; gf[3] = lo.w;
+      gf[4] = hi.x; gf[5] = hi.y; gf[6] = hi.z; gf[7] = hi.w;
+    } else {
+      const uint4 gv = g4[i];
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(gp[k]);
+        gf[2 * k] = g.x;
+        gf[2 * k + 1] = g.y;
+      }
+    }
     __nv_bfloat162* pp = reinterpret_cast<__nv_bfloat162*>(&pv);
-    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&gv);
     __nv_bfloat162* mp = reinterpret_cast<__nv_bfloat162*>(&mv);
     __nv_bfloat162* vp = reinterpret_cast<__nv_bfloat162*>(&vv);
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      float2 p = __bfloat1622float2(pp[k]), g = __bfloat1622float2(gp[k]);
+      float2 p = __bfloat1622float2(pp[k]);
       float2 m = __bfloat1622float2(mp[k]), v = __bfloat1622float2(vp[k]);
-      adam_one(p.x, g.x, m.x, v.x, a);
-      adam_one(p.y, g.y, m.y, v.y, a);
+      adam_one(p.x, gf[2 * k], m.x, v.x, a);
+      adam_one(p.y, gf[2 * k + 1], m.y, v.y, a);
       pp[k] = __floats2bfloat162_rn(p.x, p.y);
       mp[k] = __floats2bfloat162_rn(m.x, m.y);
       vp[k] = __floats2bfloat162_rn(v.x, v.y);
@@ -50,7 +65,8 @@ __global__ void __launch_bounds__(256) adamw_bf16_kernel(AdamArgs a) {
   __nv_bfloat16* m1 = reinterpret_cast<__nv_bfloat16*>(a.exp_avg);
   __nv_bfloat16* v1 = reinterpret_cast<__nv_bfloat16*>(a.exp_avg_sq);
   for (size_t i = done + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < a.numel; i += stride) {
-    float p = __bfloat162float(p1[i]), g = __bfloat162float(g1[i]), m = __bfloat162float(m1[i]), v = __bfloat162float(v1[i]);
+    float p = __bfloat162float(p1[i]), m = __bfloat162float(m1[i]), v = __bfloat162float(v1[i]);
+    const float g = a.grad_f32 ? reinterpret_cast<const float*>(a.grad)[i] : __bfloat162float(g1[i]);
     adam_one(p, g, m, v, a);
     p1[i] = __float2bfloat16_rn(p);
     m1[i] = __float2bfloat16_rn(m);

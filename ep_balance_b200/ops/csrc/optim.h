@@ -8,13 +8,14 @@ namespace epb {
 
 struct AdamArgs {
   void* param;       // bf16 or fp32
-  const void* grad;  // same dtype as param
+  const void* grad;  // same dtype as param, or fp32 for a bf16 param when grad_f32 is set
   void* exp_avg;     // same dtype as param
   void* exp_avg_sq;  // same dtype as param
   size_t numel;
   float lr, beta1, beta2, eps, weight_decay;
   float bias_correction1, bias_correction2_sqrt;  // 1 - beta1^t, sqrt(1 - beta2^t)
   int is_bf16;
+  int grad_f32;      // bf16 parameters with an fp32 (accumulated) gradient
 };
 
 cudaError_t launch_adamw(const AdamArgs& a, cudaStream_t stream);

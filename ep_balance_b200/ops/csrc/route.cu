@@ -283,7 +283,8 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   }
   __syncthreads();
   const int n = n_hosts;
-  if (n == 0) return;  // no replicas: the owner's own slot gradient is already final
+  const bool accumulate = a.accum != nullptr;
+  if (n == 0 && !accumulate) return;  // no replicas: the owner's own slot gradient is already final
   const size_t n_vec = a.elems_per_slot / 8;
   uint4* mine = reinterpret_cast<uint4*>(a.g_ptrs[a.me]) + (size_t)home * n_vec;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -294,11 +295,22 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
       const uint4* peer = reinterpret_cast<const uint4*>(a.g_ptrs[host_rank[k]]) + (size_t)host_slot[k] * n_vec;
       add8(acc, peer[i]);
     }
+    if (accumulate && a.accum_fp32) {
+      float4* dst = reinterpret_cast<float4*>(a.accum) + ((size_t)home * n_vec + i) * 2;
+      float4 lo = dst[0], hi = dst[1];
+      lo.x += acc[0]; lo.y += acc[1]; lo.z += acc[2]; lo.w += acc[3];
+      hi.x += acc[4]; hi.y += acc[5]; hi.z += acc[6]; hi.w += acc[7];
+      dst[0] = lo;
+      dst[1] = hi;
+      continue;
+    }
+    uint4* out = accumulate ? reinterpret_cast<uint4*>(a.accum) + (size_t)home * n_vec + i : mine + i;
+    if (accumulate) add8(acc, *out);
     uint4 o;
     __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
     for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    mine[i] = o;
+    *out = o;
   }
 }
 

@@ -68,8 +68,13 @@ cudaError_t launch_weight_pull(const WeightPullArgs& a, cudaStream_t stream);
 
 // Owner-side gradient return: for every expert owned by `me` with replicas, add the replicas'
 // slot gradients (peer loads) into the owner's home slot gradient, accumulating in fp32.
+// With `accum != nullptr` the sum (own slot + replicas) of EVERY home slot is added to
+// accum[home] (fp32 or bf16, [home_cap, elems_per_slot]) instead of being written back to the slot:
+// gradient accumulation over micro-batches, the slots being overwritten by each backward.
 struct GradReduceArgs {
   void* const* g_ptrs;          // R peers: [n_slot, elems_per_slot] bf16
+  void* accum;                  // optional accumulation buffer (local memory)
+  int accum_fp32;               // dtype of accum: 1 fp32, 0 bf16
   size_t elems_per_slot;
   const int32_t* slot_of;       // [E, R]
   const int32_t* main_rank;     // [E]

@@ -239,8 +239,11 @@ void MoeRuntime::reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stre
   check(launch_unit_reduce(ptr<void>("dxbuf"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H, stream), "unit_reduce(bwd)");
 }
 void MoeRuntime::reduce_weight_grads(cudaStream_t stream) {
-  if (cfg_.R <= 1) return;
+  void* acc1 = ptr<void>("acc_gw1", false);
+  void* acc2 = ptr<void>("acc_gw2", false);
+  if (cfg_.R <= 1 && acc1 == nullptr) return;
   GradReduceArgs a{};
+  a.accum_fp32 = cfg_.accum_fp32;
   a.slot_of = tables_.slot_of;
   a.main_rank = sp_.main_rank;
   a.home_index = tables_.home_index;
@@ -249,9 +252,11 @@ void MoeRuntime::reduce_weight_grads(cudaStream_t stream) {
   a.me = cfg_.me;
   a.home_cap = cfg_.home_cap;
   a.g_ptrs = ptr<void* const>("gw1_ptrs");
+  a.accum = acc1;
   a.elems_per_slot = (size_t)2 * cfg_.F * cfg_.H;
   check(launch_grad_reduce(a, stream), "grad_reduce(w1)");
   a.g_ptrs = ptr<void* const>("gw2_ptrs");
+  a.accum = acc2;
   a.elems_per_slot = (size_t)cfg_.F * cfg_.H;
   check(launch_grad_reduce(a, stream), "grad_reduce(w2)");
 }

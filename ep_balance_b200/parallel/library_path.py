@@ -31,6 +31,7 @@ from ..utils import profiling
 from .comm import a2a_raw, all_to_all_single, broadcast_from_main, global_rank
 from .grouped_mlp import grouped_expert_mlp
 from .physical import assign_physical
+from .symm_weights import SymmReplicaTransport, replicator_for, symm_weights_enabled
 
 
 def _env_truthy(name: str, default: str = "0") -> bool:
@@ -299,9 +300,15 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     if cap is None and not ragged:
         cap = max(int(group_sizes.max()), 1)  # padded path only: one host read
 
-    transport = BroadcastReplicaTransport(plan=plan, spec=spec, weights_local=weights_local,
-                                          weight_shapes=weight_shapes, my_rank=my_rank, n_slot=n_slot, dtype=dtype,
-                                          device=device, group=group) if distributed or weights_local else None
+    if distributed and device.type == "cuda" and symm_weights_enabled():
+        # device-initiated weight channel: one-sided gets/puts over the symmetric heap
+        rep = replicator_for(group, spec.main_rank, weight_shapes, dtype, device)
+        transport = SymmReplicaTransport(rep, plan.x, n_slot, weights_local)
+    else:
+        transport = BroadcastReplicaTransport(plan=plan, spec=spec, weights_local=weights_local,
+                                              weight_shapes=weight_shapes, my_rank=my_rank, n_slot=n_slot,
+                                              dtype=dtype, device=device, group=group) \
+            if distributed or weights_local else None
 
     with profiling.record("apply/route", time_it=True, device=device):
         phys_id, dst_rank = assign_physical(unit_expert, plan, spec, my_rank)

@@ -27,7 +27,11 @@ class FusedAdamW(torch.optim.Optimizer):
         for group in self.param_groups:
             b1, b2 = group["betas"]
             for p in group["params"]:
-                if p.grad is None:
+                # Megatron convention: an fp32 ``main_grad`` accumulated over micro-batches wins over ``.grad``
+                grad = getattr(p, "main_grad", None)
+                if grad is None:
+                    grad = p.grad
+                if grad is None:
                     continue
                 st = self.state[p]
                 if not st:
@@ -35,6 +39,6 @@ class FusedAdamW(torch.optim.Optimizer):
                     st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
                     st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
                 st["step"] += 1
-                self._ext.adamw_step(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
+                self._ext.adamw_step(p.data, grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
                                      group["eps"], group["weight_decay"], st["step"])
         return loss

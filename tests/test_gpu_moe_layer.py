@@ -116,3 +116,49 @@ def test_bounded_wait_reports_status_and_context_survives():
     torch.cuda.synchronize()
     assert status.tolist()[0] == 2
     assert float(torch.ones(4, device="cuda").sum()) == 4.0  # the context is still usable
+
+
+@pytest.mark.parametrize("acc_dtype", [torch.bfloat16, torch.float32])
+def test_weight_gradients_accumulate_over_micro_batches(acc_dtype):
+    """Two micro-batches through one layer: the accumulation buffer holds the sum of both weight
+    gradients (fp32 oracle), for a single rank and for four emulated ranks with replicas."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+
+    torch.manual_seed(3)
+    for world in (1, 4):
+        E, N, H, Fd = 8, 256, 256, 256
+        cfg = MoEConfig(hidden=H, ffn=Fd, num_experts=E, top_k=2, max_tokens=N, extra_slots=2,
+                        capacity_factor=float(world), grad_accum_dtype=acc_dtype)
+        cl = EmulatedCluster(cfg, world=world)
+        bias = torch.zeros(E, device="cuda")
+        bias[:2] = 3.0
+        for l in cl.layers:
+            l.router_bias = bias
+            l.zero_grad_accum()
+        w1, w2 = cl.full_weights()
+        want1 = torch.zeros_like(w1, dtype=torch.float32)
+        want2 = torch.zeros_like(w2, dtype=torch.float32)
+        for mb in range(2):
+            tokens = [torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)]
+            douts = [torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)]
+            res = cl.step(tokens, douts)
+            for r in range(world):
+                _, _, _, idx, prob = res[r]
+                _, _, _, dw1, dw2 = _oracle(tokens[r], idx, prob, w1, w2, douts[r])
+                want1 += dw1
+                want2 += dw2
+        torch.cuda.synchronize()
+        for l in cl.layers:
+            l.check_status()
+        if acc_dtype == torch.float32:
+            got1 = torch.cat([l.w1.main_grad for l in cl.layers])
+            got2 = torch.cat([l.w2.main_grad for l in cl.layers])
+        else:
+            got1, got2 = cl.full_grads()
+        assert got1.dtype == acc_dtype
+        assert _rel(got1, want1) < 3e-2, world
+        assert _rel(got2, want2) < 3e-2, world
+        for l in cl.layers:
+            l.zero_grad_accum()
+        assert float(torch.cat([l._acc_gw1.flatten() for l in cl.layers]).abs().sum()) == 0.0
