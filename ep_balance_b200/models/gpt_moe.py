@@ -37,6 +37,7 @@ class GPTMoEConfig:
     capacity_factor: float = 2.0
     num_domains: int = 1
     rope_base: float = 10000.0
+    grad_accum_dtype: Optional[torch.dtype] = None  # set for steps made of several micro-batches
 
     @property
     def tokens_per_rank(self) -> int:
@@ -99,7 +100,8 @@ class GPTMoE(nn.Module):
         self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         mcfg = MoEConfig(hidden=cfg.hidden, ffn=cfg.ffn, num_experts=cfg.experts, top_k=cfg.top_k,
                          max_tokens=cfg.tokens_per_rank, extra_slots=cfg.extra_slots,
-                         capacity_factor=cfg.capacity_factor, num_domains=cfg.num_domains)
+                         capacity_factor=cfg.capacity_factor, num_domains=cfg.num_domains,
+                         grad_accum_dtype=cfg.grad_accum_dtype)
         self.heaps: List[SymmetricHeap] = []
         blocks = []
         for layer in range(cfg.layers):
@@ -170,3 +172,24 @@ class GPTMoE(nn.Module):
     def check_status(self) -> None:
         for b in self.blocks:
             b.moe.check_status()
+
+    def zero_expert_grad_accum(self) -> None:
+        for b in self.blocks:
+            b.moe.zero_grad_accum()
+
+    # ---- checkpoint state ------------------------------------------------------
+    def replicated_state(self) -> dict:
+        """Parameters that are identical on every rank (everything but the experts), by name."""
+        skip = {id(p) for p in self.expert_parameters()}
+        return {n: p.detach().cpu() for n, p in self.named_parameters() if id(p) not in skip}
+
+    def expert_state(self) -> dict:
+        """This rank's own experts (the owners' copies; replica slots are transient and not saved)."""
+        return {f"blocks.{i}.moe.{n}": getattr(b.moe, n).detach().cpu() for i, b in enumerate(self.blocks)
+                for n in ("w1", "w2")}
+
+    @torch.no_grad()
+    def load_states(self, replicated: dict, experts: dict) -> None:
+        named = dict(self.named_parameters())
+        for n, t in {**replicated, **experts}.items():
+            named[n].copy_(t.to(named[n].device, named[n].dtype))

@@ -179,7 +179,7 @@ class SymmReplicaTransport:
         out = []
         for j, shp in enumerate(rep.weight_shapes):
             box = rep.inbox[j][: rep.home_cap * w.world].view((rep.home_cap, w.world) + shp)
-            out.append(box.to(torch.float32).sum(1).to(rep.dtype))
+            out.append(box.sum(1, dtype=torch.float32).to(rep.dtype))
         return out
 
     def reduce_grads(self, grad_stacks: Sequence[Optional[torch.Tensor]]) -> List[torch.Tensor]:

@@ -51,3 +51,52 @@ def test_group_limited_routing_and_dsv3_block():
     with torch.no_grad():
         y2 = model(x[:64].detach().contiguous())  # inference-only forward at a smaller batch
     assert y2.shape == (64, 256) and torch.isfinite(y2.float()).all()
+
+
+def _run_train(capsys, argv, env=None):
+    import os
+
+    from ep_balance_b200.launch import train_gpt_moe
+
+    old = {k: os.environ.get(k) for k in (env or {})}
+    os.environ.update(env or {})
+    try:
+        assert train_gpt_moe.main(argv) == 0
+    finally:
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    out = capsys.readouterr().out
+    from ep_balance_b200.eval.extract_train_metrics import ITER_RE
+
+    return {int(m.group("iter")): float(m.group("loss")) for m in ITER_RE.finditer(out)}, out
+
+
+TINY = ["--layers", "2", "--hidden", "256", "--heads", "4", "--ffn", "256", "--experts", "8", "--top-k", "2",
+        "--vocab", "512", "--seq-len", "128", "--micro-batch", "2", "--lr", "1e-3"]
+
+
+def test_training_resumes_from_a_checkpoint_with_the_same_losses(tmp_path, capsys):
+    ck = str(tmp_path / "ck")
+    full, _ = _run_train(capsys, TINY + ["--steps", "6", "--num-micro-batches", "2"])
+    first, _ = _run_train(capsys, TINY + ["--steps", "3", "--num-micro-batches", "2", "--save", ck])
+    second, out = _run_train(capsys, TINY + ["--steps", "6", "--num-micro-batches", "2", "--load", ck])
+    assert "resume_step=3" in out
+    assert sorted(second) == [4, 5, 6] and sorted(first) == [1, 2, 3]
+    for it in (1, 2, 3):
+        assert abs(first[it] - full[it]) < 1e-6
+    for it in (4, 5, 6):
+        assert abs(second[it] - full[it]) < 2e-3 * abs(full[it]), (it, second[it], full[it])
+
+
+def test_observe_mode_logs_plans_and_writes_a_trace(tmp_path, capsys):
+    from ep_balance_b200.core.trace import load_routing_trace
+
+    trace = str(tmp_path / "trace.pt")
+    _, out = _run_train(capsys, TINY + ["--steps", "2"], env={"EPLB_MODE": "observe", "EPLB_TRACE_OUT": trace,
+                                                             "EPLB_TRACE_EVERY": "1"})
+    assert out.count("[EPLB] layer=") == 4      # 2 layers x 2 steps
+    t = load_routing_trace(trace)
+    assert len(t["samples"]) == 4 and t["meta"]["num_experts"] == 8
