@@ -8,7 +8,8 @@ Every rank owns ``--home`` experts (default weights 3 x 7168 x 2048 bf16 = 88 MB
 (rank r hosts one expert of each of ranks r+1 .. r+slots).  Timed with CUDA events, max over ranks:
 
 * ``pull``      device-initiated get of the replica weights (this package's batched-get kernel)
-* ``return``    put of every slot gradient into the owner's inbox + the owner's sum
+* ``return``    gradient return: hosts stage their slot gradients, owners sum their replicas' rows with
+                peer loads (``return_inbox_protocol`` = the reference's put-into-inbox + sum protocol)
 * ``nccl``      what the reference's default transport does: one ``dist.broadcast`` per replicated
                 expert and tensor, and one ``dist.reduce`` per expert and tensor for the gradients
                 (eplb/integration/overlap.py:113-148, 203-232)
@@ -74,7 +75,8 @@ def main(argv=None) -> int:
     dtype = torch.bfloat16
     main_rank = torch.arange(E) // home
     per_expert = sum(torch.Size(s).numel() for s in shapes) * 2
-    sw = SymmetricWorld(SymmWeightReplicator.arena_bytes(E, world, shapes, dtype, home_cap=home), dev)
+    sw = SymmetricWorld(SymmWeightReplicator.arena_bytes(E, world, shapes, dtype, home_cap=home,
+                                                            n_slot=sum(home + s for s in a.slots)), dev)
     rep = SymmWeightReplicator(sw, main_rank, shapes, dtype)
     weights_local = {rank * home + i: tuple(torch.randn(s, device=dev).to(dtype) for s in shapes) for i in range(home)}
     rows = []
@@ -93,17 +95,21 @@ def main(argv=None) -> int:
         remote_bytes = slots * per_expert
         grads = [torch.randn((n_slot,) + s, device=dev).to(dtype) for s in shapes]
 
-        def grad_return():
+        def grad_return_inbox():
             tr.clear_inbox()
             sw.world_fence(2)
             tr.push(grads)
             sw.world_fence(3)
             tr.collect()
 
+        def grad_return():
+            tr.reduce_grads(grads)
+
         row = {"ranks": world, "slots": slots, "expert_mb": per_expert / 2 ** 20,
                "pull_ms": _time(lambda: tr.pull(), a.iters, a.warmup, dev),
                "pull_with_publish_and_fences_ms": _time(lambda: tr.materialize_replicas(), a.iters, a.warmup, dev),
-               "return_ms": _time(grad_return, a.iters, a.warmup, dev)}
+               "return_ms": _time(grad_return, a.iters, a.warmup, dev),
+               "return_inbox_protocol_ms": _time(grad_return_inbox, a.iters, a.warmup, dev)}
         row["pull_gbs"] = remote_bytes / row["pull_ms"] / 1e6
         row["return_gbs"] = remote_bytes / row["return_ms"] / 1e6
         sw.check_status()

@@ -256,6 +256,30 @@ void symm_barrier(torch::Tensor signal_ptrs, int64_t slot, int64_t me, torch::Te
              "launch_symm_barrier");
 }
 
+// Owner-side gradient return over explicit tables (the library path's symmetric weight channel).
+void grad_reduce(torch::Tensor g_ptrs, int64_t elems_per_slot, torch::Tensor slot_of, torch::Tensor main_rank,
+                 torch::Tensor home_index, int64_t me, int64_t home_cap, torch::Tensor accum, bool include_self) {
+  const c10::cuda::CUDAGuard guard(g_ptrs.device());
+  epb::GradReduceArgs a{};
+  a.g_ptrs = reinterpret_cast<void* const*>(dptr<int64_t>(g_ptrs, "g_ptrs", torch::kInt64));
+  a.elems_per_slot = (size_t)elems_per_slot;
+  a.slot_of = dptr<int32_t>(slot_of, "slot_of", torch::kInt32);
+  a.main_rank = dptr<int32_t>(main_rank, "main_rank", torch::kInt32);
+  a.home_index = dptr<int32_t>(home_index, "home_index", torch::kInt32);
+  a.E = (int)main_rank.numel();
+  a.R = (int)g_ptrs.numel();
+  TORCH_CHECK(slot_of.numel() == (int64_t)a.E * a.R, "slot_of must be [E, R]");
+  a.me = (int)me;
+  a.home_cap = (int)home_cap;
+  TORCH_CHECK(accum.is_cuda() && accum.is_contiguous(), "accum must be a contiguous CUDA tensor");
+  TORCH_CHECK(accum.scalar_type() == torch::kFloat32 || accum.scalar_type() == torch::kBFloat16, "accum: fp32 or bf16");
+  TORCH_CHECK(accum.numel() == home_cap * elems_per_slot, "accum must be [home_cap, elems_per_slot]");
+  a.accum = accum.data_ptr();
+  a.accum_fp32 = accum.scalar_type() == torch::kFloat32 ? 1 : 0;
+  a.include_self = include_self ? 1 : 0;
+  cuda_check(epb::launch_grad_reduce(a, current_stream()), "launch_grad_reduce");
+}
+
 // ---- symmetric heap over CUDA IPC: one cudaMalloc per rank, mapped into every peer process
 py::tuple ipc_alloc(int64_t nbytes) {
   void* p = nullptr;
@@ -297,6 +321,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("signal_peers", &signal_peers);
   m.def("wait_signal", &wait_signal);
   m.def("symm_barrier", &symm_barrier);
+  m.def("grad_reduce", &grad_reduce);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);

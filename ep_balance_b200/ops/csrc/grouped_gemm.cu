@@ -39,7 +39,10 @@ struct Geometry {
 };
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
-constexpr int MAX_GROUPS = 320;  // barriers + flags + (MAX_GROUPS + 1) ints must fit in 2 KB
+constexpr int MAX_GROUPS = 320;  // barriers + flags + (MAX_GROUPS + 1) ints must fit in kCtrlBytes
+constexpr int kCtrlBytes = 1536;
+static_assert((6 * 2 + 4) * 8 + 8 + (MAX_GROUPS + 1) * 4 <= kCtrlBytes, "control block does not fit");
+constexpr int kStageWarpBytes = 4096;  // staging tile of one epilogue warp
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -318,6 +321,26 @@ __device__ __forceinline__ void stage_flush(const uint4* tile, int lane, char* r
     if (base != 0ull) *reinterpret_cast<uint4*>(base + byte_off + p * 16) = tile[stage_index(r, p)];
   }
 }
+// Wide variant for rows that may live on another GPU: the tile holds 32 rows x 128 B (8 pieces per
+// row, piece p of row r at r*8 + (p ^ (r & 7))), filled 64 B at a time and flushed with four rows x
+// 128 contiguous bytes per instruction, so peer stores leave the SM as full 128-byte segments.
+__device__ __forceinline__ int wide_index(int r, int p) { return r * 8 + (p ^ (r & 7)); }
+__device__ __forceinline__ void wide_store_half(uint4* tile, int lane, const uint4 (&p)[4], int half) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) tile[wide_index(lane, half * 4 + i)] = p[i];
+  __syncwarp();
+}
+// `pieces` = 8 (both halves valid) or 4 (only the first 64 B of each row).
+__device__ __forceinline__ void wide_flush(const uint4* tile, int lane, char* rowptr, int byte_off, int pieces) {
+  const unsigned long long mine = reinterpret_cast<unsigned long long>(rowptr);
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3), p = lane & 7;
+    const unsigned long long base = __shfl_sync(0xffffffffu, mine, r);
+    if (base != 0ull && p < pieces) *reinterpret_cast<uint4*>(base + byte_off + p * 16) = tile[wide_index(r, p)];
+  }
+}
 // ---------------------------------------------------------------- kernel
 template <int kMode, int kCtas>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -337,7 +360,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
   int* tile_prefix = abort_flag + 1;  // [MAX_GROUPS + 1]
-  uint4* stage_tiles = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 2048);  // 8 warps x 2 KB
+  uint4* stage_tiles = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + kCtrlBytes);  // 8 warps x 4 KB
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const Shape shape = make_shape<kMode, kCtas>(args);
@@ -505,7 +528,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // tile and written out with row-contiguous 16-byte stores (8 rows x 64 B per instruction).
     const int quarter = warp & 3;      // TMEM lanes [32*quarter, 32*quarter + 32)
     const int half = (warp - 2) >> 2;  // which half of the tile's column chunks this warp handles
-    uint4* stg = stage_tiles + (warp - 2) * 128;
+    uint4* stg = stage_tiles + (warp - 2) * (kStageWarpBytes / 16);
     uint32_t acc_phase[2] = {0, 0};
     int local = 0;
     Tile t;
@@ -645,8 +668,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
               for (int i = 0; i < 4; ++i) pk[i] = make_uint4(0, 0, 0, 0);
             }
-            stage_store(stg, lane, pk);
-            stage_flush(stg, lane, orow, (col0 + c * 32) * 2);
+            wide_store_half(stg, lane, pk, k & 1);
+            if ((k & 1) || c + 1 >= nchunks) wide_flush(stg, lane, orow, (col0 + (c - (k & 1)) * 32) * 2, (k & 1) ? 8 : 4);
           }
         }
       }
@@ -677,8 +700,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
 template <int kCtas>
 constexpr size_t smem_bytes() {
-  return Geometry<kCtas>::STAGES * Geometry<kCtas>::STAGE_BYTES + 1024 /*align*/ + 2048 /*barriers, flags, tile prefix*/ +
-         8 * 2048 /*staging*/;
+  return Geometry<kCtas>::STAGES * Geometry<kCtas>::STAGE_BYTES + 1024 /*align*/ + kCtrlBytes /*barriers, flags, tile prefix*/ +
+         8 * kStageWarpBytes /*staging*/;
 }
 
 // ---------------------------------------------------------------- tensor maps

@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
     int n = 0;
     for (int h = 0; h < a.R && n < 64; ++h) {
       int s = a.slot_of[(size_t)e * a.R + h];
-      if (h != a.me && s >= 0) {
+      if ((h != a.me || a.include_self) && s >= 0) {
         host_rank[n] = h;
         host_slot[n] = s;
         ++n;
@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    add8(acc, mine[i]);
+    if (!a.include_self) add8(acc, mine[i]);
     for (int k = 0; k < n; ++k) {
       const uint4* peer = reinterpret_cast<const uint4*>(a.g_ptrs[host_rank[k]]) + (size_t)host_slot[k] * n_vec;
       add8(acc, peer[i]);

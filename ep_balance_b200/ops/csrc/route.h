@@ -75,6 +75,8 @@ struct GradReduceArgs {
   void* const* g_ptrs;          // R peers: [n_slot, elems_per_slot] bf16
   void* accum;                  // optional accumulation buffer (local memory)
   int accum_fp32;               // dtype of accum: 1 fp32, 0 bf16
+  int include_self;             // 1: the owner's own contribution sits in slot_of[e, me] like any host's
+                                //    (slot order = hosted experts by id); 0: it sits in the home slot
   size_t elems_per_slot;
   const int32_t* slot_of;       // [E, R]
   const int32_t* main_rank;     // [E]

@@ -75,7 +75,11 @@ class SymmetricWorld:
         self._fence_epochs = torch.zeros(NUM_FENCES, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self.use_bulk = True
-        self.blocks_per_desc = 8    # reference default EPLB_GIN_GRID=8 (eplb/integration/gin_weights.py:106)
+        # CTAs per descriptor.  None: spread about two waves of CTAs over the descriptors of a call, so a
+        # short schedule (one or two replica slots) still keeps enough bytes in flight to fill NVLink.
+        # The reference uses a fixed EPLB_GIN_GRID=8 (eplb/integration/gin_weights.py:106).
+        self.blocks_per_desc: Optional[int] = None
+        self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -127,7 +131,7 @@ class SymmetricWorld:
         without a host read (reference: nccl_gin.get_batched, nccl_gin/csrc/nccl_gin.cu:1143-1193)."""
         self._check_local(local)
         self.ext.get_batched(desc.contiguous(), self.window_ptrs, local.data_ptr(), bool(self.use_bulk),
-                             int(blocks or self.blocks_per_desc), self.status)
+                             self._blocks(blocks, desc), self.status)
 
     def put_batched(self, local: torch.Tensor, desc: torch.Tensor, *, blocks: Optional[int] = None) -> None:
         """Mirror of :meth:`get_batched`: ``local[local_off:+nbytes]`` is stored into ``peer``'s arena at
@@ -135,7 +139,14 @@ class SymmetricWorld:
         orders after the data (reference: nccl_gin.put_batched, nccl_gin/csrc/nccl_gin.cu:1195-1230)."""
         self._check_local(local)
         self.ext.put_batched(desc.contiguous(), self.window_ptrs, local.data_ptr(), bool(self.use_bulk),
-                             int(blocks or self.blocks_per_desc), self.status)
+                             self._blocks(blocks, desc), self.status)
+
+    def _blocks(self, blocks: Optional[int], desc: torch.Tensor) -> int:
+        if blocks:
+            return int(blocks)
+        if self.blocks_per_desc:
+            return int(self.blocks_per_desc)
+        return max(8, min(128, 2 * self._sm_count // max(int(desc.shape[0]), 1)))
 
     def get(self, dst: torch.Tensor, src: torch.Tensor, peer: int, *, blocks: Optional[int] = None) -> None:
         """``dst[...] = src`` as it exists on ``peer``; ``src`` is a (view of a) symmetric tensor."""

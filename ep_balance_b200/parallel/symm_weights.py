@@ -94,15 +94,27 @@ class SymmWeightReplicator:
         self.inbox = [world.create_tensor((self.home_cap * world.world + 1,) + s, dtype) for s in self.weight_shapes]
         self.home_off = [world.offset_of(t) for t in self.home]
         self.inbox_off = [world.offset_of(t) for t in self.inbox]
+        self._gslot: Dict[int, List[torch.Tensor]] = {}      # n_slot -> per-tensor symmetric gradient staging
+
+    def gslot(self, n_slot: int) -> List[torch.Tensor]:
+        """Symmetric ``[n_slot, ...]`` windows where every host stages its slot gradients for the owners
+        to read (collective on first use per ``n_slot``)."""
+        g = self._gslot.get(int(n_slot))
+        if g is None:
+            g = [self.world.create_tensor((int(n_slot),) + s, self.dtype) for s in self.weight_shapes]
+            self._gslot[int(n_slot)] = g
+        return g
 
     @staticmethod
-    def arena_bytes(num_experts: int, world_size: int, weight_shapes, dtype, home_cap: Optional[int] = None) -> int:
+    def arena_bytes(num_experts: int, world_size: int, weight_shapes, dtype, home_cap: Optional[int] = None,
+                    n_slot: int = 0) -> int:
+        """Arena size for the home and inbox windows plus one gradient staging window of ``n_slot`` rows."""
         es = torch.empty((), dtype=dtype).element_size()
         cap = home_cap if home_cap is not None else -(-num_experts // world_size)
         total = 0
         for s in weight_shapes:
             wb = int(torch.Size(tuple(s)).numel()) * es
-            total += (cap + cap * world_size + 1) * wb + 1024
+            total += (cap + cap * world_size + 1 + int(n_slot)) * wb + 2048
         return total
 
 
@@ -115,6 +127,8 @@ class SymmReplicaTransport:
         self.n_slot = int(n_slot)
         self.weights_local = weights_local
         w = rep.world
+        self._x = x.to(w.device)
+        self._rt = None
         self.sched = replica_schedule(x.to(w.device), rep.main_rank, rep.local_slot_of_e, w.rank, self.n_slot, w.world)
         s = self.sched
         slots = torch.arange(self.n_slot, dtype=torch.int64, device=w.device)
@@ -182,10 +196,59 @@ class SymmReplicaTransport:
             out.append(box.sum(1, dtype=torch.float32).to(rep.dtype))
         return out
 
+    # ---- owner-side reduce (bf16): hosts stage, owners read their replicas' rows and sum in registers
+    def owner_reduce_available(self) -> bool:
+        rep = self.rep
+        return rep.dtype == torch.bfloat16 and rep.world.world <= 64 and all(b % 16 == 0 for b in rep.wb)
+
+    def _reduce_tables(self):
+        if getattr(self, "_rt", None) is None:
+            rep, w = self.rep, self.rep.world
+            x = self._x.to(torch.int64)
+            slot_of = torch.where(x > 0, torch.cumsum(x, 0) - 1, torch.full_like(x, -1))
+            slot_of = torch.where(slot_of < self.n_slot, slot_of, torch.full_like(slot_of, -1)).to(torch.int32).contiguous()
+            gs = rep.gslot(self.n_slot)
+            ptrs = [torch.tensor([w.heap.address("arena", r) + w.offset_of(t) for r in range(w.world)],
+                                 dtype=torch.int64, device=w.device) for t in gs]
+            self._rt = (slot_of, rep.main_rank.to(torch.int32).contiguous(),
+                        rep.local_slot_of_e.to(torch.int32).contiguous(), gs, ptrs)
+        return self._rt
+
+    def stage(self, grad_stacks: Sequence[Optional[torch.Tensor]]) -> None:
+        _, _, _, gs, _ = self._reduce_tables()
+        for j, g in enumerate(grad_stacks):
+            if g is None:
+                gs[j].zero_()
+            else:
+                gs[j].copy_(g)
+
+    def owner_sum(self) -> List[torch.Tensor]:
+        """``[home_cap, ...]`` per weight tensor: sum over every host's staged row (peer loads, fp32 accumulate)."""
+        rep, w = self.rep, self.rep.world
+        slot_of, main32, home32, _, ptrs = self._reduce_tables()
+        out = []
+        for j, shp in enumerate(rep.weight_shapes):
+            acc = torch.zeros((rep.home_cap,) + shp, dtype=torch.float32, device=w.device)
+            w.ext.grad_reduce(ptrs[j], rep.wb[j] // 2, slot_of, main32, home32, w.rank, rep.home_cap, acc, True)
+            out.append(acc.to(rep.dtype))
+        return out
+
     def reduce_grads(self, grad_stacks: Sequence[Optional[torch.Tensor]]) -> List[torch.Tensor]:
-        """clear -> fence -> push -> fence -> sum (reference: gin_weights.py:343-377).  Returns one
-        gradient per owned expert and weight tensor, in ``sorted(weights_local)`` order."""
+        """Returns one gradient per owned expert and weight tensor, in ``sorted(weights_local)`` order.
+
+        bf16 weights: stage -> fence -> owners sum their replicas' rows with peer loads -> fence (the
+        gradient crosses NVLink once and nothing is zeroed or re-read).  Other dtypes take the
+        reference's inbox protocol: clear -> fence -> push -> fence -> sum (gin_weights.py:343-377)."""
         w = self.rep.world
+        n_w = len(self.rep.weight_shapes)
+        if self.owner_reduce_available():
+            with profiling.record("apply/grad_move", time_it=True, device=w.device):
+                self.stage(grad_stacks)
+                w.world_fence(2)
+                rows = self.owner_sum()
+                w.world_fence(3)
+            mine = [rows[j].index_select(0, self._owned_rows) for j in range(n_w)]
+            return [mine[j][i] for i in range(len(self.owned)) for j in range(n_w)]
         with profiling.record("apply/grad_move", time_it=True, device=w.device):
             self.clear_inbox()
             w.world_fence(2)
@@ -241,7 +304,8 @@ def replicator_for(group, main_rank: torch.Tensor, weight_shapes, dtype, device)
     if rep is None:
         world_size = dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
         _, cap = local_slot_table(main_rank, world_size)
-        arena = SymmWeightReplicator.arena_bytes(int(main_rank.numel()), world_size, shapes, dtype, home_cap=cap)
+        arena = SymmWeightReplicator.arena_bytes(int(main_rank.numel()), world_size, shapes, dtype, home_cap=cap,
+                                                 n_slot=2 * cap + 8)
         world = SymmetricWorld(arena, device, group=group)
         rep = SymmWeightReplicator(world, main_rank, shapes, dtype)
         _REPLICATORS[key] = rep

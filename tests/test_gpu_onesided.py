@@ -116,7 +116,7 @@ def test_replica_weight_channel_matches_indexing():
     x[0, 2] = 1
     x[0, 3] = 1
     x[5, 0] = 1
-    arena = SymmWeightReplicator.arena_bytes(E, R, shapes, dtype)
+    arena = SymmWeightReplicator.arena_bytes(E, R, shapes, dtype, n_slot=n_slot)
     worlds = _worlds(R, arena=arena)
     try:
         g = torch.Generator(device="cuda").manual_seed(0)
@@ -152,6 +152,15 @@ def test_replica_weight_channel_matches_indexing():
                         hosted = [ee for ee in range(E) if x[ee, r]]
                         want += grads[r][j][hosted.index(e)].float()
                 torch.testing.assert_close(rows[owner][j][ls].float(), want, atol=2e-2, rtol=2e-2)
+        # the owner-side reduce (hosts stage, owners read with peer loads) gives the same sums
+        assert trs[0].owner_reduce_available()
+        for r, t in enumerate(trs):
+            t.stage(grads[r])
+        rows2 = [t.owner_sum() for t in trs]
+        torch.cuda.synchronize()
+        for r in range(R):
+            for j in range(2):
+                torch.testing.assert_close(rows2[r][j].float(), rows[r][j].float(), atol=2e-2, rtol=2e-2)
         worlds[0].check_status()
     finally:
         worlds[0].destroy()
