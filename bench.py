@@ -126,8 +126,10 @@ def host_batches(tokens: int, hidden: int, rank: int, count: int = 4):
     return [torch.randn(tokens, hidden, generator=g).to(torch.bfloat16).pin_memory() for _ in range(count)]
 
 
-def timed_loop(step_fn, steps: int, world: int):
-    """Barrier + sync, K steps between CUDA events on the current stream, sync + barrier."""
+def timed_loop(step_fn, steps: int, world: int, finish=None):
+    """Barrier + sync, K steps between CUDA events on the current stream, sync + barrier.
+    ``finish`` (optional) runs after the last step and before the closing event (drains reads that
+    the loop defers by one step, so that every step's result is read inside the timed region)."""
     import torch
     import torch.distributed as dist
 
@@ -138,6 +140,8 @@ def timed_loop(step_fn, steps: int, world: int):
     t0.record()
     for i in range(steps):
         step_fn(i)
+    if finish is not None:
+        finish()
     t1.record()
     torch.cuda.synchronize()
     if world > 1:
@@ -196,7 +200,9 @@ def run_ours(args):
     opt = FusedAdamW(layer.parameters(), lr=1e-5)
     batches = host_batches(args.tokens, CFG["hidden"], rank)
     dev_batches = [b.to(dev) for b in batches]
-    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+    loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+    loss_ready = [torch.cuda.Event() for _ in range(2)]
+    losses_read = []
 
     def train_step(x):
         out = layer(x)
@@ -211,7 +217,10 @@ def run_ours(args):
         train_step(x)
 
     # End-to-end loop: the input of step i+1 is copied host->device on a side stream while step i
-    # computes (two device staging buffers); the loss of every step is read back to the host.
+    # computes (two device staging buffers).  The loss of every step is copied device->host into
+    # pinned memory asynchronously and read by the host one step later, after step i+1 has been
+    # enqueued, so the GPU never idles while the host launches; the last loss is read before the
+    # closing event of the timed loop.
     copy_stream = torch.cuda.Stream(device=dev)
     staging = [torch.empty_like(dev_batches[0]) for _ in range(2)]
     ready = [torch.cuda.Event() for _ in range(2)]
@@ -233,7 +242,22 @@ def run_ours(args):
         x = staging[slot].detach().requires_grad_(True)
         loss = train_step(x)
         consumed[slot].record()
-        loss_host.copy_(loss.detach().reshape(1), non_blocking=False)  # device->host read of the step's loss
+        loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)  # device->host, 4 bytes
+        loss_ready[slot].record()
+        if pending["step"] is not None:
+            read_loss(pending["step"])
+        pending["step"] = i
+
+    pending = {"step": None}
+
+    def read_loss(i):
+        loss_ready[i % 2].synchronize()
+        losses_read.append(float(loss_host[i % 2]))
+
+    def finish_e2e():
+        if pending["step"] is not None:
+            read_loss(pending["step"])
+            pending["step"] = None
 
     for ev in consumed:
         ev.record()
@@ -249,7 +273,11 @@ def run_ours(args):
     launches = layer.rt.launches()
     for i in range(min(3, args.warmup)):
         step_e2e(i)
-    ms_e2e = timed_loop(step_e2e, args.steps, world)
+    finish_e2e()
+    losses_read.clear()
+    ms_e2e = timed_loop(step_e2e, args.steps, world, finish=finish_e2e)
+    if len(losses_read) != args.steps or not all(v == v and v > 0 for v in losses_read):
+        raise RuntimeError(f"end-to-end loop read {len(losses_read)} losses for {args.steps} steps: {losses_read[:4]}")
     clocks = sampler.stop() if rank == 0 else {}
     layer.check_status()
 
@@ -276,6 +304,8 @@ def run_ours(args):
     loads = layer.rank_loads().float()
     extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],
              "gemm_ctas": args.gemm_ctas,
+             "e2e_loop": "input H2D prefetched on a side stream (double-buffered); loss D2H copied asynchronously and "
+                         "read by the host one step later, the last one before the closing event",
              "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return, fused AdamW"}
     if rank == 0:
         emit(args, world, "ours", ms_dev, ms_e2e, launches, clocks, batches[0].numel() * 2, 4, extra)

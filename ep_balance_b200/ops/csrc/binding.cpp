@@ -258,7 +258,8 @@ void symm_barrier(torch::Tensor signal_ptrs, int64_t slot, int64_t me, torch::Te
 
 // Owner-side gradient return over explicit tables (the library path's symmetric weight channel).
 void grad_reduce(torch::Tensor g_ptrs, int64_t elems_per_slot, torch::Tensor slot_of, torch::Tensor main_rank,
-                 torch::Tensor home_index, int64_t me, int64_t home_cap, torch::Tensor accum, bool include_self) {
+                 torch::Tensor home_index, int64_t me, int64_t home_cap, torch::Tensor accum, bool include_self,
+                 bool overwrite) {
   const c10::cuda::CUDAGuard guard(g_ptrs.device());
   epb::GradReduceArgs a{};
   a.g_ptrs = reinterpret_cast<void* const*>(dptr<int64_t>(g_ptrs, "g_ptrs", torch::kInt64));
@@ -277,6 +278,7 @@ void grad_reduce(torch::Tensor g_ptrs, int64_t elems_per_slot, torch::Tensor slo
   a.accum = accum.data_ptr();
   a.accum_fp32 = accum.scalar_type() == torch::kFloat32 ? 1 : 0;
   a.include_self = include_self ? 1 : 0;
+  a.overwrite = overwrite ? 1 : 0;
   cuda_check(epb::launch_grad_reduce(a, current_stream()), "launch_grad_reduce");
 }
 

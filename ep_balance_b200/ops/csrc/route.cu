@@ -297,7 +297,11 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
     }
     if (accumulate && a.accum_fp32) {
       float4* dst = reinterpret_cast<float4*>(a.accum) + ((size_t)home * n_vec + i) * 2;
-      float4 lo = dst[0], hi = dst[1];
+      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+      if (!a.overwrite) {
+        lo = dst[0];
+        hi = dst[1];
+      }
       lo.x += acc[0]; lo.y += acc[1]; lo.z += acc[2]; lo.w += acc[3];
       hi.x += acc[4]; hi.y += acc[5]; hi.z += acc[6]; hi.w += acc[7];
       dst[0] = lo;
@@ -305,7 +309,7 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
       continue;
     }
     uint4* out = accumulate ? reinterpret_cast<uint4*>(a.accum) + (size_t)home * n_vec + i : mine + i;
-    if (accumulate) add8(acc, *out);
+    if (accumulate && !a.overwrite) add8(acc, *out);
     uint4 o;
     __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
@@ -372,7 +376,10 @@ cudaError_t launch_weight_pull(const WeightPullArgs& a, cudaStream_t stream) {
 cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream) {
   if (a.home_cap <= 0) return cudaSuccess;
   if (a.elems_per_slot % 8 != 0 || a.R > 64) return cudaErrorInvalidValue;
-  dim3 grid(64, a.home_cap);
+  int gx = (2 * 148 + a.home_cap - 1) / a.home_cap;  // about two waves of CTAs in total
+  if (gx < 64) gx = 64;
+  if (gx > 256) gx = 256;
+  dim3 grid(gx, a.home_cap);
   grad_reduce_kernel<<<grid, 512, 0, stream>>>(a);
   return cudaGetLastError();
 }

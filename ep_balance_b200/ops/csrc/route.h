@@ -75,6 +75,7 @@ struct GradReduceArgs {
   void* const* g_ptrs;          // R peers: [n_slot, elems_per_slot] bf16
   void* accum;                  // optional accumulation buffer (local memory)
   int accum_fp32;               // dtype of accum: 1 fp32, 0 bf16
+  int overwrite;                // 1: accum receives the sum (its previous content is not read)
   int include_self;             // 1: the owner's own contribution sits in slot_of[e, me] like any host's
                                 //    (slot order = hosted experts by id); 0: it sits in the home slot
   size_t elems_per_slot;

@@ -129,6 +129,7 @@ class SymmReplicaTransport:
         w = rep.world
         self._x = x.to(w.device)
         self._rt = None
+        self._home_has_holes = len(weights_local) < rep.home_cap
         self.sched = replica_schedule(x.to(w.device), rep.main_rank, rep.local_slot_of_e, w.rank, self.n_slot, w.world)
         s = self.sched
         slots = torch.arange(self.n_slot, dtype=torch.int64, device=w.device)
@@ -228,9 +229,11 @@ class SymmReplicaTransport:
         slot_of, main32, home32, _, ptrs = self._reduce_tables()
         out = []
         for j, shp in enumerate(rep.weight_shapes):
-            acc = torch.zeros((rep.home_cap,) + shp, dtype=torch.float32, device=w.device)
-            w.ext.grad_reduce(ptrs[j], rep.wb[j] // 2, slot_of, main32, home32, w.rank, rep.home_cap, acc, True)
-            out.append(acc.to(rep.dtype))
+            # rows of home slots that hold no expert are never written: start from zeros only then
+            acc = (torch.zeros if self._home_has_holes else torch.empty)((rep.home_cap,) + shp, dtype=rep.dtype,
+                                                                         device=w.device)
+            w.ext.grad_reduce(ptrs[j], rep.wb[j] // 2, slot_of, main32, home32, w.rank, rep.home_cap, acc, True, True)
+            out.append(acc)
         return out
 
     def reduce_grads(self, grad_stacks: Sequence[Optional[torch.Tensor]]) -> List[torch.Tensor]:
