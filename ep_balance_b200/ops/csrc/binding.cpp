@@ -9,6 +9,7 @@
 #include <string>
 
 #include "grouped_gemm.h"
+#include "grouped_gemm_fp8.h"
 #include "onesided.h"
 #include "optim.h"
 #include "route.h"
@@ -282,6 +283,58 @@ void grad_reduce(torch::Tensor g_ptrs, int64_t elems_per_slot, torch::Tensor slo
   cuda_check(epb::launch_grad_reduce(a, current_stream()), "launch_grad_reduce");
 }
 
+// ---- block-scaled fp8 grouped GEMM and its quantisers
+void quantize_rows(torch::Tensor x, torch::Tensor q, torch::Tensor sfa) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 2 && q.dim() == 2 && q.sizes() == x.sizes(), "x and q must be [rows, K]");
+  const int rows = (int)x.size(0), K = (int)x.size(1);
+  TORCH_CHECK(rows % 128 == 0 && K % 128 == 0, "rows and K must be multiples of 128");
+  TORCH_CHECK(sfa.numel() == (int64_t)(rows / 128) * ((K / 128 + 3) / 4) * 512, "sfa has the wrong size");
+  cuda_check(epb::launch_quantize_rows(dptr<void>(x, "x", torch::kBFloat16), dptr<uint8_t>(q, "q", torch::kUInt8),
+                                       dptr<uint8_t>(sfa, "sfa", torch::kUInt8), rows, K, current_stream()),
+             "launch_quantize_rows");
+}
+void quantize_weights(torch::Tensor w, torch::Tensor q, torch::Tensor sfb) {
+  const c10::cuda::CUDAGuard guard(w.device());
+  TORCH_CHECK(w.dim() == 3 && q.sizes() == w.sizes(), "w and q must be [slots, N, K]");
+  const int S = (int)w.size(0), N = (int)w.size(1), K = (int)w.size(2);
+  TORCH_CHECK(N % 128 == 0 && K % 128 == 0, "N and K must be multiples of 128");
+  TORCH_CHECK(sfb.numel() == (int64_t)S * (N / 128) * ((K / 128 + 3) / 4) * 512, "sfb has the wrong size");
+  cuda_check(epb::launch_quantize_weights(dptr<void>(w, "w", torch::kBFloat16), dptr<uint8_t>(q, "q", torch::kUInt8),
+                                          dptr<uint8_t>(sfb, "sfb", torch::kUInt8), S, N, K, current_stream()),
+             "launch_quantize_weights");
+}
+void grouped_gemm_fp8(torch::Tensor aq, torch::Tensor sfa, torch::Tensor bq, torch::Tensor sfb, torch::Tensor out,
+                      torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor group_wslot, torch::Tensor totals,
+                      torch::Tensor status, int64_t num_sms) {
+  const c10::cuda::CUDAGuard guard(aq.device());
+  TORCH_CHECK(aq.dim() == 2 && bq.dim() == 3 && out.dim() == 2, "aq [T, K], bq [slots, N, K], out [T, N]");
+  const int64_t T = aq.size(0), K = aq.size(1), N = bq.size(1);
+  TORCH_CHECK(bq.size(2) == K && out.size(0) == T && out.size(1) == N, "shape mismatch");
+  TORCH_CHECK(T % 128 == 0 && K % 128 == 0 && N % 128 == 0, "T, K and N must be multiples of 128");
+  const int64_t kgroups = (K / 128 + 3) / 4;
+  TORCH_CHECK(sfa.numel() == (T / 128) * kgroups * 512, "sfa has the wrong size");
+  TORCH_CHECK(sfb.numel() == bq.size(0) * (N / 128) * kgroups * 512, "sfb has the wrong size");
+  epb::Fp8GemmArgs g{};
+  g.group_off = dptr<int32_t>(group_off, "group_off", torch::kInt32);
+  g.group_rows = dptr<int32_t>(group_rows, "group_rows", torch::kInt32);
+  g.group_wslot = dptr<int32_t>(group_wslot, "group_wslot", torch::kInt32);
+  g.totals = dptr<int32_t>(totals, "totals", torch::kInt32);
+  g.n_groups_cap = (int)group_rows.numel();
+  g.row_capacity = (int)T;
+  g.N = (int)N;
+  g.K = (int)K;
+  g.sfa = dptr<uint8_t>(sfa, "sfa", torch::kUInt8);
+  g.sfb = dptr<uint8_t>(sfb, "sfb", torch::kUInt8);
+  g.out = dptr<void>(out, "out", torch::kBFloat16);
+  g.status = dptr<int>(status, "status", torch::kInt32);
+  CUtensorMap tmA, tmB;
+  TORCH_CHECK(epb::make_tmap_fp8_2d(&tmA, dptr<uint8_t>(aq, "aq", torch::kUInt8), T, K) &&
+                  epb::make_tmap_fp8_3d(&tmB, dptr<uint8_t>(bq, "bq", torch::kUInt8), bq.size(0), N, K),
+              "cuTensorMapEncodeTiled failed");
+  cuda_check(epb::launch_grouped_gemm_fp8(tmA, tmB, g, (int)num_sms, current_stream()), "launch_grouped_gemm_fp8");
+}
+
 // ---- symmetric heap over CUDA IPC: one cudaMalloc per rank, mapped into every peer process
 py::tuple ipc_alloc(int64_t nbytes) {
   void* p = nullptr;
@@ -324,6 +377,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_signal", &wait_signal);
   m.def("symm_barrier", &symm_barrier);
   m.def("grad_reduce", &grad_reduce);
+  m.def("quantize_rows", &quantize_rows);
+  m.def("quantize_weights", &quantize_weights);
+  m.def("grouped_gemm_fp8", &grouped_gemm_fp8);
   m.def("ipc_alloc", &ipc_alloc);
   m.def("ipc_open", &ipc_open);
   m.def("ipc_close", &ipc_close);

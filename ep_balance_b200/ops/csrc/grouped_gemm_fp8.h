@@ -1,0 +1,56 @@
+// Block-scaled fp8 (e4m3) ragged grouped GEMM on tcgen05 with the scale factors in tensor memory
+// (grouped_gemm_fp8.cu), plus the quantisers that produce its operands.
+//
+// The reference has no fp8 path (its expert GEMMs are torch._grouped_mm in bf16,
+// eplb/integration/grouped_mlp.py:88-114); this is the DeepSeek-V3 recipe: activations scaled per
+// 1 x 128 block, weights per 128 x 128 block.  Scales are powers of two stored as one biased
+// exponent byte (UE8M0, value 2^(b-127)), which is what `tcgen05.mma.kind::mxf8f6f4.block_scale`
+// consumes, so the products are rescaled inside the tensor core and the accumulator in TMEM is the
+// final fp32 result: no per-k-block promotion pass over the accumulator is needed.
+//
+// Scale-factor layout ("chunk"): 512 bytes hold the scales of 128 rows (or weight columns) for four
+// consecutive 128-wide k-blocks; byte (r % 32) * 16 + (r / 32) * 4 + kb % 4.  This is the order in
+// which `tcgen05.cp.32x128b.warpx4` spreads a chunk over the 128 TMEM lanes, so a chunk goes
+// global -> shared (bulk copy) -> tensor memory without being rearranged.
+//   activations: sfa[row_tile][kgroup][512],  row_tile = row / 128, kgroup = k / 512
+//   weights:     sfb[slot][n_tile][kgroup][512], n_tile = n / 128 (all 128 entries of a k-block equal)
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace epb {
+
+struct Fp8GemmArgs {
+  // group geometry (device), as in GemmArgs: groups start on multiples of 128 rows
+  const int32_t* group_off;
+  const int32_t* group_rows;
+  const int32_t* group_wslot;
+  const int32_t* totals;       // [2]: padded rows, number of groups
+  int n_groups_cap;
+  int row_capacity;
+  int N;                       // output columns, multiple of 128
+  int K;                       // reduction extent, multiple of 128
+  const uint8_t* sfa;          // [row_capacity / 128][kgroups][512]
+  const uint8_t* sfb;          // [slots][N / 128][kgroups][512]
+  void* out;                   // bf16 [row_capacity, N] (rows kept local), or
+  void* const* out_ptrs;       // R peer buffers [units, N]: row r goes to out_ptrs[meta[r].x] row meta[r].y
+  const int2* meta;
+  int* status;
+};
+
+// Tensor maps over the e4m3 bytes: A [rows, K], B [slots, N, K]; boxes of 128 x 128 bytes, 128-byte swizzle.
+bool make_tmap_fp8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols);
+bool make_tmap_fp8_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols);
+
+cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmArgs& args,
+                                    int num_sms, cudaStream_t stream);
+
+// bf16 [rows, K] -> e4m3 [rows, K] + 1 x 128 scales in chunk layout.  rows % 128 == 0, K % 128 == 0.
+cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, cudaStream_t stream);
+// bf16 [slots, N, K] -> e4m3 + 128 x 128 scales in chunk layout.  N % 128 == 0, K % 128 == 0.
+cudaError_t launch_quantize_weights(const void* w, uint8_t* q, uint8_t* sfb, int slots, int N, int K,
+                                    cudaStream_t stream);
+
+}  // namespace epb
