@@ -77,3 +77,31 @@ class EmulatedCluster:
         for l in L:
             l.rt.reduce_weight_grads()
         return [(outs[r], dtok[r], dprob[r], routing[r][0], routing[r][1]) for r in range(self.world)]
+
+    @torch.no_grad()
+    def forward_fp8(self, tokens: List[torch.Tensor], routing=None):
+        """Inference forward of every rank with block-scaled fp8 expert GEMMs (``MoEConfig.fp8_inference``;
+        call ``quantize_weights()`` on every layer first).  Returns (outputs, routing)."""
+        L, K = self.layers, self.cfg.top_k
+        if routing is None:
+            routing = [l.route_tokens(t) for l, t in zip(L, tokens)]
+        n = [t.shape[0] for t in tokens]
+        outs = [torch.empty_like(t) for t in tokens]
+        for l, (idx, _), m in zip(L, routing, n):
+            l.rt.publish(idx.data_ptr(), m * K)
+        for l in L:
+            l.rt.solve()
+        for l, (idx, _), m in zip(L, routing, n):
+            l.rt.route(idx.data_ptr(), m * K)
+        for l, t, m in zip(L, tokens, n):
+            l.rt.dispatch_tokens(t.data_ptr(), m * K)
+        for l in L:
+            l.rt.pull_weights_fp8()
+        for l in L:
+            l.rt.gemm1_fp8()
+            l.rt.act_fp8()
+        for l in L:
+            l.rt.gemm2_fp8()
+        for l, (_, p), o, m in zip(L, routing, outs, n):
+            l.rt.reduce_out(p.data_ptr(), o.data_ptr(), m)
+        return outs, routing

@@ -60,6 +60,10 @@ class MoEConfig:
     # ``param.main_grad`` for fp32), for steps made of several micro-batches; clear it with
     # ``FusedMoE.zero_grad_accum()`` (or ``optimizer.zero_grad(set_to_none=False)`` in the bf16 case).
     grad_accum_dtype: Optional[torch.dtype] = None
+    # True: forwards that run without autograd (inference) use block-scaled fp8 expert GEMMs (e4m3, 1 x 128
+    # activation scales, 128 x 128 weight scales, power-of-two scale factors).  Call
+    # ``FusedMoE.quantize_weights()`` after the weights change; replicas then pull the fp8 copies.
+    fp8_inference: bool = False
 
 
 def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
@@ -81,7 +85,17 @@ def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
     lay.add("w2", (w_slots, H, F), torch.bfloat16)
     lay.add("gw1", (w_slots, 2 * F, H), torch.bfloat16)
     lay.add("gw2", (w_slots, H, F), torch.bfloat16)
+    if cfg.fp8_inference:
+        lay.add("w1q", (w_slots, 2 * F, H), torch.uint8)
+        lay.add("w2q", (w_slots, H, F), torch.uint8)
+        lay.add("sfb1", (w_slots, _sf_bytes(2 * F, H)), torch.uint8)
+        lay.add("sfb2", (w_slots, _sf_bytes(H, F)), torch.uint8)
     return lay
+
+
+def _sf_bytes(n: int, k: int) -> int:
+    """Bytes of the scale-factor chunks of an ``[n, k]`` operand (512 per 128 rows and four 128-wide k-blocks)."""
+    return (n // 128) * ((k // 128 + 3) // 4) * 512
 
 
 def row_capacity(cfg: MoEConfig, world: int) -> int:
@@ -189,13 +203,26 @@ class FusedMoE(nn.Module):
             self._acc_gw1 = torch.zeros((self.home_cap, 2 * F, H), dtype=cfg.grad_accum_dtype, device=dev)
             self._acc_gw2 = torch.zeros((self.home_cap, H, F), dtype=cfg.grad_accum_dtype, device=dev)
             ptrs["acc_gw1"], ptrs["acc_gw2"] = self._acc_gw1.data_ptr(), self._acc_gw2.data_ptr()
-        for name in ("omega", "signals", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"):
+        symm_names = ["omega", "signals", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"]
+        table_names = [("omega", "omega_ptrs"), ("signals", "signal_ptrs"), ("xbuf", "xbuf_ptrs"),
+                       ("meta", "meta_ptrs"), ("ybuf", "ybuf_ptrs"), ("dybuf", "dybuf_ptrs"),
+                       ("dxbuf", "dxbuf_ptrs"), ("w1", "w1_ptrs"), ("w2", "w2_ptrs"), ("gw1", "gw1_ptrs"),
+                       ("gw2", "gw2_ptrs")]
+        self._fp8_ready = False
+        if cfg.fp8_inference:
+            if H % 128 or F % 128:
+                raise ValueError("fp8_inference needs hidden and ffn to be multiples of 128")
+            symm_names += ["w1q", "w2q", "sfb1", "sfb2"]
+            table_names += [(n, n + "_ptrs") for n in ("w1q", "w2q", "sfb1", "sfb2")]
+            cap = self.row_capacity
+            u8 = dict(dtype=torch.uint8, device=dev)
+            self._fp8_local = {"xq": torch.zeros((cap, H), **u8), "sfx": torch.zeros(cap // 128 * _sf_bytes(128, H), **u8),
+                               "actq": torch.zeros((cap, F), **u8), "sfact": torch.zeros(cap // 128 * _sf_bytes(128, F), **u8)}
+            ptrs.update({k: v.data_ptr() for k, v in self._fp8_local.items()})
+        for name in symm_names:
             ptrs[name] = heap.address(name, rank)
         self._tables: List[torch.Tensor] = []
-        for name, key in (("omega", "omega_ptrs"), ("signals", "signal_ptrs"), ("xbuf", "xbuf_ptrs"),
-                          ("meta", "meta_ptrs"), ("ybuf", "ybuf_ptrs"), ("dybuf", "dybuf_ptrs"),
-                          ("dxbuf", "dxbuf_ptrs"), ("w1", "w1_ptrs"), ("w2", "w2_ptrs"), ("gw1", "gw1_ptrs"),
-                          ("gw2", "gw2_ptrs")):
+        for name, key in table_names:
             t = heap.peer_ptrs(name)
             self._tables.append(t)
             ptrs[key] = t.data_ptr()
@@ -230,6 +257,15 @@ class FusedMoE(nn.Module):
         if self.w2.grad is None or self.w2.grad.data_ptr() != self._gw2.data_ptr():
             self.w2.grad = self._gw2
 
+    def quantize_weights(self) -> None:
+        """Refresh the fp8 copies (and scale factors) of this rank's own experts from the bf16 parameters.
+        In a multi-rank group, call it on every rank and synchronise (e.g. ``dist.barrier`` after a stream
+        sync) before the next fp8 forward: replicas read the owners' fp8 slots."""
+        if not self.cfg.fp8_inference:
+            raise RuntimeError("MoEConfig.fp8_inference is off")
+        self.rt.quantize_own_weights()
+        self._fp8_ready = True
+
     def zero_grad_accum(self) -> None:
         """Clear the gradient accumulation buffers (start of a step made of several micro-batches)."""
         if self._acc_gw1 is not None:
@@ -257,6 +293,11 @@ class FusedMoE(nn.Module):
             raise ValueError("more tokens than MoEConfig.max_tokens")
         tokens = tokens.contiguous()
         top_idx, prob = self.route_tokens(tokens)
+        if self.cfg.fp8_inference and self._fp8_ready and not torch.is_grad_enabled():
+            out = torch.empty_like(tokens)
+            self.rt.forward_fp8(tokens.data_ptr(), top_idx.data_ptr(), prob.data_ptr(), out.data_ptr(), tokens.shape[0])
+            self._keep = (tokens, top_idx, prob)  # alive until the enqueued kernels have read them
+            return out
         return _FusedMoEFunction.apply(tokens, top_idx, prob, self)
 
     # ---- introspection (these read device memory: debugging / tests only) ---

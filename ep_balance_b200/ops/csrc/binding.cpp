@@ -291,7 +291,7 @@ void quantize_rows(torch::Tensor x, torch::Tensor q, torch::Tensor sfa) {
   TORCH_CHECK(rows % 128 == 0 && K % 128 == 0, "rows and K must be multiples of 128");
   TORCH_CHECK(sfa.numel() == (int64_t)(rows / 128) * ((K / 128 + 3) / 4) * 512, "sfa has the wrong size");
   cuda_check(epb::launch_quantize_rows(dptr<void>(x, "x", torch::kBFloat16), dptr<uint8_t>(q, "q", torch::kUInt8),
-                                       dptr<uint8_t>(sfa, "sfa", torch::kUInt8), rows, K, current_stream()),
+                                       dptr<uint8_t>(sfa, "sfa", torch::kUInt8), rows, K, nullptr, current_stream()),
              "launch_quantize_rows");
 }
 void quantize_weights(torch::Tensor w, torch::Tensor q, torch::Tensor sfb) {
@@ -414,6 +414,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("dgrad1", [](MoeRuntime& r) { r.dgrad1(current_stream()); })
       .def("reduce_dtokens", [](MoeRuntime& r, uint64_t dt, int n) { r.reduce_dtokens(mp(dt), n, current_stream()); })
       .def("reduce_weight_grads", [](MoeRuntime& r) { r.reduce_weight_grads(current_stream()); })
+      .def("has_fp8", &MoeRuntime::has_fp8)
+      .def("quantize_own_weights", [](MoeRuntime& r) { r.quantize_own_weights(current_stream()); })
+      .def("pull_weights_fp8", [](MoeRuntime& r) { r.pull_weights_fp8(current_stream()); })
+      .def("gemm1_fp8", [](MoeRuntime& r) { r.gemm1_fp8(current_stream()); })
+      .def("act_fp8", [](MoeRuntime& r) { r.act_fp8(current_stream()); })
+      .def("gemm2_fp8", [](MoeRuntime& r) { r.gemm2_fp8(current_stream()); })
+      .def("forward_fp8", [](MoeRuntime& r, uint64_t tok, uint64_t idx, uint64_t prob, uint64_t out, int n) {
+        r.forward_fp8(cp(tok), (const int64_t*)cp(idx), (const float*)cp(prob), mp(out), n, current_stream());
+      })
       .def("forward", [](MoeRuntime& r, uint64_t tok, uint64_t idx, uint64_t prob, uint64_t out, int n) {
         r.forward(cp(tok), (const int64_t*)cp(idx), (const float*)cp(prob), mp(out), n, current_stream());
       })

@@ -417,8 +417,10 @@ __device__ __forceinline__ int chunk_byte(int r_in_128, int kb) { return (r_in_1
 
 // One warp per row; per 128-wide block each lane handles 4 consecutive values.
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                                                            uint8_t* __restrict__ sfa, int rows, int K) {
+                                                            uint8_t* __restrict__ sfa, int rows, int K,
+                                                            const int32_t* __restrict__ row_limit) {
   const int warp = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (row_limit != nullptr && *row_limit < rows) rows = *row_limit;
   if (warp >= rows) return;
   const int kblocks = K / 128, kgroups = (kblocks + 3) / 4;
   const __nv_bfloat16* xr = x + (size_t)warp * K;
@@ -441,6 +443,48 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
   // k-blocks of a partial last group keep the neutral exponent
   if (lane == 0)
     for (int kb = kblocks; kb < kgroups * 4; ++kb) chunk_row[(size_t)(kb >> 2) * 512 + chunk_byte(warp & 127, kb)] = 127;
+}
+
+// SwiGLU + quantisation in one pass: h [rows, 2F] (gate columns, then up columns) ->
+// act = silu(gate) * up as e4m3 [rows, F] with 1 x 128 scales (and, optionally, as bf16 too).
+__global__ void __launch_bounds__(256) swiglu_quantize_kernel(const __nv_bfloat16* __restrict__ h, uint8_t* __restrict__ q,
+                                                              uint8_t* __restrict__ sfa, __nv_bfloat16* __restrict__ act,
+                                                              int rows, int F, const int32_t* __restrict__ row_limit) {
+  const int warp = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (row_limit != nullptr && *row_limit < rows) rows = *row_limit;
+  if (warp >= rows) return;
+  const int kblocks = F / 128, kgroups = (kblocks + 3) / 4;
+  const __nv_bfloat16* hr = h + (size_t)warp * 2 * F;
+  uint8_t* qr = q + (size_t)warp * F;
+  uint8_t* chunk_row = sfa + (size_t)(warp >> 7) * kgroups * 512;
+  for (int kb = 0; kb < kblocks; ++kb) {
+    const uint2 graw = *reinterpret_cast<const uint2*>(hr + kb * 128 + lane * 4);
+    const uint2 uraw = *reinterpret_cast<const uint2*>(hr + F + kb * 128 + lane * 4);
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&graw);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&uraw);
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float2 g = __bfloat1622float2(gh[j]), u = __bfloat1622float2(uh[j]);
+      v[2 * j] = g.x * __fdividef(1.f, 1.f + __expf(-g.x)) * u.x;
+      v[2 * j + 1] = g.y * __fdividef(1.f, 1.f + __expf(-g.y)) * u.y;
+    }
+    if (act != nullptr) {
+      uint2 o;
+      o.x = pack_bf16(v[0], v[1]);
+      o.y = pack_bf16(v[2], v[3]);
+      *reinterpret_cast<uint2*>(act + (size_t)warp * F + kb * 128 + lane * 4) = o;
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const int e = scale_exponent(amax);
+    const float inv = exp2_int(-e);
+    const unsigned lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+    const unsigned hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint32_t*>(qr + kb * 128 + lane * 4) = (lo & 0xffffu) | (hi << 16);
+    if (lane == 0) chunk_row[(size_t)(kb >> 2) * 512 + chunk_byte(warp & 127, kb)] = (uint8_t)(e + 127);
+  }
 }
 
 // One CTA per (k-block, n-block, slot): 128 x 128 values, 256 threads, 64 values each.
@@ -551,11 +595,22 @@ cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& t
   return cudaGetLastError();
 }
 
-cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, cudaStream_t stream) {
+cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, const int32_t* row_limit,
+                                 cudaStream_t stream) {
   if (rows % 128 != 0 || K % 128 != 0) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
   const int blocks = (rows + 7) / 8;
-  quantize_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), q, sfa, rows, K);
+  quantize_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), q, sfa, rows, K, row_limit);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_quantize(const void* h, uint8_t* q, uint8_t* sfa, void* act, int rows, int F,
+                                   const int32_t* row_limit, cudaStream_t stream) {
+  if (rows % 128 != 0 || F % 128 != 0) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  const int blocks = (rows + 7) / 8;
+  swiglu_quantize_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(h), q, sfa,
+                                                     reinterpret_cast<__nv_bfloat16*>(act), rows, F, row_limit);
   return cudaGetLastError();
 }
 

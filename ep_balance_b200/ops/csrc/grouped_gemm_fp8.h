@@ -48,7 +48,13 @@ cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& t
                                     int num_sms, cudaStream_t stream);
 
 // bf16 [rows, K] -> e4m3 [rows, K] + 1 x 128 scales in chunk layout.  rows % 128 == 0, K % 128 == 0.
-cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, cudaStream_t stream);
+// `row_limit` (device, may be null): only rows below *row_limit are processed.
+cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, const int32_t* row_limit,
+                                 cudaStream_t stream);
+// h bf16 [rows, 2F] (gate columns, then up columns) -> silu(gate) * up as e4m3 [rows, F] + scales;
+// `act` (bf16 [rows, F], may be null) also receives the unquantised activation.
+cudaError_t launch_swiglu_quantize(const void* h, uint8_t* q, uint8_t* sfa, void* act, int rows, int F,
+                                   const int32_t* row_limit, cudaStream_t stream);
 // bf16 [slots, N, K] -> e4m3 + 128 x 128 scales in chunk layout.  N % 128 == 0, K % 128 == 0.
 cudaError_t launch_quantize_weights(const void* w, uint8_t* q, uint8_t* sfb, int slots, int N, int K,
                                     cudaStream_t stream);

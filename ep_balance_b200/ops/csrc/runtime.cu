@@ -100,6 +100,17 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
   tmap2(&tm_act_mn_, ptr<void>("act"), T, F, 64, 64);
   tmap2(&tm_dh_mn_, ptr<void>("hbuf"), T, 2 * F, 64, 64);
   tmap2(&tm_x_mn_, ptr<void>("xbuf"), T, H, 64, 64);
+
+  // optional block-scaled fp8 forward
+  if (ptr<void>("w1q", false) != nullptr) {
+    if (c.H % 128 || c.F % 128) throw std::runtime_error("MoeRuntime: the fp8 path needs H % 128 == 0 and F % 128 == 0");
+    for (const char* name : {"w2q", "sfb1", "sfb2", "xq", "sfx", "actq", "sfact", "w1q_ptrs", "w2q_ptrs", "sfb1_ptrs", "sfb2_ptrs"})
+      ptr<void>(name);
+    if (!make_tmap_fp8_2d(&tm_xq_, ptr<void>("xq"), T, H) || !make_tmap_fp8_2d(&tm_actq_, ptr<void>("actq"), T, F) ||
+        !make_tmap_fp8_3d(&tm_w1q_, ptr<void>("w1q"), S, 2 * F, H) || !make_tmap_fp8_3d(&tm_w2q_, ptr<void>("w2q"), S, H, F))
+      throw std::runtime_error("MoeRuntime: cuTensorMapEncodeTiled (fp8) failed");
+    fp8_ = true;
+  }
 }
 
 // ------------------------------------------------------------------ forward pieces
@@ -196,6 +207,98 @@ void MoeRuntime::gemm2(cudaStream_t stream) {
 }
 void MoeRuntime::reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream) {
   check(launch_unit_reduce(ptr<void>("ybuf"), topk_prob, out, num_tokens, cfg_.topk, cfg_.H, stream), "unit_reduce");
+}
+
+// ------------------------------------------------------------------ block-scaled fp8 forward
+namespace {
+inline size_t sf_bytes_per_slot(int N, int K) { return (size_t)(N / 128) * ((K / 128 + 3) / 4) * 512; }
+}  // namespace
+
+void MoeRuntime::quantize_own_weights(cudaStream_t stream) {
+  if (!fp8_) throw std::runtime_error("MoeRuntime: fp8 regions were not provided");
+  check(launch_quantize_weights(ptr<void>("w1"), ptr<uint8_t>("w1q"), ptr<uint8_t>("sfb1"), cfg_.home_cap, 2 * cfg_.F,
+                                cfg_.H, stream),
+        "quantize_weights(w1)");
+  check(launch_quantize_weights(ptr<void>("w2"), ptr<uint8_t>("w2q"), ptr<uint8_t>("sfb2"), cfg_.home_cap, cfg_.H,
+                                cfg_.F, stream),
+        "quantize_weights(w2)");
+}
+
+void MoeRuntime::pull_weights_fp8(cudaStream_t stream) {
+  if (cfg_.w_slots <= cfg_.home_cap) return;
+  WeightPullArgs a{};
+  a.slot_of = tables_.slot_of;
+  a.main_rank = sp_.main_rank;
+  a.home_index = tables_.home_index;
+  a.E = cfg_.E;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.home_cap = cfg_.home_cap;
+  a.n_slot = cfg_.w_slots;
+  // the pull kernel counts 2-byte elements
+  const size_t w1_bytes = (size_t)2 * cfg_.F * cfg_.H, w2_bytes = (size_t)cfg_.F * cfg_.H;
+  const struct { const char* name; size_t bytes; } regions[4] = {
+      {"w1q_ptrs", w1_bytes}, {"w2q_ptrs", w2_bytes},
+      {"sfb1_ptrs", sf_bytes_per_slot(2 * cfg_.F, cfg_.H)}, {"sfb2_ptrs", sf_bytes_per_slot(cfg_.H, cfg_.F)}};
+  for (const auto& r : regions) {
+    a.w_ptrs = ptr<void* const>(r.name);
+    a.elems_per_slot = r.bytes / 2;
+    check(launch_weight_pull(a, stream), "weight_pull(fp8)");
+  }
+}
+
+void MoeRuntime::gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int K, const uint8_t* sfa,
+                          const uint8_t* sfb, void* out, void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
+  Fp8GemmArgs g{};
+  g.group_off = tables_.group_off;
+  g.group_rows = tables_.group_rows;
+  g.group_wslot = tables_.group_wslot;
+  g.totals = tables_.totals;
+  g.n_groups_cap = cfg_.w_slots;
+  g.row_capacity = cfg_.row_capacity;
+  g.N = N;
+  g.K = K;
+  g.sfa = sfa;
+  g.sfb = sfb;
+  g.out = out;
+  g.out_ptrs = out_ptrs;
+  g.meta = meta;
+  g.status = sp_.status;
+  check(launch_grouped_gemm_fp8(a, b, g, cfg_.num_sms, stream), "grouped_gemm_fp8");
+}
+
+void MoeRuntime::gemm1_fp8(cudaStream_t stream) {
+  check(launch_quantize_rows(ptr<void>("xbuf"), ptr<uint8_t>("xq"), ptr<uint8_t>("sfx"), cfg_.row_capacity, cfg_.H,
+                             tables_.totals, stream),
+        "quantize_rows(x)");
+  gemm_fp8(tm_xq_, tm_w1q_, 2 * cfg_.F, cfg_.H, ptr<uint8_t>("sfx"), ptr<uint8_t>("sfb1"), ptr<void>("hbuf"), nullptr,
+           nullptr, stream);
+}
+void MoeRuntime::act_fp8(cudaStream_t stream) {
+  check(launch_swiglu_quantize(ptr<void>("hbuf"), ptr<uint8_t>("actq"), ptr<uint8_t>("sfact"), nullptr, cfg_.row_capacity,
+                               cfg_.F, tables_.totals, stream),
+        "swiglu_quantize");
+}
+void MoeRuntime::gemm2_fp8(cudaStream_t stream) {
+  gemm_fp8(tm_actq_, tm_w2q_, cfg_.H, cfg_.F, ptr<uint8_t>("sfact"), ptr<uint8_t>("sfb2"), nullptr,
+           ptr<void* const>("ybuf_ptrs"), ptr<const int2>("meta"), stream);
+}
+
+void MoeRuntime::forward_fp8(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out,
+                             int num_tokens, cudaStream_t stream) {
+  if (!fp8_) throw std::runtime_error("MoeRuntime: fp8 regions were not provided");
+  const int U = num_tokens * cfg_.topk;
+  publish(topk_idx, U, stream);
+  solve(stream);
+  route(topk_idx, U, stream);
+  dispatch_tokens(tokens, U, stream);
+  pull_weights_fp8(stream);
+  barrier(1, stream);
+  gemm1_fp8(stream);
+  act_fp8(stream);
+  gemm2_fp8(stream);
+  barrier(2, stream);
+  reduce_out(topk_prob, out, num_tokens, stream);
 }
 
 // ------------------------------------------------------------------ backward pieces

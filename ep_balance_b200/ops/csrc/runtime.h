@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "grouped_gemm.h"
+#include "grouped_gemm_fp8.h"
 #include "route.h"
 #include "solver.h"
 
@@ -56,6 +57,16 @@ class MoeRuntime {
   void reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream);
   void reduce_weight_grads(cudaStream_t stream);
 
+  // ---- block-scaled fp8 forward (inference): present when the fp8 weight regions were given
+  bool has_fp8() const { return fp8_; }
+  void quantize_own_weights(cudaStream_t stream);   // bf16 home slots -> e4m3 + 128 x 128 scales
+  void pull_weights_fp8(cudaStream_t stream);       // replicas pull e4m3 bytes and scale chunks: half the bytes of bf16
+  void gemm1_fp8(cudaStream_t stream);              // quantise received rows (1 x 128), h = x W1^T
+  void act_fp8(cudaStream_t stream);                // SwiGLU + quantise
+  void gemm2_fp8(cudaStream_t stream);              // y = act W2^T, rows scattered to their sources
+  void forward_fp8(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out, int num_tokens,
+                   cudaStream_t stream);
+
   // ---- whole passes
   void forward(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out, int num_tokens,
                cudaStream_t stream);
@@ -92,6 +103,10 @@ class MoeRuntime {
   CUtensorMap tm_x_k_, tm_act_k_, tm_dy_k_, tm_dh_k_;           // K-major A operands
   CUtensorMap tm_w1_k_, tm_w2_k_, tm_w1_mn_, tm_w2_mn_;          // weights as B
   CUtensorMap tm_dy_mn_, tm_act_mn_, tm_dh_mn_, tm_x_mn_;        // Wgrad operands (MN-major)
+  bool fp8_ = false;
+  CUtensorMap tm_xq_, tm_actq_, tm_w1q_, tm_w2q_;                // e4m3 operands
+  void gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int K, const uint8_t* sfa, const uint8_t* sfb,
+                void* out, void* const* out_ptrs, const int2* meta, cudaStream_t stream);
 };
 
 }  // namespace epb

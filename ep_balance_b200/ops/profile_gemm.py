@@ -27,6 +27,7 @@ def main() -> None:
     ap.add_argument("--modes", default="fwd1,fwd2,dgrad2,dgrad1,wgrad")
     ap.add_argument("--iters", type=int, default=1)
     ap.add_argument("--ctas", type=int, default=2, choices=[1, 2])
+    ap.add_argument("--fp8", action="store_true", help="also time the block-scaled fp8 GEMMs (x W1^T and act W2^T)")
     a = ap.parse_args()
     ext = load()
     dev = torch.device("cuda")
@@ -68,6 +69,32 @@ def main() -> None:
         torch.cuda.synchronize()
         ms = t0.elapsed_time(t1) / a.iters
         print(f"{name:<7} {ms:8.4f} ms  {flops / ms * 1e-9:8.1f} TFLOP/s  status={status.tolist()[0]}")
+    if a.fp8:
+        from . import fp8
+
+        for name, A, W, N in (("fp8_w1", x, w1, 2 * Fd), ("fp8_w2", act, w2, H)):
+            aq, sfa = fp8.quantize_rows(A)
+            bq, sfb = fp8.quantize_weights(W)
+            out = torch.empty(T, N, device=dev).bfloat16()
+            run = lambda: fp8.grouped_gemm_fp8(aq, sfa, bq, sfb, out, goff, grows, gws, totals, status, sms)
+            run()
+            torch.cuda.synchronize()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(a.iters):
+                run()
+            t1.record()
+            torch.cuda.synchronize()
+            ms = t0.elapsed_time(t1) / a.iters
+            flops = 2 * real * A.shape[1] * N
+            print(f"{name:<7} {ms:8.4f} ms  {flops / ms * 1e-9:8.1f} TFLOP/s  status={status.tolist()[0]}")
+            tq0, tq1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            tq0.record()
+            for _ in range(a.iters):
+                fp8.quantize_rows(A)
+            tq1.record()
+            torch.cuda.synchronize()
+            print(f"{name:<7} quantize_rows [{A.shape[0]}, {A.shape[1]}] {tq0.elapsed_time(tq1) / a.iters:8.4f} ms")
 
 
 if __name__ == "__main__":

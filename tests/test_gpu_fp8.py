@@ -71,3 +71,35 @@ def test_fp8_grouped_gemm_matches_dequantised_fp32(K, N):
         # rows past the group's end were not touched
         pad_end = o + (r + 127) // 128 * 128
         assert bool((out[o + r:pad_end] == 7.0).all())
+
+
+@pytest.mark.parametrize("world", [1, 4])
+def test_fp8_inference_forward_matches_bf16_oracle(world):
+    """Whole layer forward with fp8 expert GEMMs (single rank; four emulated ranks with fp8 replica pulls)."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+    from ep_balance_b200.models.reference_moe import moe_reference
+
+    torch.manual_seed(2)
+    E, K, N, H, Fd = 16, 2, 256, 256, 384
+    cfg = MoEConfig(hidden=H, ffn=Fd, num_experts=E, top_k=K, max_tokens=N, extra_slots=2, num_domains=1,
+                    capacity_factor=float(world), fp8_inference=True)
+    cl = EmulatedCluster(cfg, world=world)
+    bias = torch.zeros(E, device="cuda")
+    bias[:3] = 3.0
+    for l in cl.layers:
+        l.router_bias = bias
+        l.quantize_weights()
+    tokens = [torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)]
+    outs, routing = cl.forward_fp8(tokens)
+    torch.cuda.synchronize()
+    for l in cl.layers:
+        l.check_status()
+    if world > 1:
+        assert int(cl.layers[0].last_plan().x.sum()) > E   # replicas exist, so fp8 weights crossed ranks
+    w1, w2 = cl.full_weights()
+    for r in range(world):
+        idx, prob = routing[r]
+        want = moe_reference(tokens[r].float(), idx, prob, w1.float(), w2.float())
+        assert _rel(outs[r], want) < 0.08, r
+        assert _rel(outs[r], want) > 1e-4   # it really is the quantised path
