@@ -5,7 +5,8 @@
         --master-port 29523 -m ep_balance_b200.launch.run_dsv3_stack
 
 Synthetic N(0,1) tokens, random-init weights, skewed router (bias tuned to expert max/mean ~= 4).
-Device-timed with CUDA events, max over ranks.  bf16 expert GEMMs (no fp8 path in this version).
+Device-timed with CUDA events, max over ranks.  Training runs bf16 expert GEMMs; ``--fp8`` adds the
+inference forward with block-scaled fp8 expert GEMMs (1 x 128 activation, 128 x 128 weight scales).
 """
 
 from __future__ import annotations
@@ -28,6 +29,9 @@ def main(argv=None):
     p.add_argument("--steps", type=int, default=5)
     p.add_argument("--warmup", type=int, default=2)
     p.add_argument("--infer-batches", type=int, nargs="*", default=[64, 256, 1024, 4096])
+    p.add_argument("--graphs", action="store_true",
+                   help="also time the inference forward replayed from a CUDA graph (one graph per batch size)")
+    p.add_argument("--fp8", action="store_true", help="also time the inference forward with block-scaled fp8 expert GEMMs")
     a = p.parse_args(argv)
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -41,7 +45,7 @@ def main(argv=None):
     from ..utils.workload import router_bias_for_imbalance
 
     cfg = DSv3Config(layers=a.layers, hidden=a.hidden, ffn=a.ffn, experts=a.experts, shared_ffn=a.ffn,
-                     max_tokens=a.tokens, num_domains=2 if world >= 4 else 1)
+                     max_tokens=a.tokens, num_domains=2 if world >= 4 else 1, fp8_inference=a.fp8)
     model = DSv3Stack(cfg, dev, rank=rank, world=world)
     if world > 1:
         for prm in model.dense_parameters():
@@ -82,6 +86,21 @@ def main(argv=None):
     out["train_tokens_per_s"] = a.tokens * world / (out["train_ms_per_step"] * 1e-3)
     loads = model.blocks[0].moe.rank_loads().float()
     out["rank_load_max_over_mean_layer0"] = float(loads.max() / loads.mean().clamp_min(1))
+    def graphed(xb):
+        """Capture one forward of the whole stack and return a replay function (static input and output)."""
+        static_in = xb.clone()
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                model(static_in)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = model(static_in)
+        return graph.replay, static_out
+
     infer = {}
     with torch.no_grad():
         for nb in a.infer_batches:
@@ -90,7 +109,31 @@ def main(argv=None):
             xb = x[:nb].contiguous()
             model(xb)
             infer[str(nb)] = timed(lambda: model(xb), a.steps)
+            if a.graphs:
+                replay, _ = graphed(xb)
+                infer[f"{nb}_graph"] = timed(replay, a.steps)
     out["inference_forward_ms"] = infer
+    if a.fp8:
+        model.quantize_weights()
+        infer8, err = {}, {}
+        with torch.no_grad():
+            for nb in a.infer_batches:
+                if nb > a.tokens:
+                    continue
+                xb = x[:nb].contiguous()
+                y8 = model(xb)
+                for b in model.blocks:
+                    b.moe._fp8_ready = False
+                y16 = model(xb)
+                for b in model.blocks:
+                    b.moe._fp8_ready = True
+                err[str(nb)] = float((y8.float() - y16.float()).norm() / y16.float().norm().clamp_min(1e-12))
+                infer8[str(nb)] = timed(lambda: model(xb), a.steps)
+                if a.graphs:
+                    replay, _ = graphed(xb)
+                    infer8[f"{nb}_graph"] = timed(replay, a.steps)
+        out["inference_forward_fp8_ms"] = infer8
+        out["fp8_vs_bf16_relative_error"] = err
     model.check_status()
     if rank == 0:
         print(json.dumps(out), flush=True)

@@ -49,6 +49,7 @@ class DSv3Config:
     extra_slots: int = 2
     capacity_factor: float = 2.0
     num_domains: int = 2
+    fp8_inference: bool = False  # forwards without autograd use block-scaled fp8 expert GEMMs
 
 
 class SharedExpert(nn.Module):
@@ -83,11 +84,12 @@ class DSv3Stack(nn.Module):
     def __init__(self, cfg: DSv3Config, device, *, rank: int = 0, world: int = 1, group=None,
                  solver_cfg: Optional[EPLBConfig] = None) -> None:
         super().__init__()
-        self.cfg, self.rank, self.world = cfg, rank, world
+        self.cfg, self.rank, self.world, self.group = cfg, rank, world, group
         domains = cfg.num_domains if world % max(cfg.num_domains, 1) == 0 and world >= cfg.num_domains else 1
         mcfg = MoEConfig(hidden=cfg.hidden, ffn=cfg.ffn, num_experts=cfg.experts, top_k=cfg.top_k,
                          max_tokens=cfg.max_tokens, extra_slots=cfg.extra_slots,
-                         capacity_factor=cfg.capacity_factor, num_domains=domains)
+                         capacity_factor=cfg.capacity_factor, num_domains=domains,
+                         fp8_inference=cfg.fp8_inference)
         self.heaps: List[SymmetricHeap] = []
         blocks = []
         for layer in range(cfg.layers):
@@ -120,3 +122,12 @@ class DSv3Stack(nn.Module):
     def check_status(self) -> None:
         for b in self.blocks:
             b.moe.check_status()
+
+    def quantize_weights(self) -> None:
+        """Refresh the fp8 copies of every layer's own experts (``DSv3Config.fp8_inference``); collective:
+        every rank calls it, and the ranks are synchronised before the next forward reads peers' copies."""
+        for b in self.blocks:
+            b.moe.quantize_weights()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier(group=self.group)

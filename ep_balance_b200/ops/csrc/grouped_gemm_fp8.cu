@@ -415,13 +415,25 @@ __device__ __forceinline__ int scale_exponent(float amax) {
 __device__ __forceinline__ float exp2_int(int e) { return __int_as_float((e + 127) << 23); }  // e in [-126, 127]
 __device__ __forceinline__ int chunk_byte(int r_in_128, int kb) { return (r_in_128 & 31) * 16 + (r_in_128 >> 5) * 4 + (kb & 3); }
 
+// Is `row` inside one of the groups?  The whole warp calls this with the same row.
+__device__ __forceinline__ bool row_is_real(const RowGroups& g, int row, int lane) {
+  if (g.group_off == nullptr) return true;
+  if (row >= g.totals[0]) return false;
+  int n = g.totals[1];
+  if (n > g.n_groups_cap) n = g.n_groups_cap;
+  for (int base = 0; base < n; base += 32) {
+    const int i = base + lane;
+    const bool in = i < n && row >= g.group_off[i] && row < g.group_off[i] + g.group_rows[i];
+    if (__ballot_sync(0xffffffffu, in)) return true;
+  }
+  return false;
+}
+
 // One warp per row; per 128-wide block each lane handles 4 consecutive values.
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
-                                                            uint8_t* __restrict__ sfa, int rows, int K,
-                                                            const int32_t* __restrict__ row_limit) {
+                                                            uint8_t* __restrict__ sfa, int rows, int K, RowGroups groups) {
   const int warp = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
-  if (row_limit != nullptr && *row_limit < rows) rows = *row_limit;
-  if (warp >= rows) return;
+  if (warp >= rows || !row_is_real(groups, warp, lane)) return;
   const int kblocks = K / 128, kgroups = (kblocks + 3) / 4;
   const __nv_bfloat16* xr = x + (size_t)warp * K;
   uint8_t* qr = q + (size_t)warp * K;
@@ -449,10 +461,9 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
 // act = silu(gate) * up as e4m3 [rows, F] with 1 x 128 scales (and, optionally, as bf16 too).
 __global__ void __launch_bounds__(256) swiglu_quantize_kernel(const __nv_bfloat16* __restrict__ h, uint8_t* __restrict__ q,
                                                               uint8_t* __restrict__ sfa, __nv_bfloat16* __restrict__ act,
-                                                              int rows, int F, const int32_t* __restrict__ row_limit) {
+                                                              int rows, int F, RowGroups groups) {
   const int warp = (int)((blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
-  if (row_limit != nullptr && *row_limit < rows) rows = *row_limit;
-  if (warp >= rows) return;
+  if (warp >= rows || !row_is_real(groups, warp, lane)) return;
   const int kblocks = F / 128, kgroups = (kblocks + 3) / 4;
   const __nv_bfloat16* hr = h + (size_t)warp * 2 * F;
   uint8_t* qr = q + (size_t)warp * F;
@@ -595,22 +606,24 @@ cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& t
   return cudaGetLastError();
 }
 
-cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, const int32_t* row_limit,
+cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, const RowGroups* groups,
                                  cudaStream_t stream) {
   if (rows % 128 != 0 || K % 128 != 0) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
   const int blocks = (rows + 7) / 8;
-  quantize_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), q, sfa, rows, K, row_limit);
+  quantize_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), q, sfa, rows, K,
+                                                   groups ? *groups : RowGroups{nullptr, nullptr, nullptr, 0});
   return cudaGetLastError();
 }
 
 cudaError_t launch_swiglu_quantize(const void* h, uint8_t* q, uint8_t* sfa, void* act, int rows, int F,
-                                   const int32_t* row_limit, cudaStream_t stream) {
+                                   const RowGroups* groups, cudaStream_t stream) {
   if (rows % 128 != 0 || F % 128 != 0) return cudaErrorInvalidValue;
   if (rows == 0) return cudaSuccess;
   const int blocks = (rows + 7) / 8;
   swiglu_quantize_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(h), q, sfa,
-                                                     reinterpret_cast<__nv_bfloat16*>(act), rows, F, row_limit);
+                                                     reinterpret_cast<__nv_bfloat16*>(act), rows, F,
+                                                     groups ? *groups : RowGroups{nullptr, nullptr, nullptr, 0});
   return cudaGetLastError();
 }
 

@@ -47,14 +47,23 @@ bool make_tmap_fp8_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64
 cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmArgs& args,
                                     int num_sms, cudaStream_t stream);
 
+// Optional description of which rows of a buffer hold data (device tables of the group layout): row r
+// is real when group_off[g] <= r < group_off[g] + group_rows[g] for some g < min(totals[1], n_groups_cap).
+struct RowGroups {
+  const int32_t* group_off;
+  const int32_t* group_rows;
+  const int32_t* totals;
+  int n_groups_cap;
+};
+
 // bf16 [rows, K] -> e4m3 [rows, K] + 1 x 128 scales in chunk layout.  rows % 128 == 0, K % 128 == 0.
-// `row_limit` (device, may be null): only rows below *row_limit are processed.
-cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, const int32_t* row_limit,
+// `groups` (may be null): only real rows are processed; the rest keep whatever they held.
+cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int rows, int K, const RowGroups* groups,
                                  cudaStream_t stream);
 // h bf16 [rows, 2F] (gate columns, then up columns) -> silu(gate) * up as e4m3 [rows, F] + scales;
 // `act` (bf16 [rows, F], may be null) also receives the unquantised activation.
 cudaError_t launch_swiglu_quantize(const void* h, uint8_t* q, uint8_t* sfa, void* act, int rows, int F,
-                                   const int32_t* row_limit, cudaStream_t stream);
+                                   const RowGroups* groups, cudaStream_t stream);
 // bf16 [slots, N, K] -> e4m3 + 128 x 128 scales in chunk layout.  N % 128 == 0, K % 128 == 0.
 cudaError_t launch_quantize_weights(const void* w, uint8_t* q, uint8_t* sfb, int slots, int N, int K,
                                     cudaStream_t stream);

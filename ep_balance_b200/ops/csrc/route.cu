@@ -168,29 +168,33 @@ __global__ void __launch_bounds__(256) unit_reduce_kernel(const uint4* __restric
                                                          const float* __restrict__ unit_scale,
                                                          uint4* __restrict__ out, int num_tokens, int topk,
                                                          int vec_per_row) {
+  // one warp per (token, 32-vector chunk of the row): small batches still fill the machine
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-  const int t = blockIdx.x * wpb + warp;
+  const int chunks = (vec_per_row + 31) / 32;
+  const long long item = (long long)blockIdx.x * wpb + warp;
+  const int t = (int)(item / chunks);
   if (t >= num_tokens) return;
-  for (int v = lane; v < vec_per_row; v += 32) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int k = 0; k < topk; ++k) {
-      const size_t u = (size_t)t * topk + k;
-      const uint4 val = unit_rows[u * vec_per_row + v];
-      const float s = unit_scale ? unit_scale[u] : 1.f;
-      const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&val);
+  const int v = (int)(item - (long long)t * chunks) * 32 + lane;
+  if (v >= vec_per_row) return;
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll 8
+  for (int k = 0; k < topk; ++k) {
+    const size_t u = (size_t)t * topk + k;
+    const uint4 val = unit_rows[u * vec_per_row + v];
+    const float s = unit_scale ? unit_scale[u] : 1.f;
+    const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&val);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 f = __bfloat1622float2(pv[i]);
-        acc[2 * i] += s * f.x;
-        acc[2 * i + 1] += s * f.y;
-      }
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(pv[i]);
+      acc[2 * i] += s * f.x;
+      acc[2 * i + 1] += s * f.y;
     }
-    uint4 o;
-    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-    out[(size_t)t * vec_per_row + v] = o;
   }
+  uint4 o;
+  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  out[(size_t)t * vec_per_row + v] = o;
 }
 
 // ------------------------------------------------------------------ cross-rank barrier
@@ -352,7 +356,9 @@ cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, v
                                int H, cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
   const int wpb = 8;
-  unit_reduce_kernel<<<ceil_div(num_tokens, wpb), wpb * 32, 0, stream>>>(
+  const long long items = (long long)num_tokens * ceil_div(H / 8, 32);
+  if (items == 0) return cudaSuccess;
+  unit_reduce_kernel<<<(unsigned)((items + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
       reinterpret_cast<const uint4*>(unit_rows), unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8);
   return cudaGetLastError();
 }

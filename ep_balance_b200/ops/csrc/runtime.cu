@@ -130,7 +130,7 @@ void MoeRuntime::route(const int64_t* topk_idx, int num_units, cudaStream_t stre
         "route_assign");
 }
 
-void MoeRuntime::dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream) {
+void MoeRuntime::dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream, bool zero_pad) {
   DispatchArgs a{};
   a.rows = tokens;
   a.num_units = num_units;
@@ -145,7 +145,7 @@ void MoeRuntime::dispatch_tokens(const void* tokens, int num_units, cudaStream_t
   a.local_buf = ptr<void>("xbuf");
   a.slot_off = tables_.group_off;
   a.slot_rows = tables_.group_rows;
-  a.n_slot = cfg_.w_slots;
+  a.n_slot = zero_pad ? cfg_.w_slots : 0;
   a.row_capacity = cfg_.row_capacity;
   check(launch_dispatch(a, stream), "dispatch");
 }
@@ -268,15 +268,17 @@ void MoeRuntime::gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int
 }
 
 void MoeRuntime::gemm1_fp8(cudaStream_t stream) {
+  const RowGroups groups{tables_.group_off, tables_.group_rows, tables_.totals, cfg_.w_slots};
   check(launch_quantize_rows(ptr<void>("xbuf"), ptr<uint8_t>("xq"), ptr<uint8_t>("sfx"), cfg_.row_capacity, cfg_.H,
-                             tables_.totals, stream),
+                             &groups, stream),
         "quantize_rows(x)");
   gemm_fp8(tm_xq_, tm_w1q_, 2 * cfg_.F, cfg_.H, ptr<uint8_t>("sfx"), ptr<uint8_t>("sfb1"), ptr<void>("hbuf"), nullptr,
            nullptr, stream);
 }
 void MoeRuntime::act_fp8(cudaStream_t stream) {
+  const RowGroups groups{tables_.group_off, tables_.group_rows, tables_.totals, cfg_.w_slots};
   check(launch_swiglu_quantize(ptr<void>("hbuf"), ptr<uint8_t>("actq"), ptr<uint8_t>("sfact"), nullptr, cfg_.row_capacity,
-                               cfg_.F, tables_.totals, stream),
+                               cfg_.F, &groups, stream),
         "swiglu_quantize");
 }
 void MoeRuntime::gemm2_fp8(cudaStream_t stream) {
@@ -291,7 +293,7 @@ void MoeRuntime::forward_fp8(const void* tokens, const int64_t* topk_idx, const 
   publish(topk_idx, U, stream);
   solve(stream);
   route(topk_idx, U, stream);
-  dispatch_tokens(tokens, U, stream);
+  dispatch_tokens(tokens, U, stream, /*zero_pad=*/false);  // outputs of padding rows are never stored
   pull_weights_fp8(stream);
   barrier(1, stream);
   gemm1_fp8(stream);

@@ -42,7 +42,8 @@ class MoeRuntime {
   void publish(const int64_t* topk_idx, int num_units, cudaStream_t stream);
   void solve(cudaStream_t stream);
   void route(const int64_t* topk_idx, int num_units, cudaStream_t stream);
-  void dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream);
+  // zero_pad: clear the padding rows behind every group (needed when a backward pass will contract over them)
+  void dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream, bool zero_pad = true);
   void pull_weights(cudaStream_t stream);
   void barrier(int slot, cudaStream_t stream);
   void gemm1(cudaStream_t stream);
