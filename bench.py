@@ -57,12 +57,17 @@ class ClockSampler:
         self.gpu_index = gpu_index
         self.proc = None
         self.lines = []
+        self.first = 0
         self.thread = None
+
+    def mark(self) -> None:
+        """Samples taken before this call (warm-up) are not reported."""
+        self.first = len(self.lines)
 
     def start(self) -> None:
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -85,7 +90,7 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        for line in self.lines[self.first:]:
             parts = [x.strip() for x in line.split(",")]
             if len(parts) < 8:
                 continue
@@ -261,14 +266,15 @@ def run_ours(args):
 
     for ev in consumed:
         ev.record()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # started before the warm-up so that it is already sampling when the timed region begins
     for i in range(args.warmup):
         step_device(i)
     torch.cuda.synchronize()
     layer.check_status()
     layer.rt.reset_launches()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark()
     ms_dev = timed_loop(step_device, args.steps, world)
     launches = layer.rt.launches()
     for i in range(min(3, args.warmup)):
@@ -438,16 +444,18 @@ def run_reference(args):
         loss = train_step(x)
         loss_host.copy_(loss.detach().reshape(1), non_blocking=False)
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     try:
         for i in range(args.warmup):
             step_device(i)
         torch.cuda.synchronize()
     except Exception as exc:
+        sampler.stop()
         print(json.dumps({"impl": "reference", "unavailable": f"reference step failed: {type(exc).__name__}: {exc}"[:400]}))
         return
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.mark()
     ms_dev = timed_loop(step_device, args.steps, world)
     for i in range(min(3, args.warmup)):
         step_e2e(i)
