@@ -161,12 +161,12 @@ class FusedMoE(nn.Module):
         g = torch.Generator(device="cpu").manual_seed(1234 + seed)
         self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(dev, cfg.router_dtype))
         w1_all, w2_all = heap.tensor("w1", rank), heap.tensor("w2", rank)
-        ge = torch.Generator(device="cpu")
+        ge = torch.Generator(device=dev)
         for i in range(self.home_cap):
             e = rank * self.home_cap + i
-            ge.manual_seed(10_000 + 7919 * seed + e)  # weights depend on the expert id only
-            w1_all[i].copy_((torch.randn(2 * F, H, generator=ge) * 0.02).to(torch.bfloat16))
-            w2_all[i].copy_((torch.randn(H, F, generator=ge) * 0.02).to(torch.bfloat16))
+            ge.manual_seed(10_000 + 7919 * seed + e)  # weights depend on the expert id only, not on the world size
+            w1_all[i].copy_((torch.randn(2 * F, H, generator=ge, device=dev) * 0.02).to(torch.bfloat16))
+            w2_all[i].copy_((torch.randn(H, F, generator=ge, device=dev) * 0.02).to(torch.bfloat16))
         self.w1 = nn.Parameter(w1_all[: self.home_cap])
         self.w2 = nn.Parameter(w2_all[: self.home_cap])
         self._gw1 = heap.tensor("gw1", rank)[: self.home_cap]
