@@ -18,7 +18,8 @@ scripts/pretrain_eplb_moe.py:100-176):
 ``EPLB_LOG=1``           print the ``[EPLB]`` line in apply mode too (one host read per layer)
 
 ``--num-micro-batches`` accumulates gradients over several micro-batches per optimizer step (expert
-weight gradients in an fp32 ``main_grad``).  ``--save/--load/--save-interval`` checkpoint the owners'
+weight gradients in an fp32 ``main_grad``).  ``--heartbeat-file`` turns on host-side failure detection (``parallel/health.py``).
+``--save/--load/--save-interval`` checkpoint the owners'
 weights, optimizer state, data and skew generators; resuming reproduces the uninterrupted run.
 Iteration lines use Megatron's format so ``ep_balance_b200.eval.extract_train_metrics`` parses them.
 """
@@ -61,6 +62,9 @@ def main(argv=None):
     p.add_argument("--save", default="", help="checkpoint directory to write")
     p.add_argument("--load", default="", help="checkpoint directory to resume from (newest complete step)")
     p.add_argument("--save-interval", type=int, default=0, help="save every N steps (0: only at the end when --save is set)")
+    p.add_argument("--heartbeat-file", default="",
+                   help="path of a shared file store: ranks publish a heartbeat per step, refuse to launch a step "
+                        "when a peer is stale or reported a failure, and publish their own device status errors")
     a = p.parse_args(argv)
 
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
@@ -153,9 +157,19 @@ def main(argv=None):
         print(f"[ep_balance_b200] mode={mode} world={world} domains={cfg.num_domains} extra_slots={extra} "
               f"micro_batches={M} resume_step={start_step}", flush=True)
 
+    guard = None
+    if a.heartbeat_file:
+        from ..parallel.health import Heartbeat, StepGuard
+
+        hb = Heartbeat(dist.FileStore(a.heartbeat_file, world), rank, world, stale_after_s=120.0)
+        hb.beat(start_step)
+        hb.wait_for_all(300.0)
+        guard = StepGuard(hb, [model.check_status], check_every=10)
     gbs = a.micro_batch * world * M
     flops = _flops_per_step(a, a.micro_batch * a.seq_len * M)
     for step in range(start_step + 1, a.steps + 1):
+        if guard is not None:
+            guard.before_step(step)
         bias = skew.step()
         t0 = time.perf_counter()
         if M > 1:
@@ -187,6 +201,8 @@ def main(argv=None):
                       f"elapsed time per iteration (ms): {ms:.1f} | throughput per GPU (TFLOP/s/GPU): {flops / ms / 1e9:.1f} | "
                       f"learning rate: {a.lr:.6E} | global batch size: {gbs:5d} | lm loss: {float(lv):.6E} | "
                       f"grad norm: {float(gn):.3f} | rank load max/mean: {imb:.3f} |", flush=True)
+        if guard is not None:
+            guard.after_step(step)
         if a.save and a.save_interval > 0 and step % a.save_interval == 0 and step != a.steps:
             save(step)
     if a.save:
