@@ -59,6 +59,8 @@ def main(argv=None):
     p.add_argument("--lr", type=float, default=1e-4)
     p.add_argument("--log-every", type=int, default=1)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--data", default="", help="prefix of a token dataset written by launch/prepare_data.py "
+                                                "(default: uniform-random token ids)")
     p.add_argument("--save", default="", help="checkpoint directory to write")
     p.add_argument("--load", default="", help="checkpoint directory to resume from (newest complete step)")
     p.add_argument("--save-interval", type=int, default=0, help="save every N steps (0: only at the end when --save is set)")
@@ -103,6 +105,13 @@ def main(argv=None):
     skew = DriftingRouterSkew(a.layers, a.experts, rho=0.9, scale=float(os.environ.get("ROUTER_SKEW", "1.0")),
                               seed=a.seed, device=dev)
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)
+    dataset = None
+    if a.data:
+        from ..utils.data import TokenDataset
+
+        dataset = TokenDataset(a.data)
+        if dataset.meta["vocab_size"] > a.vocab:
+            raise SystemExit(f"--vocab {a.vocab} is smaller than the dataset's vocabulary {dataset.meta['vocab_size']}")
     start_step = 0
     if a.load:
         start_step, rep, shard = load_checkpoint(a.load, rank=rank, world=world)
@@ -176,7 +185,10 @@ def main(argv=None):
             model.zero_expert_grad_accum()
         total = torch.zeros((), device=dev)
         for mb in range(M):
-            ids = torch.randint(0, a.vocab, (a.micro_batch, a.seq_len + 1), generator=gen).to(dev, non_blocking=True)
+            if dataset is not None:
+                ids = dataset.sample_batch(a.micro_batch, a.seq_len, gen).to(dev, non_blocking=True)
+            else:
+                ids = torch.randint(0, a.vocab, (a.micro_batch, a.seq_len + 1), generator=gen).to(dev, non_blocking=True)
             model.set_router_bias(bias)
             loss = model(ids[:, :-1], ids[:, 1:]) / M
             loss.backward()
