@@ -59,6 +59,10 @@ def main(argv=None):
     p.add_argument("--lr", type=float, default=1e-4)
     p.add_argument("--log-every", type=int, default=1)
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--skip-train", action="store_true",
+                   help="no optimizer steps: run --eval-iters forward passes of the (loaded) model, e.g. to capture "
+                        "a routing trace of a frozen checkpoint with EPLB_MODE=observe and EPLB_TRACE_OUT")
+    p.add_argument("--eval-iters", type=int, default=10)
     p.add_argument("--data", default="", help="prefix of a token dataset written by launch/prepare_data.py "
                                                 "(default: uniform-random token ids)")
     p.add_argument("--save", default="", help="checkpoint directory to write")
@@ -174,6 +178,25 @@ def main(argv=None):
         hb.beat(start_step)
         hb.wait_for_all(300.0)
         guard = StepGuard(hb, [model.check_status], check_every=10)
+    if a.skip_train:
+        # frozen-checkpoint capture (reference: eval/run_expert_hotspot.sh:1-117): forward only, no skew drift
+        with torch.no_grad():
+            for it in range(1, a.eval_iters + 1):
+                if dataset is not None:
+                    ids = dataset.sample_batch(a.micro_batch, a.seq_len, gen).to(dev)
+                else:
+                    ids = torch.randint(0, a.vocab, (a.micro_batch, a.seq_len + 1), generator=gen).to(dev)
+                loss = model(ids[:, :-1], ids[:, 1:])
+                observe(it, 0)
+                if rank == 0:
+                    print(f" evaluation iteration {it:6d}/{a.eval_iters:6d} | lm loss: {float(loss):.6E} |", flush=True)
+        if trace is not None:
+            trace.flush()
+        model.check_status()
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return 0
     gbs = a.micro_batch * world * M
     flops = _flops_per_step(a, a.micro_batch * a.seq_len * M)
     for step in range(start_step + 1, a.steps + 1):

@@ -100,3 +100,14 @@ def test_observe_mode_logs_plans_and_writes_a_trace(tmp_path, capsys):
     assert out.count("[EPLB] layer=") == 4      # 2 layers x 2 steps
     t = load_routing_trace(trace)
     assert len(t["samples"]) == 4 and t["meta"]["num_experts"] == 8
+
+
+def test_frozen_checkpoint_capture_runs_forward_only(tmp_path, capsys):
+    from ep_balance_b200.core.trace import load_routing_trace
+
+    ck, trace = str(tmp_path / "ck"), str(tmp_path / "hot.pt")
+    _run_train(capsys, TINY + ["--steps", "2", "--save", ck])
+    _, out = _run_train(capsys, TINY + ["--load", ck, "--skip-train", "--eval-iters", "3"],
+                        env={"EPLB_MODE": "observe", "EPLB_TRACE_OUT": trace, "EPLB_TRACE_EVERY": "1"})
+    assert out.count("evaluation iteration") == 3 and "iteration        3/" not in out
+    assert len(load_routing_trace(trace)["samples"]) == 6      # 2 layers x 3 forward passes
