@@ -64,6 +64,9 @@ class MoEConfig:
     # activation scales, 128 x 128 weight scales, power-of-two scale factors).  Call
     # ``FusedMoE.quantize_weights()`` after the weights change; replicas then pull the fp8 copies.
     fp8_inference: bool = False
+    # False: Dgrad2 is a plain GEMM into a [rows, ffn] buffer followed by one elementwise SwiGLU-gradient pass
+    # (faster; costs that buffer).  True: the SwiGLU gradient runs in the GEMM epilogue, in place.
+    fused_dgrad2: bool = False
 
 
 def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
@@ -195,6 +198,8 @@ class FusedMoE(nn.Module):
             "hbuf": torch.zeros((self.row_capacity, 2 * F), dtype=torch.bfloat16, device=dev),
             "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
         }
+        if not cfg.fused_dgrad2:
+            self.loc["dact"] = torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev)
         ptrs = {k: v.data_ptr() for k, v in self.loc.items()}
         self._acc_gw1 = self._acc_gw2 = None
         if cfg.grad_accum_dtype is not None:
@@ -235,7 +240,8 @@ class FusedMoE(nn.Module):
                       allow_cross=int(sc.allow_cross_domain),
                       probe=int(sc.stage2_patience_all_scales and iters > sc.stage2_stagnation_patience + 1),
                       s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync),
-                      gemm_ctas=cfg.gemm_ctas, accum_fp32=int(cfg.grad_accum_dtype == torch.float32))
+                      gemm_ctas=cfg.gemm_ctas, accum_fp32=int(cfg.grad_accum_dtype == torch.float32),
+                      fused_dgrad2=int(cfg.fused_dgrad2))
         self.rt = load().MoeRuntime(rt_cfg, ptrs)
         self.bind_grads()
 

@@ -60,6 +60,7 @@ LayerConfig config_from_dict(const py::dict& d) {
   c.allow_cross = get_int(d, "allow_cross", 1);
   c.probe = get_int(d, "probe", 0);
   c.accum_fp32 = get_int(d, "accum_fp32", 0);
+  c.fused_dgrad2 = get_int(d, "fused_dgrad2", 0);
   c.s_tok = d.contains("s_tok") ? d["s_tok"].cast<int64_t>() : 0;
   c.num_sms = get_int(d, "num_sms", 148);
   c.multi_rank_sync = get_int(d, "multi_rank_sync", 1);

@@ -322,6 +322,35 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   }
 }
 
+__global__ void __launch_bounds__(256) swiglu_backward_kernel(const uint4* __restrict__ dact, uint4* __restrict__ h,
+                                                             int rows, int F, const int32_t* __restrict__ row_limit) {
+  if (row_limit != nullptr && *row_limit < rows) rows = *row_limit;
+  const int vec_per_row = F / 8;
+  const size_t total = (size_t)rows * vec_per_row;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+    const size_t r = i / vec_per_row;
+    const int v = (int)(i - r * vec_per_row);
+    uint4* hrow = h + r * (size_t)(2 * vec_per_row);
+    const uint4 d4 = dact[i], g4 = hrow[v], u4 = hrow[vec_per_row + v];
+    const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d4);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 og, ou;
+    __nv_bfloat162* ogp = reinterpret_cast<__nv_bfloat162*>(&og);
+    __nv_bfloat162* oup = reinterpret_cast<__nv_bfloat162*>(&ou);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 d = __bfloat1622float2(dp[k]), g = __bfloat1622float2(gp[k]), u = __bfloat1622float2(up[k]);
+      const float s0 = __fdividef(1.f, 1.f + __expf(-g.x)), s1 = __fdividef(1.f, 1.f + __expf(-g.y));
+      ogp[k] = __floats2bfloat162_rn(d.x * u.x * (s0 + g.x * s0 * (1.f - s0)), d.y * u.y * (s1 + g.y * s1 * (1.f - s1)));
+      oup[k] = __floats2bfloat162_rn(d.x * g.x * s0, d.y * g.y * s1);
+    }
+    hrow[v] = og;
+    hrow[vec_per_row + v] = ou;
+  }
+}
+
 __global__ void wait_probe_kernel(const unsigned* flag, unsigned target, unsigned long long budget_ns, int* status) {
   if (threadIdx.x == 0 && !wait_ge<true>(flag, target, budget_ns)) set_status(status, kStatusSignalTimeout, 60);
 }
@@ -387,6 +416,15 @@ cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream) {
   if (gx > 256) gx = 256;
   dim3 grid(gx, a.home_cap);
   grad_reduce_kernel<<<grid, 512, 0, stream>>>(a);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_swiglu_backward(const void* dact, void* h, int rows, int F, const int32_t* row_limit,
+                                   cudaStream_t stream) {
+  if (F % 8 != 0) return cudaErrorInvalidValue;
+  if (rows <= 0) return cudaSuccess;
+  swiglu_backward_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(dact), reinterpret_cast<uint4*>(h), rows,
+                                                     F, row_limit);
   return cudaGetLastError();
 }
 

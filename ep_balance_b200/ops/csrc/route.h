@@ -86,6 +86,12 @@ struct GradReduceArgs {
 };
 cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream);
 
+// SwiGLU backward over the first *row_limit rows, in place over the saved pre-activations:
+//   h[:, :F] <- dact * up * d/dg[g * sigmoid(g)],   h[:, F:] <- dact * g * sigmoid(g)
+// One fully coalesced pass (16-byte accesses); used after a plain Dgrad2 GEMM that wrote dact.
+cudaError_t launch_swiglu_backward(const void* dact, void* h, int rows, int F, const int32_t* row_limit,
+                                   cudaStream_t stream);
+
 // Wait on a flag nobody sets: exercises the bounded-wait / error-status path on one GPU.
 cudaError_t launch_wait_probe(const unsigned* flag, unsigned target, unsigned long long budget_ns, int* status,
                               cudaStream_t stream);

@@ -331,7 +331,18 @@ void MoeRuntime::wgrad2(cudaStream_t stream) {
   gemm(kWgrad, tm_dy_mn_, tm_act_mn_, cfg_.F, 0, cfg_.H, ptr<void>("gw2"), nullptr, nullptr, nullptr, stream);
 }
 void MoeRuntime::dgrad2(cudaStream_t stream) {
-  gemm(kDgrad2, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), nullptr, nullptr, nullptr, stream);
+  void* dact = ptr<void>("dact", false);
+  if (dact == nullptr || cfg_.fused_dgrad2) {
+    // SwiGLU gradient inside the GEMM epilogue (reads and rewrites the saved pre-activations row by row)
+    gemm(kDgrad2, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), nullptr, nullptr, nullptr, stream);
+    return;
+  }
+  // Plain Dgrad GEMM into `dact`, then one coalesced elementwise pass: the fused epilogue's per-row
+  // global loads of the pre-activations are latency-bound and keep the tensor pipe at ~40 %, so the two
+  // launches together are faster than the fused one.
+  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, dact, nullptr, nullptr, nullptr, stream);
+  check(launch_swiglu_backward(dact, ptr<void>("hbuf"), cfg_.row_capacity, cfg_.F, tables_.totals, stream),
+        "swiglu_backward");
 }
 void MoeRuntime::wgrad1(cudaStream_t stream) {
   gemm(kWgrad, tm_dh_mn_, tm_x_mn_, cfg_.H, 0, 2 * cfg_.F, ptr<void>("gw1"), nullptr, nullptr, nullptr, stream);

@@ -30,6 +30,7 @@ struct LayerConfig {
   int64_t s_tok = 0;
   int num_sms = 148;
   int gemm_ctas = 2;        // 2: grouped GEMMs run on CTA pairs (256-row tiles); 1: single CTAs (128-row tiles)
+  int fused_dgrad2 = 0;     // 1: SwiGLU gradient in the Dgrad2 epilogue; 0: plain GEMM + elementwise pass (needs 'dact')
   int accum_fp32 = 0;       // dtype of the optional gradient accumulation buffers (acc_gw1/acc_gw2)
   int multi_rank_sync = 1;  // 0: one process emulates all ranks, kernels are ordered by the stream
 };
