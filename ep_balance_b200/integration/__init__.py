@@ -10,6 +10,7 @@ from ..parallel.library_path import (AllToAllAdapter, BroadcastReplicaTransport,
                                      sync_free_moe_forward)
 from ..parallel.physical import assign_physical, build_phys_slot_table
 from ..parallel.rebalancer import EPLBRebalancer
+from ..parallel.symm_weights import SymmReplicaTransport, SymmWeightReplicator, symm_weights_enabled
 from .megatron import (MegatronEPLBHook, assert_plan_replicated, attach_router_observers, build_spec_for_megatron,
                        omega_row_from_routing_map, omega_row_from_topk_indices, reduce_router_counts_tp_cp,
                        setup_eplb_observer)

@@ -110,6 +110,44 @@ def row_capacity(cfg: MoEConfig, world: int) -> int:
     return (rows + tile - 1) // tile * tile
 
 
+def _split3(w: torch.Tensor) -> torch.Tensor:
+    """fp32 ``[A, B]`` -> bf16 ``[3A, B]`` whose three row blocks sum to ``w`` to 24 mantissa bits."""
+    hi = w.to(torch.bfloat16)
+    r1 = w - hi.float()
+    mid = r1.to(torch.bfloat16)
+    lo = (r1 - mid.float()).to(torch.bfloat16)
+    return torch.cat([hi, mid, lo], 0)
+
+
+class _RouterLinear(torch.autograd.Function):
+    """fp32 router logits ``x @ W^T`` from bf16 tokens on the tensor cores, without an fp32 copy of ``x``.
+
+    ``W`` (fp32) is split into three bf16 terms; bf16 x bf16 products are exact in the fp32 accumulator,
+    so one bf16 GEMM against the stacked terms reproduces the fp32 product to fp32 rounding.  The weight
+    gradient splits the (fp32) logit gradient the same way.  Library GEMMs (the router is not one of the
+    fused expert paths)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        E = w.shape[0]
+        stacked = torch.mm(x, _split3(w).t(), out_dtype=torch.float32)      # [N, 3E]
+        ctx.save_for_backward(x, w)
+        return stacked.view(x.shape[0], 3, E).sum(1)
+
+    @staticmethod
+    def backward(ctx, g):
+        x, w = ctx.saved_tensors
+        E = w.shape[0]
+        g = g.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[1]:
+            g3 = _split3(g.t().contiguous())                                  # [3E, N] bf16
+            dw = torch.mm(g3, x, out_dtype=torch.float32).view(3, E, -1).sum(0)
+        if ctx.needs_input_grad[0]:
+            dx = torch.mm(g.to(torch.bfloat16), w.to(torch.bfloat16))
+        return dx, dw
+
+
 class _FusedMoEFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tokens, topk_idx, topk_prob, layer):
@@ -282,7 +320,10 @@ class FusedMoE(nn.Module):
     def route_tokens(self, tokens: torch.Tensor):
         """fp32 router: logits = x . W_r^T (+ bias), top-k, softmax over the selected logits."""
         with profiling.record("apply/route", time_it=True, device=tokens.device):
-            logits = tokens.to(self.router.dtype) @ self.router.t()
+            if tokens.is_cuda and tokens.dtype == torch.bfloat16 and self.router.dtype == torch.float32:
+                logits = _RouterLinear.apply(tokens, self.router)
+            else:
+                logits = tokens.to(self.router.dtype) @ self.router.t()
             if self.router_bias is not None:
                 logits = logits + self.router_bias
             if self.route_fn is not None:

@@ -163,3 +163,22 @@ def test_weight_gradients_accumulate_over_micro_batches(acc_dtype):
         for l in cl.layers:
             l.zero_grad_accum()
         assert float(torch.cat([l._acc_gw1.flatten() for l in cl.layers]).abs().sum()) == 0.0
+
+
+def test_router_logits_from_bf16_tokens_match_fp32_matmul():
+    from ep_balance_b200.models.moe_layer import _RouterLinear
+
+    torch.manual_seed(5)
+    x = torch.randn(1024, 512, device="cuda").bfloat16().requires_grad_(True)
+    w = (torch.randn(64, 512, device="cuda") * 0.02).requires_grad_(True)
+    out = _RouterLinear.apply(x, w)
+    g = torch.randn_like(out)
+    out.backward(g)
+    xr = x.detach().double().requires_grad_(True)
+    wr = w.detach().double().requires_grad_(True)
+    ref = xr @ wr.t()
+    ref.backward(g.double())
+    assert out.dtype == torch.float32
+    assert _rel(out, ref) < 2e-6            # fp32-grade, far below bf16's 4e-3
+    assert _rel(w.grad, wr.grad) < 2e-6
+    assert _rel(x.grad, xr.grad) < 1e-2     # token gradient is bf16
