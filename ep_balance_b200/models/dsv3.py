@@ -73,6 +73,7 @@ class DSv3Block(nn.Module):
         self.moe = moe
         self.shared = SharedExpert(cfg.hidden, cfg.shared_ffn)
         moe.route_fn = lambda logits: group_limited_topk(logits, cfg.n_groups, cfg.topk_groups, cfg.top_k)
+        moe.fused_router = dict(mode=2, n_groups=cfg.n_groups, topk_groups=cfg.topk_groups, scale=1.0)
 
     def forward(self, x):
         h = self.norm(x)

@@ -214,6 +214,10 @@ class FusedMoE(nn.Module):
         self._gw2 = heap.tensor("gw2", rank)[: self.home_cap]
         self.router_bias: Optional[torch.Tensor] = None  # additive logit skew (synthetic workloads)
         self.route_fn = None  # optional ``logits [N, E] -> (top_idx int64 [N, K], prob fp32 [N, K])``
+        # Inference (no autograd) selects experts with one fused kernel.  ``None``: the default top-k + softmax
+        # (or sigmoid) router; a model with its own ``route_fn`` sets ``dict(mode=2, n_groups=, topk_groups=, scale=)``
+        # to get the fused group-limited variant, or ``False`` to always use ``route_fn``.
+        self.fused_router = None
 
         # ---- local state
         i32 = dict(dtype=torch.int32, device=dev)
@@ -324,6 +328,14 @@ class FusedMoE(nn.Module):
                 logits = _RouterLinear.apply(tokens, self.router)
             else:
                 logits = tokens.to(self.router.dtype) @ self.router.t()
+            if tokens.is_cuda and not torch.is_grad_enabled() and logits.dtype == torch.float32 and (
+                    self.fused_router or (self.fused_router is None and self.route_fn is None)):
+                fr = self.fused_router or dict(mode=0 if self.cfg.normalize_topk else 1, n_groups=1, topk_groups=1, scale=1.0)
+                top_idx = torch.empty((tokens.shape[0], self.cfg.top_k), dtype=torch.int64, device=tokens.device)
+                prob = torch.empty((tokens.shape[0], self.cfg.top_k), dtype=torch.float32, device=tokens.device)
+                load().router_topk(logits.contiguous(), self.router_bias, fr["mode"], fr["n_groups"], fr["topk_groups"],
+                                   fr["scale"], top_idx, prob)
+                return top_idx, prob
             if self.router_bias is not None:
                 logits = logits + self.router_bias
             if self.route_fn is not None:

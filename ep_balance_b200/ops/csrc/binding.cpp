@@ -13,6 +13,7 @@
 #include "onesided.h"
 #include "optim.h"
 #include "route.h"
+#include "router.h"
 #include "runtime.h"
 #include "solver.h"
 
@@ -336,6 +337,24 @@ void grouped_gemm_fp8(torch::Tensor aq, torch::Tensor sfa, torch::Tensor bq, tor
   cuda_check(epb::launch_grouped_gemm_fp8(tmA, tmB, g, (int)num_sms, current_stream()), "launch_grouped_gemm_fp8");
 }
 
+// Fused inference router: logits [N, E] -> (expert ids int64 [N, K], gate weights fp32 [N, K]).
+void router_topk(torch::Tensor logits, c10::optional<torch::Tensor> bias, int64_t mode, int64_t n_groups,
+                 int64_t topk_groups, double scale, torch::Tensor idx, torch::Tensor weights) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && idx.dim() == 2 && weights.sizes() == idx.sizes() && idx.size(0) == logits.size(0),
+              "logits [N, E], idx/weights [N, K]");
+  const float* b = nullptr;
+  if (bias.has_value() && bias->defined()) {
+    TORCH_CHECK(bias->numel() == logits.size(1), "bias must be [E]");
+    b = dptr<float>(*bias, "bias", torch::kFloat32);
+  }
+  cuda_check(epb::launch_router_topk(dptr<float>(logits, "logits", torch::kFloat32), b, (int)logits.size(0),
+                                     (int)logits.size(1), (int)idx.size(1), (int)mode, (int)n_groups, (int)topk_groups,
+                                     (float)scale, dptr<int64_t>(idx, "idx", torch::kInt64),
+                                     dptr<float>(weights, "weights", torch::kFloat32), current_stream()),
+             "launch_router_topk");
+}
+
 // ---- symmetric heap over CUDA IPC: one cudaMalloc per rank, mapped into every peer process
 py::tuple ipc_alloc(int64_t nbytes) {
   void* p = nullptr;
@@ -378,6 +397,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_signal", &wait_signal);
   m.def("symm_barrier", &symm_barrier);
   m.def("grad_reduce", &grad_reduce);
+  m.def("router_topk", &router_topk);
   m.def("quantize_rows", &quantize_rows);
   m.def("quantize_weights", &quantize_weights);
   m.def("grouped_gemm_fp8", &grouped_gemm_fp8);

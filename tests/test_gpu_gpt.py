@@ -111,3 +111,32 @@ def test_frozen_checkpoint_capture_runs_forward_only(tmp_path, capsys):
                         env={"EPLB_MODE": "observe", "EPLB_TRACE_OUT": trace, "EPLB_TRACE_EVERY": "1"})
     assert out.count("evaluation iteration") == 3 and "iteration        3/" not in out
     assert len(load_routing_trace(trace)["samples"]) == 6      # 2 layers x 3 forward passes
+
+
+@pytest.mark.parametrize("E,G,KG,K", [(256, 8, 4, 8), (64, 4, 2, 6), (32, 8, 4, 4)])
+def test_fused_router_matches_the_pytorch_formulation(E, G, KG, K):
+    from ep_balance_b200.models.dsv3 import group_limited_topk
+    from ep_balance_b200.ops.extension import load
+
+    torch.manual_seed(E)
+    ext = load()
+    N = 300
+    logits = torch.randn(N, E, device="cuda") * 2
+    bias = torch.randn(E, device="cuda")
+    idx = torch.empty(N, K, dtype=torch.int64, device="cuda")
+    w = torch.empty(N, K, dtype=torch.float32, device="cuda")
+    # group-limited (DeepSeek-V3)
+    ext.router_topk(logits, bias, 2, G, KG, 1.0, idx, w)
+    want_idx, want_w = group_limited_topk(logits + bias, G, KG, K)
+    assert torch.equal(idx.sort(-1).values, want_idx.sort(-1).values)
+    got = torch.zeros(N, E, device="cuda").scatter_(1, idx, w)
+    ref = torch.zeros(N, E, device="cuda").scatter_(1, want_idx, want_w)
+    torch.testing.assert_close(got, ref, atol=1e-5, rtol=1e-4)
+    # plain top-k + softmax over the selected logits
+    ext.router_topk(logits, None, 0, 1, 1, 1.0, idx, w)
+    tv, ti = logits.topk(K, dim=-1)
+    assert torch.equal(idx, ti)
+    torch.testing.assert_close(w, torch.softmax(tv, -1), atol=1e-6, rtol=1e-5)
+    # sigmoid gates
+    ext.router_topk(logits, None, 1, 1, 1, 1.0, idx, w)
+    torch.testing.assert_close(w, torch.sigmoid(tv), atol=1e-6, rtol=1e-5)
