@@ -45,6 +45,9 @@ def _flops_per_step(a, tokens: int) -> float:
 
 def main(argv=None):
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--model", default=os.environ.get("MODEL", ""),
+                   help="named shape from launch/recipes.py (qwen3_30b_a3b, deepseek_v2_160e, glm45_air, gpt_moe_1b); "
+                        "sets layers/hidden/heads/ffn/experts/top-k, NUM_LAYERS overrides the depth")
     p.add_argument("--layers", type=int, default=16)
     p.add_argument("--hidden", type=int, default=2048)
     p.add_argument("--heads", type=int, default=16)
@@ -72,6 +75,12 @@ def main(argv=None):
                    help="path of a shared file store: ranks publish a heartbeat per step, refuse to launch a step "
                         "when a peer is stale or reported a failure, and publish their own device status errors")
     a = p.parse_args(argv)
+    if a.model:
+        from .recipes import recipe
+
+        shape = recipe(a.model, int(os.environ.get("NUM_LAYERS", "0") or 0))
+        a.layers, a.hidden, a.heads, a.ffn = shape["layers"], shape["hidden"], shape["heads"], shape["ffn"]
+        a.experts, a.top_k = shape["experts"], shape["top_k"]
 
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)

@@ -53,7 +53,7 @@ def _import_built() -> ModuleType:
     return mod
 
 
-def build(verbose: bool = False) -> ModuleType:
+def build(verbose: bool = bool(int(os.environ.get("EPLB_CUDA_BUILD_VERBOSE", "0") or 0))) -> ModuleType:
     """Compile every source for sm_100a (no GPU needed) and import the result."""
     import torch  # noqa: F401  (must be imported before the extension)
     from torch.utils.cpp_extension import load
