@@ -357,15 +357,12 @@ def phase_table(layer, x):
 
 # ---------------------------------------------------------------- the reference
 def run_reference(args):
-    ref_root = os.path.join(ROOT, "baseline", "_ref")
-    if os.path.isdir("/root/repo/baseline/_ref/eplb"):
-        ref_root = "/root/repo/baseline/_ref"  # stable path: lets a pre-built solver extension be reused
-    if not os.path.isdir(os.path.join(ref_root, "eplb")):
+    from ep_balance_b200.baselines.reference_install import use_reference  # path lookup only
+
+    ref_root = use_reference(ROOT)
+    if ref_root is None:
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref is not installed (pip --target install of the reference)"}))
         return
-    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(ref_root, "_torch_ext"))
-    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0+PTX")
-    sys.path.insert(0, ref_root)
     import torch
     import torch.distributed as dist
     import torch.nn.functional as F

@@ -131,12 +131,11 @@ def measure(ranks: int, experts: int, domains: int, extra: int, skew: float, imp
     n_slot = -(-experts // ranks) + extra
     wb, s_tok = 3 * 7168 * 2048 * 2, 7168 * 2
     if impl == "reference":
-        root = "/root/repo/baseline/_ref" if os.path.isdir("/root/repo/baseline/_ref/eplb") else os.path.join(
-            os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "baseline", "_ref")
-        os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(root, "_torch_ext"))
-        os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0+PTX")
-        if root not in sys.path:
-            sys.path.insert(0, root)
+        from ..baselines.reference_install import use_reference
+
+        repo_root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        if use_reference(repo_root) is None:
+            raise SystemExit("the reference is not installed under baseline/_ref")
         import eplb
 
         topo = eplb.Topology.from_nvlink_rdma(domains, ranks // domains, device=dev)

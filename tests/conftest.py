@@ -14,7 +14,7 @@ def pytest_configure(config):
 
 def reference_package():
     """Import the upstream package for differential tests; None when it is not on this machine."""
-    for cand in (os.path.join(ROOT, "baseline", "_ref"), "/root/reference"):
+    for cand in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("EPLB_REFERENCE_DIR", "")):
         if os.path.isdir(os.path.join(cand, "eplb")):
             if cand not in sys.path:
                 sys.path.append(cand)

@@ -11,16 +11,13 @@ import torch
 pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-REF = os.path.join(ROOT, "baseline", "_ref")
 
 
 def _reference():
-    if not os.path.isdir(os.path.join(REF, "eplb")):
+    from ep_balance_b200.baselines.reference_install import use_reference
+
+    if use_reference(ROOT) is None:
         pytest.skip("reference is not installed under baseline/_ref")
-    os.environ.setdefault("TORCH_EXTENSIONS_DIR", os.path.join(REF, "_torch_ext"))
-    os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0+PTX")
-    if REF not in sys.path:
-        sys.path.insert(0, REF)
     import eplb
 
     return eplb
