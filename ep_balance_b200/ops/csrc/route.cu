@@ -403,7 +403,12 @@ cudaError_t launch_weight_pull(const WeightPullArgs& a, cudaStream_t stream) {
   const int replica_slots = a.n_slot - a.home_cap;
   if (replica_slots <= 0) return cudaSuccess;
   if (a.elems_per_slot % 8 != 0) return cudaErrorInvalidValue;
-  dim3 grid(64, replica_slots);
+  // about two waves of CTAs over all replica slots: a pull of one or two experts must still keep
+  // enough 16-byte peer loads in flight to fill NVLink
+  int gx = (2 * 148 + replica_slots - 1) / replica_slots;
+  if (gx < 32) gx = 32;
+  if (gx > 160) gx = 160;
+  dim3 grid(gx, replica_slots);
   weight_pull_kernel<<<grid, 512, 0, stream>>>(a);
   return cudaGetLastError();
 }
