@@ -121,19 +121,21 @@ def main(argv=None):
                 if nb > a.tokens:
                     continue
                 xb = x[:nb].contiguous()
-                y8 = model(xb)
-                for b in model.blocks:
-                    b.moe._fp8_ready = False
-                y16 = model(xb)
-                for b in model.blocks:
-                    b.moe._fp8_ready = True
+                # numerical error of the fp8 expert GEMMs: first layer's routed output for the same input and the
+                # same routing.  (Whole-stack outputs differ by more: a few per cent of noise flips near-tied
+                # top-k choices in later layers, which is a property of discrete routing, not of the kernels.)
+                moe0, h0 = model.blocks[0].moe, model.blocks[0].norm(xb)
+                y8 = moe0(h0)
+                moe0._fp8_ready = False
+                y16 = moe0(h0)
+                moe0._fp8_ready = True
                 err[str(nb)] = float((y8.float() - y16.float()).norm() / y16.float().norm().clamp_min(1e-12))
                 infer8[str(nb)] = timed(lambda: model(xb), a.steps)
                 if a.graphs:
                     replay, _ = graphed(xb)
                     infer8[f"{nb}_graph"] = timed(replay, a.steps)
         out["inference_forward_fp8_ms"] = infer8
-        out["fp8_vs_bf16_relative_error"] = err
+        out["fp8_vs_bf16_layer_relative_error"] = err
     model.check_status()
     if rank == 0:
         print(json.dumps(out), flush=True)
