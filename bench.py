@@ -205,8 +205,6 @@ def run_ours(args):
     opt = FusedAdamW(layer.parameters(), lr=1e-5)
     batches = host_batches(args.tokens, CFG["hidden"], rank)
     dev_batches = [b.to(dev) for b in batches]
-    loss_host = torch.zeros(2, dtype=torch.float32).pin_memory()
-    loss_ready = [torch.cuda.Event() for _ in range(2)]
     losses_read = []
 
     def train_step(x):
@@ -221,25 +219,34 @@ def run_ours(args):
         x = dev_batches[i % len(dev_batches)].detach().requires_grad_(True)
         train_step(x)
 
-    # End-to-end loop: the input of step i+1 is copied host->device on a side stream while step i
-    # computes (two device staging buffers).  The loss of every step is copied device->host into
-    # pinned memory asynchronously and read by the host one step later, after step i+1 has been
-    # enqueued, so the GPU never idles while the host launches; the last loss is read before the
-    # closing event of the timed loop.
+    # End-to-end loop.  Inputs: the batch of step i+1 is copied host->device on a side stream while step i
+    # computes (ring of DEPTH device staging buffers).  Results: the loss of every step is copied
+    # device->host into pinned memory asynchronously and read by the host LAG steps later, so the host can
+    # enqueue ahead of the GPU (with device-side cross-rank barriers in every step, a host that waits for
+    # its own GPU each step stalls every other rank too).  The losses still outstanding at the end are
+    # read before the closing event of the timed loop.
+    DEPTH, LAG = 3, 2
     copy_stream = torch.cuda.Stream(device=dev)
-    staging = [torch.empty_like(dev_batches[0]) for _ in range(2)]
-    ready = [torch.cuda.Event() for _ in range(2)]
-    consumed = [torch.cuda.Event() for _ in range(2)]
+    staging = [torch.empty_like(dev_batches[0]) for _ in range(DEPTH)]
+    ready = [torch.cuda.Event() for _ in range(DEPTH)]
+    consumed = [torch.cuda.Event() for _ in range(DEPTH)]
+    loss_host = torch.zeros(DEPTH, dtype=torch.float32).pin_memory()
+    loss_ready = [torch.cuda.Event() for _ in range(DEPTH)]
+    pending = []
 
     def prefetch(i):
-        slot = i % 2
+        slot = i % DEPTH
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(consumed[slot])
             staging[slot].copy_(batches[i % len(batches)], non_blocking=True)
             ready[slot].record(copy_stream)
 
+    def read_loss(i):
+        loss_ready[i % DEPTH].synchronize()
+        losses_read.append(float(loss_host[i % DEPTH]))
+
     def step_e2e(i):
-        slot = i % 2
+        slot = i % DEPTH
         if i == 0:
             prefetch(0)
         prefetch(i + 1)
@@ -249,20 +256,13 @@ def run_ours(args):
         consumed[slot].record()
         loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)  # device->host, 4 bytes
         loss_ready[slot].record()
-        if pending["step"] is not None:
-            read_loss(pending["step"])
-        pending["step"] = i
-
-    pending = {"step": None}
-
-    def read_loss(i):
-        loss_ready[i % 2].synchronize()
-        losses_read.append(float(loss_host[i % 2]))
+        pending.append(i)
+        while len(pending) > LAG:
+            read_loss(pending.pop(0))
 
     def finish_e2e():
-        if pending["step"] is not None:
-            read_loss(pending["step"])
-            pending["step"] = None
+        while pending:
+            read_loss(pending.pop(0))
 
     for ev in consumed:
         ev.record()
@@ -310,8 +310,8 @@ def run_ours(args):
     loads = layer.rank_loads().float()
     extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],
              "gemm_ctas": args.gemm_ctas,
-             "e2e_loop": "input H2D prefetched on a side stream (double-buffered); loss D2H copied asynchronously and "
-                         "read by the host one step later, the last one before the closing event",
+             "e2e_loop": "input H2D prefetched on a side stream (ring of 3 staging buffers); loss D2H copied "
+                         "asynchronously and read by the host two steps later, the outstanding ones before the closing event",
              "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return, fused AdamW"}
     if rank == 0:
         emit(args, world, "ours", ms_dev, ms_e2e, launches, clocks, batches[0].numel() * 2, 4, extra)
