@@ -94,7 +94,7 @@ class EmulatedCluster:
         for l, (idx, _), m in zip(L, routing, n):
             l.rt.route(idx.data_ptr(), m * K)
         for l, t, m in zip(L, tokens, n):
-            l.rt.dispatch_tokens(t.data_ptr(), m * K)
+            l.rt.dispatch_fp8(t.data_ptr(), m * K)
         for l in L:
             l.rt.pull_weights_fp8()
         for l in L:

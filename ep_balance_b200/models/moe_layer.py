@@ -93,6 +93,8 @@ def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
         lay.add("w2q", (w_slots, H, F), torch.uint8)
         lay.add("sfb1", (w_slots, _sf_bytes(2 * F, H)), torch.uint8)
         lay.add("sfb2", (w_slots, _sf_bytes(H, F)), torch.uint8)
+        lay.add("xq", (cap, H), torch.uint8)                      # received rows, quantised by the sender
+        lay.add("sfx", (cap // 128 * _sf_bytes(128, H),), torch.uint8)
     return lay
 
 
@@ -259,12 +261,11 @@ class FusedMoE(nn.Module):
         if cfg.fp8_inference:
             if H % 128 or F % 128:
                 raise ValueError("fp8_inference needs hidden and ffn to be multiples of 128")
-            symm_names += ["w1q", "w2q", "sfb1", "sfb2"]
-            table_names += [(n, n + "_ptrs") for n in ("w1q", "w2q", "sfb1", "sfb2")]
+            symm_names += ["w1q", "w2q", "sfb1", "sfb2", "xq", "sfx"]
+            table_names += [(n, n + "_ptrs") for n in ("w1q", "w2q", "sfb1", "sfb2", "xq", "sfx")]
             cap = self.row_capacity
             u8 = dict(dtype=torch.uint8, device=dev)
-            self._fp8_local = {"xq": torch.zeros((cap, H), **u8), "sfx": torch.zeros(cap // 128 * _sf_bytes(128, H), **u8),
-                               "actq": torch.zeros((cap, F), **u8), "sfact": torch.zeros(cap // 128 * _sf_bytes(128, F), **u8)}
+            self._fp8_local = {"actq": torch.zeros((cap, F), **u8), "sfact": torch.zeros(cap // 128 * _sf_bytes(128, F), **u8)}
             ptrs.update({k: v.data_ptr() for k, v in self._fp8_local.items()})
         for name in symm_names:
             ptrs[name] = heap.address(name, rank)

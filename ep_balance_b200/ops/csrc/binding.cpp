@@ -438,6 +438,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("has_fp8", &MoeRuntime::has_fp8)
       .def("quantize_own_weights", [](MoeRuntime& r) { r.quantize_own_weights(current_stream()); })
       .def("pull_weights_fp8", [](MoeRuntime& r) { r.pull_weights_fp8(current_stream()); })
+      .def("dispatch_fp8", [](MoeRuntime& r, uint64_t tok, int u) { r.dispatch_fp8(cp(tok), u, current_stream()); })
       .def("gemm1_fp8", [](MoeRuntime& r) { r.gemm1_fp8(current_stream()); })
       .def("act_fp8", [](MoeRuntime& r) { r.act_fp8(current_stream()); })
       .def("gemm2_fp8", [](MoeRuntime& r) { r.gemm2_fp8(current_stream()); })

@@ -457,6 +457,51 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
     for (int kb = kblocks; kb < kgroups * 4; ++kb) chunk_row[(size_t)(kb >> 2) * 512 + chunk_byte(warp & 127, kb)] = 127;
 }
 
+// One warp per routed unit.  A 128-wide block is held by 16 lanes (8 values each); the block maximum is a
+// 4-step shuffle inside the half-warp.  Stores go to the destination rank's buffers (peer memory).
+__global__ void __launch_bounds__(256) dispatch_fp8_kernel(DispatchFp8Args a) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
+  const int u = blockIdx.x * wpb + warp;
+  if (u >= a.num_units) return;
+  const int dst = a.unit_dst[u], row = a.unit_row[u];
+  if (dst < 0 || row >= a.row_capacity) return;
+  const int vec_per_row = a.H / 8;
+  const int kgroups = (a.H / 128 + 3) / 4;
+  const uint4* src = reinterpret_cast<const uint4*>(a.rows) + (size_t)(u / a.topk) * vec_per_row;
+  uint8_t* qrow = a.xq_ptrs[dst] + (size_t)row * a.H;
+  uint8_t* chunk_row = a.sfx_ptrs[dst] + (size_t)(row >> 7) * kgroups * 512;
+  for (int v = lane; v < vec_per_row + (32 - vec_per_row % 32) % 32; v += 32) {
+    const bool have = v < vec_per_row;
+    const uint4 raw = have ? src[v] : make_uint4(0, 0, 0, 0);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float f[8];
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 p = __bfloat1622float2(h[j]);
+      f[2 * j] = p.x;
+      f[2 * j + 1] = p.y;
+      amax = fmaxf(amax, fmaxf(fabsf(p.x), fabsf(p.y)));
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!have) continue;
+    const int e = scale_exponent(amax);
+    const float inv = exp2_int(-e);
+    uint32_t out[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const unsigned lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j] * inv, f[4 * j + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+      const unsigned hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j + 2] * inv, f[4 * j + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+      out[j] = (lo & 0xffffu) | (hi << 16);
+    }
+    *reinterpret_cast<uint2*>(qrow + (size_t)v * 8) = make_uint2(out[0], out[1]);
+    const int kb = v >> 4;
+    if ((lane & 15) == 0) chunk_row[(size_t)(kb >> 2) * 512 + chunk_byte(row & 127, kb)] = (uint8_t)(e + 127);
+  }
+  if (lane == 0 && a.meta_ptrs != nullptr) a.meta_ptrs[dst][row] = make_int2(a.me, u);
+}
+
 // SwiGLU + quantisation in one pass: h [rows, 2F] (gate columns, then up columns) ->
 // act = silu(gate) * up as e4m3 [rows, F] with 1 x 128 scales (and, optionally, as bf16 too).
 __global__ void __launch_bounds__(256) swiglu_quantize_kernel(const __nv_bfloat16* __restrict__ h, uint8_t* __restrict__ q,
@@ -613,6 +658,14 @@ cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int ro
   const int blocks = (rows + 7) / 8;
   quantize_rows_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const __nv_bfloat16*>(x), q, sfa, rows, K,
                                                    groups ? *groups : RowGroups{nullptr, nullptr, nullptr, 0});
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dispatch_fp8(const DispatchFp8Args& a, cudaStream_t stream) {
+  if (a.H % 128 != 0) return cudaErrorInvalidValue;
+  if (a.num_units <= 0) return cudaSuccess;
+  const int wpb = 8;
+  dispatch_fp8_kernel<<<(a.num_units + wpb - 1) / wpb, wpb * 32, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

@@ -64,6 +64,21 @@ cudaError_t launch_quantize_rows(const void* x, uint8_t* q, uint8_t* sfa, int ro
 // `act` (bf16 [rows, F], may be null) also receives the unquantised activation.
 cudaError_t launch_swiglu_quantize(const void* h, uint8_t* q, uint8_t* sfa, void* act, int rows, int F,
                                    const RowGroups* groups, cudaStream_t stream);
+// Dispatch fused with the 1 x 128 quantisation: every routed unit's token row is quantised in registers and
+// stored as e4m3 bytes (plus its scale bytes) straight into the destination rank's operand buffer, so half
+// the bytes of a bf16 dispatch cross NVLink and no separate quantisation pass runs on the receiver.
+struct DispatchFp8Args {
+  const void* rows;             // bf16 [num_tokens, H]
+  int num_units, topk, H, R, me;
+  const int32_t* unit_dst;      // [U]
+  const int32_t* unit_row;      // [U]
+  uint8_t* const* xq_ptrs;      // R peers: e4m3 [row_capacity, H]
+  uint8_t* const* sfx_ptrs;     // R peers: scale chunks [row_capacity / 128][kgroups][512]
+  int2* const* meta_ptrs;       // R peers: {src rank, unit} per row
+  int row_capacity;
+};
+cudaError_t launch_dispatch_fp8(const DispatchFp8Args& a, cudaStream_t stream);
+
 // bf16 [slots, N, K] -> e4m3 + 128 x 128 scales in chunk layout.  N % 128 == 0, K % 128 == 0.
 cudaError_t launch_quantize_weights(const void* w, uint8_t* q, uint8_t* sfb, int slots, int N, int K,
                                     cudaStream_t stream);

@@ -104,7 +104,8 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
   // optional block-scaled fp8 forward
   if (ptr<void>("w1q", false) != nullptr) {
     if (c.H % 128 || c.F % 128) throw std::runtime_error("MoeRuntime: the fp8 path needs H % 128 == 0 and F % 128 == 0");
-    for (const char* name : {"w2q", "sfb1", "sfb2", "xq", "sfx", "actq", "sfact", "w1q_ptrs", "w2q_ptrs", "sfb1_ptrs", "sfb2_ptrs"})
+    for (const char* name : {"w2q", "sfb1", "sfb2", "xq", "sfx", "actq", "sfact", "w1q_ptrs", "w2q_ptrs", "sfb1_ptrs", "sfb2_ptrs",
+                             "xq_ptrs", "sfx_ptrs"})
       ptr<void>(name);
     if (!make_tmap_fp8_2d(&tm_xq_, ptr<void>("xq"), T, H) || !make_tmap_fp8_2d(&tm_actq_, ptr<void>("actq"), T, F) ||
         !make_tmap_fp8_3d(&tm_w1q_, ptr<void>("w1q"), S, 2 * F, H) || !make_tmap_fp8_3d(&tm_w2q_, ptr<void>("w2q"), S, H, F))
@@ -267,11 +268,24 @@ void MoeRuntime::gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int
   check(launch_grouped_gemm_fp8(a, b, g, cfg_.num_sms, stream), "grouped_gemm_fp8");
 }
 
+void MoeRuntime::dispatch_fp8(const void* tokens, int num_units, cudaStream_t stream) {
+  DispatchFp8Args a{};
+  a.rows = tokens;
+  a.num_units = num_units;
+  a.topk = cfg_.topk;
+  a.H = cfg_.H;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.unit_dst = ptr<const int32_t>("unit_dst");
+  a.unit_row = ptr<const int32_t>("unit_row");
+  a.xq_ptrs = ptr<uint8_t* const>("xq_ptrs");
+  a.sfx_ptrs = ptr<uint8_t* const>("sfx_ptrs");
+  a.meta_ptrs = ptr<int2* const>("meta_ptrs");
+  a.row_capacity = cfg_.row_capacity;
+  check(launch_dispatch_fp8(a, stream), "dispatch_fp8");
+}
+
 void MoeRuntime::gemm1_fp8(cudaStream_t stream) {
-  const RowGroups groups{tables_.group_off, tables_.group_rows, tables_.totals, cfg_.w_slots};
-  check(launch_quantize_rows(ptr<void>("xbuf"), ptr<uint8_t>("xq"), ptr<uint8_t>("sfx"), cfg_.row_capacity, cfg_.H,
-                             &groups, stream),
-        "quantize_rows(x)");
   gemm_fp8(tm_xq_, tm_w1q_, 2 * cfg_.F, cfg_.H, ptr<uint8_t>("sfx"), ptr<uint8_t>("sfb1"), ptr<void>("hbuf"), nullptr,
            nullptr, stream);
 }
@@ -293,7 +307,7 @@ void MoeRuntime::forward_fp8(const void* tokens, const int64_t* topk_idx, const 
   publish(topk_idx, U, stream);
   solve(stream);
   route(topk_idx, U, stream);
-  dispatch_tokens(tokens, U, stream, /*zero_pad=*/false);  // outputs of padding rows are never stored
+  dispatch_fp8(tokens, U, stream);  // rows cross NVLink as e4m3 + scales; padding rows stay stale (never stored)
   pull_weights_fp8(stream);
   barrier(1, stream);
   gemm1_fp8(stream);

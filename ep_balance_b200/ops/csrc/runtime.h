@@ -63,7 +63,8 @@ class MoeRuntime {
   bool has_fp8() const { return fp8_; }
   void quantize_own_weights(cudaStream_t stream);   // bf16 home slots -> e4m3 + 128 x 128 scales
   void pull_weights_fp8(cudaStream_t stream);       // replicas pull e4m3 bytes and scale chunks: half the bytes of bf16
-  void gemm1_fp8(cudaStream_t stream);              // quantise received rows (1 x 128), h = x W1^T
+  void dispatch_fp8(const void* tokens, int num_units, cudaStream_t stream);  // dispatch fused with the 1 x 128 quantisation
+  void gemm1_fp8(cudaStream_t stream);              // h = x W1^T on the quantised rows
   void act_fp8(cudaStream_t stream);                // SwiGLU + quantise
   void gemm2_fp8(cudaStream_t stream);              // y = act W2^T, rows scattered to their sources
   void forward_fp8(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out, int num_tokens,
