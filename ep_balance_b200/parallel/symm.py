@@ -23,6 +23,8 @@ import torch
 import torch.distributed as dist
 
 ALIGN = 256
+GUARD = 256          # bytes of canary after every region
+GUARD_BYTE = 0xA5
 
 
 def _round_up(n: int, a: int) -> int:
@@ -34,6 +36,7 @@ class HeapLayout:
 
     def __init__(self) -> None:
         self.regions: Dict[str, Tuple[int, Tuple[int, ...], torch.dtype]] = {}
+        self.guards: Dict[str, int] = {}
         self.nbytes = 0
 
     def add(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> None:
@@ -43,7 +46,9 @@ class HeapLayout:
         for s in shape:
             numel *= int(s)
         self.regions[name] = (self.nbytes, tuple(int(s) for s in shape), dtype)
-        self.nbytes = _round_up(self.nbytes + numel * torch.empty((), dtype=dtype).element_size(), ALIGN)
+        end = _round_up(self.nbytes + numel * torch.empty((), dtype=dtype).element_size(), ALIGN)
+        self.guards[name] = end          # a canary of GUARD bytes sits between this region and the next
+        self.nbytes = end + GUARD
 
 
 class SymmetricHeap:
@@ -88,6 +93,12 @@ class SymmetricHeap:
                 raise ValueError(f"unknown symmetric heap backend {self.backend!r}")
         self._flat = [self.ext.tensor_from_ptr(b, nbytes, dev_index) for b in self.bases]
         self._ptr_tables: Dict[str, torch.Tensor] = {}
+        for r in ([self.rank] if self.backend == "ipc" else range(self.world)):   # every rank paints its own heap
+            for off in layout.guards.values():
+                self._flat[r][off:off + GUARD].fill_(GUARD_BYTE)
+        if self.backend == "ipc":
+            torch.cuda.synchronize(dev_index)
+            dist.barrier(group=group)
 
     # ---- views ---------------------------------------------------------------
     def tensor(self, name: str, rank: Optional[int] = None) -> torch.Tensor:
@@ -113,6 +124,16 @@ class SymmetricHeap:
                              device=self.device)
             self._ptr_tables[key] = t
         return t
+
+    def damaged_guards(self, rank: Optional[int] = None) -> List[str]:
+        """Names of the regions whose trailing canary was overwritten on ``rank`` (default: this rank): a kernel
+        wrote past the end of that region.  One device-to-host read; for tests and debugging."""
+        r = self.rank if rank is None else int(rank)
+        bad = []
+        for name, off in self.layout.guards.items():
+            if not bool((self._flat[r][off:off + GUARD] == GUARD_BYTE).all()):
+                bad.append(name)
+        return bad
 
     def close(self) -> None:
         self._flat = []

@@ -182,3 +182,28 @@ def test_router_logits_from_bf16_tokens_match_fp32_matmul():
     assert _rel(out, ref) < 2e-6            # fp32-grade, far below bf16's 4e-3
     assert _rel(w.grad, wr.grad) < 2e-6
     assert _rel(x.grad, xr.grad) < 1e-2     # token gradient is bf16
+
+
+def test_no_kernel_writes_past_a_symmetric_region():
+    """Canary bytes behind every symmetric region survive a full step of four emulated ranks (and the check
+    itself notices a deliberate host-side overwrite)."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+
+    torch.manual_seed(4)
+    cfg = MoEConfig(hidden=256, ffn=256, num_experts=8, top_k=2, max_tokens=256, extra_slots=2, capacity_factor=4.0,
+                    fp8_inference=True)
+    cl = EmulatedCluster(cfg, world=4)
+    for l in cl.layers:
+        l.quantize_weights()
+    tokens = [torch.randn(256, 256, device="cuda").bfloat16() for _ in range(4)]
+    cl.step(tokens, [torch.randn_like(t) for t in tokens])
+    cl.forward_fp8(tokens)
+    torch.cuda.synchronize()
+    for r in range(4):
+        assert cl.heap.damaged_guards(r) == []
+    cl.heap.tensor("omega", 2).view(-1)[-1:].data_ptr()      # region end
+    flat = cl.heap._flat[2]
+    off = cl.heap.layout.guards["ybuf"]
+    flat[off + 3] = 0                                        # host-side: simulate an overrun of `ybuf`
+    assert cl.heap.damaged_guards(2) == ["ybuf"]
