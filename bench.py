@@ -295,6 +295,9 @@ def run_ours(args):
             layer.rt.enable_timing(True)
             acc = {}
             for i in range(5):
+                torch.cuda.synchronize()
+                dist.barrier()  # start the step together: otherwise `solve` also counts the host skew between ranks
+                torch.cuda.synchronize()
                 step_device(i)
                 for name, ms in layer.rt.phase_times():
                     acc.setdefault(name, []).append(ms)
