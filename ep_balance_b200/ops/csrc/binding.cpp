@@ -308,7 +308,7 @@ void quantize_weights(torch::Tensor w, torch::Tensor q, torch::Tensor sfb) {
 }
 void grouped_gemm_fp8(torch::Tensor aq, torch::Tensor sfa, torch::Tensor bq, torch::Tensor sfb, torch::Tensor out,
                       torch::Tensor group_off, torch::Tensor group_rows, torch::Tensor group_wslot, torch::Tensor totals,
-                      torch::Tensor status, int64_t num_sms) {
+                      torch::Tensor status, int64_t num_sms, int64_t ctas) {
   const c10::cuda::CUDAGuard guard(aq.device());
   TORCH_CHECK(aq.dim() == 2 && bq.dim() == 3 && out.dim() == 2, "aq [T, K], bq [slots, N, K], out [T, N]");
   const int64_t T = aq.size(0), K = aq.size(1), N = bq.size(1);
@@ -332,8 +332,18 @@ void grouped_gemm_fp8(torch::Tensor aq, torch::Tensor sfa, torch::Tensor bq, tor
   g.status = dptr<int>(status, "status", torch::kInt32);
   CUtensorMap tmA, tmB;
   TORCH_CHECK(epb::make_tmap_fp8_2d(&tmA, dptr<uint8_t>(aq, "aq", torch::kUInt8), T, K) &&
-                  epb::make_tmap_fp8_3d(&tmB, dptr<uint8_t>(bq, "bq", torch::kUInt8), bq.size(0), N, K),
+                  epb::make_tmap_fp8_3d(&tmB, dptr<uint8_t>(bq, "bq", torch::kUInt8), bq.size(0), N, K, ctas == 2 ? 64 : 128),
               "cuTensorMapEncodeTiled failed");
+  if (ctas == 2) {
+    TORCH_CHECK(T % 256 == 0, "the CTA-pair kernel needs T % 256 == 0 and groups that start on multiples of 256 rows");
+    CUtensorMap tmSFA, tmSFB;
+    TORCH_CHECK(epb::make_tmap_sf(&tmSFA, g.sfa, (uint64_t)(sfa.numel() / 512)) &&
+                    epb::make_tmap_sf(&tmSFB, g.sfb, (uint64_t)(sfb.numel() / 512)),
+                "cuTensorMapEncodeTiled (scale chunks) failed");
+    cuda_check(epb::launch_grouped_gemm_fp8_pair(tmA, tmB, tmSFA, tmSFB, g, (int)num_sms, current_stream()),
+               "launch_grouped_gemm_fp8_pair");
+    return;
+  }
   cuda_check(epb::launch_grouped_gemm_fp8(tmA, tmB, g, (int)num_sms, current_stream()), "launch_grouped_gemm_fp8");
 }
 

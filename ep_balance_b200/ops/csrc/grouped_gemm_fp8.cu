@@ -400,6 +400,288 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
   }
 }
 
+// ================================================================ CTA-pair variant (cta_group::2)
+// A thread-block cluster of two SMs computes a 256 x 128 tile: each CTA stages its own 128 rows of A, its
+// own 64 of the 128 weight rows (B) and the scale chunks it needs (its rows' SFA chunk and the whole SFB
+// chunk), so per MMA a CTA reads 6 KB of shared memory instead of 8 KB and the tensor pipe is no longer fed at
+// the shared-memory limit.  Every load is a plain TMA load (no multicast) that completes on the barrier of
+// the pair's even CTA; that CTA issues the scale copies and the MMAs for both.
+namespace pair {
+
+constexpr int STAGES = 6;
+constexpr int B_HALF = 64;                                   // weight rows staged per CTA
+constexpr int A_BYTES = BM * BK, B_BYTES = B_HALF * BK, TILE_BYTES = A_BYTES + B_BYTES;   // 16 KB + 8 KB
+constexpr int TILE_M = 2 * BM;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;               // clears the CTA-rank bit of a shared::cluster address
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(saddr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tma_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar) & kPeerBitMask), "r"(c0), "r"(c1), "r"(c2)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void commit2(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_cp_sf2(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t sfa,
+                                      uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}\n"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+      : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                             const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
+                             Fp8GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* tiles = smem;
+  uint8_t* sf_tiles = smem + STAGES * TILE_BYTES;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_tiles + STAGES * SF_BYTES);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* acc_full = empty_bar + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  int* abort_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  int* tile_prefix = abort_flag + 1;
+  uint4* stage_tiles = reinterpret_cast<uint4*>(sf_tiles + STAGES * SF_BYTES + kCtrlBytes);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta_rank = (int)cluster_ctarank();
+  const int tile_first = blockIdx.x / 2, tile_stride = gridDim.x / 2;
+  int n_groups = args.totals[1];
+  if (n_groups > args.n_groups_cap) n_groups = args.n_groups_cap;
+  const int n_tiles_n = args.N / BN;
+  const int kblocks = args.K / BK;
+  const int kgroups = (kblocks + 3) / 4;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 16);   // 8 epilogue warps of each CTA
+    }
+    *abort_flag = 0;
+    int acc = 0;
+    tile_prefix[0] = 0;
+    for (int g = 0; g < n_groups; ++g) {
+      acc += ceil_div(args.group_rows[g], TILE_M) * n_tiles_n;
+      tile_prefix[g + 1] = acc;
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc2(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int total_tiles = tile_prefix[n_groups];
+  volatile int* abort_v = abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer (both CTAs)
+    int stage = 0;
+    uint32_t phase = 0;
+    Tile t;
+    for (int ti = tile_first; ti < total_tiles; ti += tile_stride) {
+      int go = 1;
+      if (lane == 0) {
+        if (*abort_v || !find_tile(args, n_groups, n_tiles_n, tile_prefix, ti, t)) go = 0;
+        if (go) {
+          const int row_first = t.row0 + t.mt * TILE_M + cta_rank * BM;
+          const int sfa_chunk = (row_first / BM) * kgroups;
+          const int sfb_chunk = (t.wslot * n_tiles_n + t.nt) * kgroups;
+          for (int kb = 0; kb < kblocks; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v, args.status, 21)) {
+              go = 0;
+              break;
+            }
+            uint8_t* sA = tiles + stage * TILE_BYTES;
+            uint8_t* sB = sA + A_BYTES;
+            uint64_t* fb = &full_bar[stage];
+            const bool with_sf = (kb & 3) == 0;
+            if (cta_rank == 0) mbar_expect_tx(fb, 2 * (TILE_BYTES + (with_sf ? SF_BYTES : 0)));
+            tma_2d(sA, &tmA, fb, kb * BK, row_first);
+            tma_3d(sB, &tmB, fb, kb * BK, t.nt * BN + cta_rank * B_HALF, t.wslot);
+            if (with_sf) {
+              uint8_t* sS = sf_tiles + stage * SF_BYTES;
+              tma_2d(sS, &tmSFA, fb, 0, sfa_chunk + (kb >> 2));
+              tma_2d(sS + 512, &tmSFB, fb, 0, sfb_chunk + (kb >> 2));
+            }
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+        }
+      }
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) break;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ scale copies + MMA issue (even CTA only)
+    if (lane == 0 && cta_rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int local = 0;
+      uint32_t sf_buf = 0;
+      Tile t;
+      for (int ti = tile_first; ti < total_tiles && !*abort_v; ti += tile_stride, ++local) {
+        if (!find_tile(args, n_groups, n_tiles_n, tile_prefix, ti, t)) break;
+        const int buf = local & 1;
+        if (!mbar_wait(&acc_empty[buf], acc_phase[buf] ^ 1u, abort_v, args.status, 22)) break;
+        acc_phase[buf] ^= 1u;
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        bool failed = false;
+        uint32_t sfa_col = 0, sfb_col = 0;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_v, args.status, 23)) {
+            failed = true;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(tiles + stage * TILE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+          if ((kb & 3) == 0) {
+            const uint32_t sS = smem_u32(sf_tiles + stage * SF_BYTES);
+            sfa_col = tmem_base + kSfCol + sf_buf * 8;
+            sfb_col = sfa_col + 4;
+            tmem_cp_sf2(sfa_col, make_desc_sf(sS));
+            tmem_cp_sf2(sfb_col, make_desc_sf(sS + 512));
+            sf_buf ^= 1u;
+          }
+          const uint32_t id = (uint32_t)(kb & 3);
+          const uint32_t idesc = make_idesc_scaled(BN, TILE_M, id, id);
+          const uint64_t da = make_desc_sw128(sA), db = make_desc_sw128(sB);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma2(tmem_d, da + (uint64_t)(k * (UMMA_K >> 4)), db + (uint64_t)(k * (UMMA_K >> 4)), idesc, sfa_col, sfb_col,
+                  (kb | k) ? 1u : 0u);
+          const uint32_t eb = smem_u32(&empty_bar[stage]);
+          commit2(eb);
+          commit2(map_to_cta(eb, 1));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (failed) break;
+        const uint32_t ab = smem_u32(&acc_full[buf]);
+        commit2(ab);
+        commit2(map_to_cta(ab, 1));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..9 of both CTAs)
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint4* stg = stage_tiles + (warp - 2) * (kStageWarpBytes / 16);
+    uint32_t acc_phase[2] = {0, 0};
+    int local = 0;
+    Tile t;
+    char* out0 = reinterpret_cast<char*>(args.out);
+    for (int ti = tile_first; ti < total_tiles && !*abort_v; ti += tile_stride, ++local) {
+      if (!find_tile(args, n_groups, n_tiles_n, tile_prefix, ti, t)) break;
+      const int buf = local & 1;
+      if (!mbar_wait(&acc_full[buf], acc_phase[buf], abort_v, args.status, 24)) break;
+      acc_phase[buf] ^= 1u;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 64);
+      const int row_in_group = t.mt * TILE_M + cta_rank * BM + quarter * 32 + lane;
+      const size_t row = (size_t)t.row0 + row_in_group;
+      char* orow = nullptr;
+      if (row_in_group < t.rows && row < (size_t)args.row_capacity) {
+        if (args.meta != nullptr) {
+          const int2 mt = args.meta[row];
+          char* base = args.out_ptrs ? reinterpret_cast<char*>(args.out_ptrs[mt.x]) : out0;
+          orow = base + (size_t)mt.y * args.N * 2;
+        } else {
+          orow = out0 + row * (size_t)args.N * 2;
+        }
+      }
+      uint32_t v0[32], v1[32];
+      tmem_ld32(taddr, v0);
+      tmem_ld32(taddr + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
+      uint4 p0[4], p1[4];
+      pack_row(v0, p0);
+      pack_row(v1, p1);
+      __syncwarp();
+      wide_store_half(stg, lane, p0, 0);
+      wide_store_half(stg, lane, p1, 1);
+      __syncwarp();
+      wide_flush(stg, lane, orow, (t.nt * BN + half * 64) * 2);
+    }
+  }
+
+  __syncthreads();
+  if (*abort_v && threadIdx.x == 0) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves while the other may still signal it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, TMEM_COLS);
+  }
+}
+
+constexpr size_t kSmemBytes = STAGES * TILE_BYTES + STAGES * SF_BYTES + 1024 + kCtrlBytes + 8 * kStageWarpBytes;
+static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+
+}  // namespace pair
+
 constexpr size_t kSmemBytes = STAGES * TILE_BYTES + STAGES * SF_BYTES + 1024 + kCtrlBytes + 8 * kStageWarpBytes;
 static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
 
@@ -625,16 +907,55 @@ bool make_tmap_fp8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-bool make_tmap_fp8_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols) {
+bool make_tmap_fp8_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols,
+                      uint32_t box_rows) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   cuuint64_t dims[3] = {cols, rows, slots};
   cuuint64_t strides[2] = {cols, rows * cols};
-  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t box[3] = {128, box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_tmap_sf(CUtensorMap* out, const void* base, uint64_t chunks) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr || chunks == 0) return false;
+  cuuint64_t dims[2] = {128, chunks};          // one 512-byte chunk = 128 x int32
+  cuuint64_t strides[1] = {512};
+  cuuint32_t box[2] = {128, 1};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA,
+                                         const CUtensorMap& tmSFB, const Fp8GemmArgs& args, int num_sms,
+                                         cudaStream_t stream) {
+  if (args.n_groups_cap > MAX_GROUPS || args.N % BN != 0 || args.K % BK != 0 || args.K <= 0) return cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(pair::grouped_gemm_fp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)pair::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(num_sms / 2 * 2));
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = pair::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, pair::grouped_gemm_fp8_pair_kernel, tmA, tmB, tmSFA, tmSFB, args);
 }
 
 cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmArgs& args,

@@ -42,7 +42,10 @@ struct Fp8GemmArgs {
 
 // Tensor maps over the e4m3 bytes: A [rows, K], B [slots, N, K]; boxes of 128 x 128 bytes, 128-byte swizzle.
 bool make_tmap_fp8_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols);
-bool make_tmap_fp8_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols);
+bool make_tmap_fp8_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t rows, uint64_t cols,
+                      uint32_t box_rows = 128);
+// Scale chunks as a [chunks, 128] int32 tensor (one 512-byte chunk per row, no swizzle).
+bool make_tmap_sf(CUtensorMap* out, const void* base, uint64_t chunks);
 
 cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmArgs& args,
                                     int num_sms, cudaStream_t stream);
@@ -55,6 +58,12 @@ struct RowGroups {
   const int32_t* totals;
   int n_groups_cap;
 };
+
+// CTA-pair variant (thread-block cluster of two SMs, 256 x 128 tiles, cta_group::2): groups must start on
+// multiples of 256 rows; `tmB` must have box_rows = 64; scale chunks are fetched through `tmSFA` / `tmSFB`.
+cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA,
+                                         const CUtensorMap& tmSFB, const Fp8GemmArgs& args, int num_sms,
+                                         cudaStream_t stream);
 
 // bf16 [rows, K] -> e4m3 [rows, K] + 1 x 128 scales in chunk layout.  rows % 128 == 0, K % 128 == 0.
 // `groups` (may be null): only real rows are processed; the rest keep whatever they held.

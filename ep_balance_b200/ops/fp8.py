@@ -40,11 +40,14 @@ def quantize_weights(w: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q, sfb
 
 
-def grouped_gemm_fp8(aq, sfa, bq, sfb, out, group_off, group_rows, group_wslot, totals, status, num_sms=None) -> None:
-    """``out[rows of group g] = dequant(aq) @ dequant(bq[group_wslot[g]])^T`` (bf16 out, fp32 accumulate)."""
+def grouped_gemm_fp8(aq, sfa, bq, sfb, out, group_off, group_rows, group_wslot, totals, status, num_sms=None,
+                     ctas: int = 1) -> None:
+    """``out[rows of group g] = dequant(aq) @ dequant(bq[group_wslot[g]])^T`` (bf16 out, fp32 accumulate).
+    ``ctas=2`` runs the CTA-pair kernel (256 x 128 tiles; groups must start on multiples of 256 rows)."""
     if num_sms is None:
         num_sms = torch.cuda.get_device_properties(aq.device).multi_processor_count
-    load().grouped_gemm_fp8(aq, sfa, bq, sfb, out, group_off, group_rows, group_wslot, totals, status, int(num_sms))
+    load().grouped_gemm_fp8(aq, sfa, bq, sfb, out, group_off, group_rows, group_wslot, totals, status, int(num_sms),
+                            int(ctas))
 
 
 # ---------------------------------------------------------------------- plain PyTorch restatement

@@ -72,11 +72,14 @@ def main() -> None:
     if a.fp8:
         from . import fp8
 
-        for name, A, W, N in (("fp8_w1", x, w1, 2 * Fd), ("fp8_w2", act, w2, H)):
+        for name, A, W, N, fctas in (("fp8_w1", x, w1, 2 * Fd, 1), ("fp8_w2", act, w2, H, 1),
+                                     ("fp8_w1 pair", x, w1, 2 * Fd, 2), ("fp8_w2 pair", act, w2, H, 2)):
+            if fctas == 2 and any(o % 256 for o in off):
+                continue
             aq, sfa = fp8.quantize_rows(A)
             bq, sfb = fp8.quantize_weights(W)
             out = torch.empty(T, N, device=dev).bfloat16()
-            run = lambda: fp8.grouped_gemm_fp8(aq, sfa, bq, sfb, out, goff, grows, gws, totals, status, sms)
+            run = lambda: fp8.grouped_gemm_fp8(aq, sfa, bq, sfb, out, goff, grows, gws, totals, status, sms, fctas)
             run()
             torch.cuda.synchronize()
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -87,7 +90,9 @@ def main() -> None:
             torch.cuda.synchronize()
             ms = t0.elapsed_time(t1) / a.iters
             flops = 2 * real * A.shape[1] * N
-            print(f"{name:<7} {ms:8.4f} ms  {flops / ms * 1e-9:8.1f} TFLOP/s  status={status.tolist()[0]}")
+            print(f"{name:<12} {ms:8.4f} ms  {flops / ms * 1e-9:8.1f} TFLOP/s  status={status.tolist()[0]}")
+            if fctas == 2:
+                continue
             tq0, tq1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             tq0.record()
             for _ in range(a.iters):

@@ -32,18 +32,20 @@ def test_quantisers_round_trip_within_fp8_precision():
     assert _rel(fp8.dequantize_weights(qw, sfb), w) < 0.04
 
 
+@pytest.mark.parametrize("ctas", [1, 2])
 @pytest.mark.parametrize("K,N", [(512, 256), (1408, 2048), (2048, 2816)])
-def test_fp8_grouped_gemm_matches_dequantised_fp32(K, N):
+def test_fp8_grouped_gemm_matches_dequantised_fp32(K, N, ctas):
     from ep_balance_b200.ops import fp8
 
     torch.manual_seed(1)
     rows = [300, 0, 128, 77]
     slots = [2, 0, 1, 3]
     offs, total = [], 0
+    tile = 128 * ctas
     for r in rows:
         offs.append(total)
-        total += (r + 127) // 128 * 128
-    T = total + 128
+        total += (r + tile - 1) // tile * tile
+    T = total + tile
     x = torch.zeros(T, K, device="cuda", dtype=torch.bfloat16)
     for o, r in zip(offs, rows):
         x[o:o + r] = (torch.randn(r, K, device="cuda") * (1 + 3 * torch.rand(r, 1, device="cuda"))).bfloat16()
@@ -57,7 +59,7 @@ def test_fp8_grouped_gemm_matches_dequantised_fp32(K, N):
     gws = torch.tensor(slots, **i32)
     totals = torch.tensor([total, len(rows)], **i32)
     status = torch.zeros(4, **i32)
-    fp8.grouped_gemm_fp8(aq, sfa, bq, sfb, out, goff, grows, gws, totals, status)
+    fp8.grouped_gemm_fp8(aq, sfa, bq, sfb, out, goff, grows, gws, totals, status, ctas=ctas)
     torch.cuda.synchronize()
     assert status.tolist()[0] == 0
     xd, wd = fp8.dequantize_rows(aq, sfa), fp8.dequantize_weights(bq, sfb)
@@ -69,7 +71,7 @@ def test_fp8_grouped_gemm_matches_dequantised_fp32(K, N):
         # and against the unquantised product: fp8 rounding of both operands
         assert _rel(out[o:o + r], x[o:o + r].float() @ w[s].float().t()) < 0.06
         # rows past the group's end were not touched
-        pad_end = o + (r + 127) // 128 * 128
+        pad_end = o + (r + tile - 1) // tile * tile
         assert bool((out[o + r:pad_end] == 7.0).all())
 
 
