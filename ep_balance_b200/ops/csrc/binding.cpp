@@ -332,7 +332,8 @@ void grouped_gemm_fp8(torch::Tensor aq, torch::Tensor sfa, torch::Tensor bq, tor
   g.status = dptr<int>(status, "status", torch::kInt32);
   CUtensorMap tmA, tmB;
   TORCH_CHECK(epb::make_tmap_fp8_2d(&tmA, dptr<uint8_t>(aq, "aq", torch::kUInt8), T, K) &&
-                  epb::make_tmap_fp8_3d(&tmB, dptr<uint8_t>(bq, "bq", torch::kUInt8), bq.size(0), N, K, ctas == 2 ? 64 : 128),
+                  epb::make_tmap_fp8_3d(&tmB, dptr<uint8_t>(bq, "bq", torch::kUInt8), bq.size(0), N, K,
+                                        ctas == 2 ? (N % 256 == 0 ? 128 : 64) : 128),
               "cuTensorMapEncodeTiled failed");
   if (ctas == 2) {
     TORCH_CHECK(T % 256 == 0, "the CTA-pair kernel needs T % 256 == 0 and groups that start on multiples of 256 rows");

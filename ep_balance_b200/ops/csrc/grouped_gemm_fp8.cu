@@ -408,9 +408,17 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 // the pair's even CTA; that CTA issues the scale copies and the MMAs for both.
 namespace pair {
 
-constexpr int STAGES = 6;
-constexpr int B_HALF = 64;                                   // weight rows staged per CTA
-constexpr int A_BYTES = BM * BK, B_BYTES = B_HALF * BK, TILE_BYTES = A_BYTES + B_BYTES;   // 16 KB + 8 KB
+// kBN = 128: two accumulator buffers (epilogue overlaps the next tile).  kBN = 256: one 256-column accumulator
+// (the scale factors need the rest of tensor memory), twice the MMA work per TMA load and per barrier round.
+template <int kBN>
+struct Geo {
+  static constexpr int B_HALF = kBN / 2;                     // weight rows staged per CTA
+  static constexpr int A_BYTES = BM * BK, B_BYTES = B_HALF * BK, TILE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SF_BYTES = 512 + 512 * (kBN / 128);   // this CTA's SFA chunk + the SFB chunks of the whole tile
+  static constexpr int STAGES = kBN == 128 ? 6 : 5;
+  static constexpr int ACC_BUFS = kBN == 128 ? 2 : 1;
+  static constexpr size_t SMEM = STAGES * TILE_BYTES + STAGES * 2048 + 1024 + kCtrlBytes + 8 * kStageWarpBytes;
+};
 constexpr int TILE_M = 2 * BM;
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;               // clears the CTA-rank bit of a shared::cluster address
 
@@ -468,10 +476,15 @@ __device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t desc_a, uint64_t
       : "memory");
 }
 
+template <int kBN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                              const __grid_constant__ CUtensorMap tmSFA, const __grid_constant__ CUtensorMap tmSFB,
                              Fp8GemmArgs args) {
+  using G = Geo<kBN>;
+  constexpr int STAGES = G::STAGES, TILE_BYTES = G::TILE_BYTES, A_BYTES = G::A_BYTES, B_HALF = G::B_HALF;
+  constexpr int SF_BYTES = 2048;   // slot size; G::SF_BYTES of it are used
+  constexpr int ACC_BUFS = G::ACC_BUFS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* tiles = smem;
@@ -490,7 +503,8 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
   const int tile_first = blockIdx.x / 2, tile_stride = gridDim.x / 2;
   int n_groups = args.totals[1];
   if (n_groups > args.n_groups_cap) n_groups = args.n_groups_cap;
-  const int n_tiles_n = args.N / BN;
+  const int n_tiles_n = args.N / kBN;
+  const int n128 = args.N / 128;
   const int kblocks = args.K / BK;
   const int kgroups = (kblocks + 3) / 4;
 
@@ -534,7 +548,7 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
         if (go) {
           const int row_first = t.row0 + t.mt * TILE_M + cta_rank * BM;
           const int sfa_chunk = (row_first / BM) * kgroups;
-          const int sfb_chunk = (t.wslot * n_tiles_n + t.nt) * kgroups;
+          const int sfb_chunk = (t.wslot * n128 + t.nt * (kBN / 128)) * kgroups;
           for (int kb = 0; kb < kblocks; ++kb) {
             if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_v, args.status, 21)) {
               go = 0;
@@ -544,13 +558,15 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             uint8_t* sB = sA + A_BYTES;
             uint64_t* fb = &full_bar[stage];
             const bool with_sf = (kb & 3) == 0;
-            if (cta_rank == 0) mbar_expect_tx(fb, 2 * (TILE_BYTES + (with_sf ? SF_BYTES : 0)));
+            if (cta_rank == 0) mbar_expect_tx(fb, 2 * (TILE_BYTES + (with_sf ? G::SF_BYTES : 0)));
             tma_2d(sA, &tmA, fb, kb * BK, row_first);
-            tma_3d(sB, &tmB, fb, kb * BK, t.nt * BN + cta_rank * B_HALF, t.wslot);
+            tma_3d(sB, &tmB, fb, kb * BK, t.nt * kBN + cta_rank * B_HALF, t.wslot);
             if (with_sf) {
               uint8_t* sS = sf_tiles + stage * SF_BYTES;
               tma_2d(sS, &tmSFA, fb, 0, sfa_chunk + (kb >> 2));
-              tma_2d(sS + 512, &tmSFB, fb, 0, sfb_chunk + (kb >> 2));
+#pragma unroll
+              for (int j = 0; j < kBN / 128; ++j)
+                tma_2d(sS + 512 + 512 * j, &tmSFB, fb, 0, sfb_chunk + j * kgroups + (kb >> 2));
             }
             if (++stage == STAGES) {
               stage = 0;
@@ -573,11 +589,11 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
       Tile t;
       for (int ti = tile_first; ti < total_tiles && !*abort_v; ti += tile_stride, ++local) {
         if (!find_tile(args, n_groups, n_tiles_n, tile_prefix, ti, t)) break;
-        const int buf = local & 1;
+        const int buf = ACC_BUFS == 2 ? (local & 1) : 0;
         if (!mbar_wait(&acc_empty[buf], acc_phase[buf] ^ 1u, abort_v, args.status, 22)) break;
         acc_phase[buf] ^= 1u;
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * 128);
         bool failed = false;
         uint32_t sfa_col = 0, sfb_col = 0;
         for (int kb = 0; kb < kblocks; ++kb) {
@@ -590,14 +606,15 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
           const uint32_t sB = sA + A_BYTES;
           if ((kb & 3) == 0) {
             const uint32_t sS = smem_u32(sf_tiles + stage * SF_BYTES);
-            sfa_col = tmem_base + kSfCol + sf_buf * 8;
+            sfa_col = tmem_base + kSfCol + sf_buf * 16;
             sfb_col = sfa_col + 4;
             tmem_cp_sf2(sfa_col, make_desc_sf(sS));
-            tmem_cp_sf2(sfb_col, make_desc_sf(sS + 512));
+#pragma unroll
+            for (int j = 0; j < kBN / 128; ++j) tmem_cp_sf2(sfb_col + 4 * j, make_desc_sf(sS + 512 + 512 * j));
             sf_buf ^= 1u;
           }
           const uint32_t id = (uint32_t)(kb & 3);
-          const uint32_t idesc = make_idesc_scaled(BN, TILE_M, id, id);
+          const uint32_t idesc = make_idesc_scaled(kBN, TILE_M, id, id);
           const uint64_t da = make_desc_sw128(sA), db = make_desc_sw128(sB);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
@@ -629,11 +646,12 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     char* out0 = reinterpret_cast<char*>(args.out);
     for (int ti = tile_first; ti < total_tiles && !*abort_v; ti += tile_stride, ++local) {
       if (!find_tile(args, n_groups, n_tiles_n, tile_prefix, ti, t)) break;
-      const int buf = local & 1;
+      const int buf = ACC_BUFS == 2 ? (local & 1) : 0;
       if (!mbar_wait(&acc_full[buf], acc_phase[buf], abort_v, args.status, 24)) break;
       acc_phase[buf] ^= 1u;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 64);
+      constexpr int COLS_PER_WARP = kBN / 2;                      // 64 or 128 columns per warp
+      const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * 128 + half * COLS_PER_WARP);
       const int row_in_group = t.mt * TILE_M + cta_rank * BM + quarter * 32 + lane;
       const size_t row = (size_t)t.row0 + row_in_group;
       char* orow = nullptr;
@@ -646,21 +664,26 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
           orow = out0 + row * (size_t)args.N * 2;
         }
       }
-      uint32_t v0[32], v1[32];
-      tmem_ld32(taddr, v0);
-      tmem_ld32(taddr + 32, v1);
-      tmem_ld_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
-      uint4 p0[4], p1[4];
-      pack_row(v0, p0);
-      pack_row(v1, p1);
-      __syncwarp();
-      wide_store_half(stg, lane, p0, 0);
-      wide_store_half(stg, lane, p1, 1);
-      __syncwarp();
-      wide_flush(stg, lane, orow, (t.nt * BN + half * 64) * 2);
+#pragma unroll
+      for (int pairc = 0; pairc < COLS_PER_WARP / 64; ++pairc) {
+        uint32_t v0[32], v1[32];
+        tmem_ld32(taddr + pairc * 64, v0);
+        tmem_ld32(taddr + pairc * 64 + 32, v1);
+        tmem_ld_wait();
+        if (pairc == COLS_PER_WARP / 64 - 1) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));  // all values are in registers
+        }
+        uint4 p0[4], p1[4];
+        pack_row(v0, p0);
+        pack_row(v1, p1);
+        __syncwarp();
+        wide_store_half(stg, lane, p0, 0);
+        wide_store_half(stg, lane, p1, 1);
+        __syncwarp();
+        wide_flush(stg, lane, orow, (t.nt * kBN + half * COLS_PER_WARP + pairc * 64) * 2);
+      }
     }
   }
 
@@ -677,8 +700,7 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
   }
 }
 
-constexpr size_t kSmemBytes = STAGES * TILE_BYTES + STAGES * SF_BYTES + 1024 + kCtrlBytes + 8 * kStageWarpBytes;
-static_assert(kSmemBytes <= 232448, "shared memory budget exceeded");
+static_assert(Geo<128>::SMEM <= 232448 && Geo<256>::SMEM <= 232448, "shared memory budget exceeded");
 
 }  // namespace pair
 
@@ -936,17 +958,21 @@ cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorM
                                          const CUtensorMap& tmSFB, const Fp8GemmArgs& args, int num_sms,
                                          cudaStream_t stream) {
   if (args.n_groups_cap > MAX_GROUPS || args.N % BN != 0 || args.K % BK != 0 || args.K <= 0) return cudaErrorInvalidValue;
+  const bool wide = args.N % 256 == 0;   // 256-column tiles when the width allows it
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(pair::grouped_gemm_fp8_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)pair::kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(pair::grouped_gemm_fp8_pair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)pair::Geo<128>::SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(pair::grouped_gemm_fp8_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)pair::Geo<256>::SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(num_sms / 2 * 2));
   cfg.blockDim = dim3(NUM_THREADS);
-  cfg.dynamicSmemBytes = pair::kSmemBytes;
+  cfg.dynamicSmemBytes = wide ? pair::Geo<256>::SMEM : pair::Geo<128>::SMEM;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -955,7 +981,8 @@ cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorM
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, pair::grouped_gemm_fp8_pair_kernel, tmA, tmB, tmSFA, tmSFB, args);
+  if (wide) return cudaLaunchKernelEx(&cfg, pair::grouped_gemm_fp8_pair_kernel<256>, tmA, tmB, tmSFA, tmSFB, args);
+  return cudaLaunchKernelEx(&cfg, pair::grouped_gemm_fp8_pair_kernel<128>, tmA, tmB, tmSFA, tmSFB, args);
 }
 
 cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmArgs& args,

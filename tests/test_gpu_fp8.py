@@ -33,7 +33,7 @@ def test_quantisers_round_trip_within_fp8_precision():
 
 
 @pytest.mark.parametrize("ctas", [1, 2])
-@pytest.mark.parametrize("K,N", [(512, 256), (1408, 2048), (2048, 2816)])
+@pytest.mark.parametrize("K,N", [(512, 256), (640, 384), (1408, 2048), (2048, 2816)])
 def test_fp8_grouped_gemm_matches_dequantised_fp32(K, N, ctas):
     from ep_balance_b200.ops import fp8
 
