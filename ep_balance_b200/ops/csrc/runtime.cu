@@ -107,9 +107,21 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
     for (const char* name : {"w2q", "sfb1", "sfb2", "xq", "sfx", "actq", "sfact", "w1q_ptrs", "w2q_ptrs", "sfb1_ptrs", "sfb2_ptrs",
                              "xq_ptrs", "sfx_ptrs"})
       ptr<void>(name);
+    // weight boxes: 128 rows for the single-CTA kernel; the CTA-pair kernel stages half a tile's columns per CTA
+    const bool pair = c.gemm_ctas == 2;
+    const uint32_t box1 = pair ? ((2 * F) % 256 == 0 ? 128 : 64) : 128, box2 = pair ? (H % 256 == 0 ? 128 : 64) : 128;
     if (!make_tmap_fp8_2d(&tm_xq_, ptr<void>("xq"), T, H) || !make_tmap_fp8_2d(&tm_actq_, ptr<void>("actq"), T, F) ||
-        !make_tmap_fp8_3d(&tm_w1q_, ptr<void>("w1q"), S, 2 * F, H) || !make_tmap_fp8_3d(&tm_w2q_, ptr<void>("w2q"), S, H, F))
+        !make_tmap_fp8_3d(&tm_w1q_, ptr<void>("w1q"), S, 2 * F, H, box1) ||
+        !make_tmap_fp8_3d(&tm_w2q_, ptr<void>("w2q"), S, H, F, box2))
       throw std::runtime_error("MoeRuntime: cuTensorMapEncodeTiled (fp8) failed");
+    if (pair) {
+      const uint64_t kg_h = (H / 128 + 3) / 4, kg_f = (F / 128 + 3) / 4;
+      if (!make_tmap_sf(&tm_sfx_, ptr<void>("sfx"), (T / 128) * kg_h) ||
+          !make_tmap_sf(&tm_sfact_, ptr<void>("sfact"), (T / 128) * kg_f) ||
+          !make_tmap_sf(&tm_sfb1_, ptr<void>("sfb1"), S * (2 * F / 128) * kg_h) ||
+          !make_tmap_sf(&tm_sfb2_, ptr<void>("sfb2"), S * (H / 128) * kg_f))
+        throw std::runtime_error("MoeRuntime: cuTensorMapEncodeTiled (scale chunks) failed");
+    }
     fp8_ = true;
   }
 }
@@ -248,8 +260,9 @@ void MoeRuntime::pull_weights_fp8(cudaStream_t stream) {
   }
 }
 
-void MoeRuntime::gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int K, const uint8_t* sfa,
-                          const uint8_t* sfb, void* out, void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
+void MoeRuntime::gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& sfa_map,
+                          const CUtensorMap& sfb_map, int N, int K, const uint8_t* sfa, const uint8_t* sfb, void* out,
+                          void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
   Fp8GemmArgs g{};
   g.group_off = tables_.group_off;
   g.group_rows = tables_.group_rows;
@@ -265,7 +278,12 @@ void MoeRuntime::gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int
   g.out_ptrs = out_ptrs;
   g.meta = meta;
   g.status = sp_.status;
-  check(launch_grouped_gemm_fp8(a, b, g, cfg_.num_sms, stream), "grouped_gemm_fp8");
+  // the single-CTA kernel can share the pair kernel's weight map only when that map has 128-row boxes
+  const bool pair = cfg_.gemm_ctas == 2 && (fp8_pair_ || N % 256 != 0);
+  if (pair)
+    check(launch_grouped_gemm_fp8_pair(a, b, sfa_map, sfb_map, g, cfg_.num_sms, stream), "grouped_gemm_fp8_pair");
+  else
+    check(launch_grouped_gemm_fp8(a, b, g, cfg_.num_sms, stream), "grouped_gemm_fp8");
 }
 
 void MoeRuntime::dispatch_fp8(const void* tokens, int num_units, cudaStream_t stream) {
@@ -286,8 +304,8 @@ void MoeRuntime::dispatch_fp8(const void* tokens, int num_units, cudaStream_t st
 }
 
 void MoeRuntime::gemm1_fp8(cudaStream_t stream) {
-  gemm_fp8(tm_xq_, tm_w1q_, 2 * cfg_.F, cfg_.H, ptr<uint8_t>("sfx"), ptr<uint8_t>("sfb1"), ptr<void>("hbuf"), nullptr,
-           nullptr, stream);
+  gemm_fp8(tm_xq_, tm_w1q_, tm_sfx_, tm_sfb1_, 2 * cfg_.F, cfg_.H, ptr<uint8_t>("sfx"), ptr<uint8_t>("sfb1"),
+           ptr<void>("hbuf"), nullptr, nullptr, stream);
 }
 void MoeRuntime::act_fp8(cudaStream_t stream) {
   const RowGroups groups{tables_.group_off, tables_.group_rows, tables_.totals, cfg_.w_slots};
@@ -296,7 +314,7 @@ void MoeRuntime::act_fp8(cudaStream_t stream) {
         "swiglu_quantize");
 }
 void MoeRuntime::gemm2_fp8(cudaStream_t stream) {
-  gemm_fp8(tm_actq_, tm_w2q_, cfg_.H, cfg_.F, ptr<uint8_t>("sfact"), ptr<uint8_t>("sfb2"), nullptr,
+  gemm_fp8(tm_actq_, tm_w2q_, tm_sfact_, tm_sfb2_, cfg_.H, cfg_.F, ptr<uint8_t>("sfact"), ptr<uint8_t>("sfb2"), nullptr,
            ptr<void* const>("ybuf_ptrs"), ptr<const int2>("meta"), stream);
 }
 
@@ -304,6 +322,8 @@ void MoeRuntime::forward_fp8(const void* tokens, const int64_t* topk_idx, const 
                              int num_tokens, cudaStream_t stream) {
   if (!fp8_) throw std::runtime_error("MoeRuntime: fp8 regions were not provided");
   const int U = num_tokens * cfg_.topk;
+  // about U rows reach this rank; with few rows per expert the 256-row tiles of the pair kernel are mostly padding
+  fp8_pair_ = U >= 192 * cfg_.w_slots;
   publish(topk_idx, U, stream);
   solve(stream);
   route(topk_idx, U, stream);

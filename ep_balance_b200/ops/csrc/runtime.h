@@ -107,9 +107,12 @@ class MoeRuntime {
   CUtensorMap tm_w1_k_, tm_w2_k_, tm_w1_mn_, tm_w2_mn_;          // weights as B
   CUtensorMap tm_dy_mn_, tm_act_mn_, tm_dh_mn_, tm_x_mn_;        // Wgrad operands (MN-major)
   bool fp8_ = false;
+  bool fp8_pair_ = true;   // CTA-pair fp8 kernel (256-row tiles); forward_fp8 falls back to 128-row tiles for tiny batches
   CUtensorMap tm_xq_, tm_actq_, tm_w1q_, tm_w2q_;                // e4m3 operands
-  void gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, int N, int K, const uint8_t* sfa, const uint8_t* sfb,
-                void* out, void* const* out_ptrs, const int2* meta, cudaStream_t stream);
+  CUtensorMap tm_sfx_, tm_sfact_, tm_sfb1_, tm_sfb2_;            // scale chunks (CTA-pair fp8 kernel)
+  void gemm_fp8(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& sfa_map, const CUtensorMap& sfb_map, int N,
+                int K, const uint8_t* sfa, const uint8_t* sfb, void* out, void* const* out_ptrs, const int2* meta,
+                cudaStream_t stream);
 };
 
 }  // namespace epb
