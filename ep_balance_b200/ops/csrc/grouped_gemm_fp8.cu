@@ -664,20 +664,20 @@ grouped_gemm_fp8_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
           orow = out0 + row * (size_t)args.N * 2;
         }
       }
+      // read this warp's whole share of the accumulator into registers first and hand the buffer back at once:
+      // with a single accumulator the next tile's MMAs wait for exactly this read
+      uint32_t v[COLS_PER_WARP / 32][32];
+#pragma unroll
+      for (int c = 0; c < COLS_PER_WARP / 32; ++c) tmem_ld32(taddr + c * 32, v[c]);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));
 #pragma unroll
       for (int pairc = 0; pairc < COLS_PER_WARP / 64; ++pairc) {
-        uint32_t v0[32], v1[32];
-        tmem_ld32(taddr + pairc * 64, v0);
-        tmem_ld32(taddr + pairc * 64 + 32, v1);
-        tmem_ld_wait();
-        if (pairc == COLS_PER_WARP / 64 - 1) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0));  // all values are in registers
-        }
         uint4 p0[4], p1[4];
-        pack_row(v0, p0);
-        pack_row(v1, p1);
+        pack_row(v[2 * pairc], p0);
+        pack_row(v[2 * pairc + 1], p1);
         __syncwarp();
         wide_store_half(stg, lane, p0, 0);
         wide_store_half(stg, lane, p1, 1);
