@@ -41,6 +41,8 @@ def parse():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--tokens", type=int, default=CFG["tokens_per_rank"])
     p.add_argument("--gemm-ctas", type=int, default=2, choices=[1, 2], help="grouped GEMM: CTA pairs (2) or single CTAs (1)")
+    p.add_argument("--no-graph", action="store_true",
+                   help="end-to-end loop: launch every step eagerly instead of replaying it from a CUDA graph")
     p.add_argument("--phases", action="store_true", help="also print a per-phase device-time table (stderr)")
     return p.parse_args()
 
@@ -202,7 +204,7 @@ def run_ours(args):
                                                   CFG["imbalance_target"]).to(dev)
     from ep_balance_b200.utils.optim import FusedAdamW
 
-    opt = FusedAdamW(layer.parameters(), lr=1e-5)
+    opt = FusedAdamW(layer.parameters(), lr=1e-5, capturable=True)
     batches = host_batches(args.tokens, CFG["hidden"], rank)
     dev_batches = [b.to(dev) for b in batches]
     losses_read = []
@@ -245,14 +247,18 @@ def run_ours(args):
         loss_ready[i % DEPTH].synchronize()
         losses_read.append(float(loss_host[i % DEPTH]))
 
+    graphed = {"step": None}
+
     def step_e2e(i):
         slot = i % DEPTH
         if i == 0:
             prefetch(0)
         prefetch(i + 1)
         torch.cuda.current_stream().wait_event(ready[slot])
-        x = staging[slot].detach().requires_grad_(True)
-        loss = train_step(x)
+        if graphed["step"] is not None:
+            loss = graphed["step"](staging[slot])   # copies the batch into the graph's input buffer, then replays
+        else:
+            loss = train_step(staging[slot].detach().requires_grad_(True))
         consumed[slot].record()
         loss_host[slot:slot + 1].copy_(loss.detach().reshape(1), non_blocking=True)  # device->host, 4 bytes
         loss_ready[slot].record()
@@ -277,6 +283,19 @@ def run_ours(args):
     sampler.mark()
     ms_dev = timed_loop(step_device, args.steps, world)
     launches = layer.rt.launches()
+    e2e_mode = "eager launches"
+    if not args.no_graph:
+        # The whole step (router, native forward/backward, loss, AdamW) is a fixed launch sequence: capture it
+        # once and replay it, so the host cost per step is one graph launch.
+        try:
+            from ep_balance_b200.utils.graphs import GraphedStep
+
+            graphed["step"] = GraphedStep(lambda x: train_step(x.detach().requires_grad_(True)), dev_batches[0])
+            e2e_mode = "CUDA-graph replay of the whole step"
+        except Exception as exc:  # capture is an optimisation: fall back to eager launches
+            graphed["step"] = None
+            torch.cuda.synchronize()
+            print(f"[bench] graph capture failed, running the end-to-end loop eagerly: {exc}", file=sys.stderr)
     for i in range(min(3, args.warmup)):
         step_e2e(i)
     finish_e2e()
@@ -313,6 +332,7 @@ def run_ours(args):
     loads = layer.rank_loads().float()
     extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],
              "gemm_ctas": args.gemm_ctas,
+             "e2e_step": e2e_mode,
              "e2e_loop": "input H2D prefetched on a side stream (ring of 3 staging buffers); loss D2H copied "
                          "asynchronously and read by the host two steps later, the outstanding ones before the closing event",
              "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return, fused AdamW"}

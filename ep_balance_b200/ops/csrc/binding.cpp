@@ -175,7 +175,8 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
 
 // In-place AdamW step on one tensor (param, grad and both moments share dtype and shape).
 void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, torch::Tensor exp_avg_sq, double lr,
-                double beta1, double beta2, double eps, double weight_decay, int64_t step) {
+                double beta1, double beta2, double eps, double weight_decay, int64_t step,
+                c10::optional<torch::Tensor> step_tensor) {
   const c10::cuda::CUDAGuard guard(param.device());
   TORCH_CHECK(param.is_contiguous() && grad.is_contiguous() && exp_avg.is_contiguous() && exp_avg_sq.is_contiguous(),
               "adamw_step needs contiguous tensors");
@@ -201,6 +202,9 @@ void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, 
   a.bias_correction2_sqrt = (float)std::sqrt(1.0 - std::pow(beta2, (double)step));
   a.is_bf16 = param.scalar_type() == torch::kBFloat16 ? 1 : 0;
   a.grad_f32 = grad_f32 ? 1 : 0;
+  a.step_ptr = nullptr;
+  if (step_tensor.has_value() && step_tensor->defined())
+    a.step_ptr = dptr<int64_t>(*step_tensor, "step_tensor", torch::kInt64);
   cuda_check(epb::launch_adamw(a, current_stream()), "launch_adamw");
 }
 
@@ -401,7 +405,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("solve_plan", &solve_plan);
   m.def("grouped_gemm", &grouped_gemm);
   m.def("wait_probe", &wait_probe);
-  m.def("adamw_step", &adamw_step);
+  m.def("adamw_step", &adamw_step, py::arg("param"), py::arg("grad"), py::arg("exp_avg"), py::arg("exp_avg_sq"),
+        py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),
+        py::arg("step_tensor") = py::none());
   m.def("get_batched", &get_batched);
   m.def("put_batched", &put_batched);
   m.def("signal_peers", &signal_peers);

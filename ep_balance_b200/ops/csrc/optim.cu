@@ -16,7 +16,17 @@ __device__ __forceinline__ void adam_one(float& p, float g, float& m, float& v, 
   p -= (a.lr / a.bias_correction1) * (m / denom);
 }
 
+// With a device step counter the two bias corrections are derived here, once per thread.
+__device__ __forceinline__ void resolve_step(AdamArgs& a) {
+  if (a.step_ptr != nullptr) {
+    const float t = (float)(*a.step_ptr);
+    a.bias_correction1 = 1.f - powf(a.beta1, t);
+    a.bias_correction2_sqrt = sqrtf(1.f - powf(a.beta2, t));
+  }
+}
+
 __global__ void __launch_bounds__(256) adamw_bf16_kernel(AdamArgs a) {
+  resolve_step(a);
   const size_t n_vec = a.numel / 8;
   uint4* p4 = reinterpret_cast<uint4*>(a.param);
   const uint4* g4 = reinterpret_cast<const uint4*>(a.grad);
@@ -75,6 +85,7 @@ __global__ void __launch_bounds__(256) adamw_bf16_kernel(AdamArgs a) {
 }
 
 __global__ void __launch_bounds__(256) adamw_f32_kernel(AdamArgs a) {
+  resolve_step(a);
   float* p = reinterpret_cast<float*>(a.param);
   const float* g = reinterpret_cast<const float*>(a.grad);
   float* m = reinterpret_cast<float*>(a.exp_avg);

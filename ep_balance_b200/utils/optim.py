@@ -3,7 +3,9 @@
 Expert weights of :class:`~ep_balance_b200.models.moe_layer.FusedMoE` are two flat bf16 tensors
 per layer, so the whole expert update is two launches.  Moments are kept in the parameter's dtype
 (the convention of ``torch.optim.AdamW(fused=True)``).  No host synchronisation: the step count
-lives on the host and enters the kernel as two bias-correction scalars.
+lives on the host and enters the kernel as two bias-correction scalars.  With ``capturable=True`` the step
+count lives on the device instead and the kernel derives the bias corrections itself, so ``step()`` can be
+captured in a CUDA graph and replayed.
 """
 
 from __future__ import annotations
@@ -17,9 +19,10 @@ from ..ops.extension import load
 
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 1e-2) -> None:
+                 weight_decay: float = 1e-2, capturable: bool = False) -> None:
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self._ext = load()
+        self.capturable = bool(capturable)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -35,10 +38,14 @@ class FusedAdamW(torch.optim.Optimizer):
                     continue
                 st = self.state[p]
                 if not st:
-                    st["step"] = 0
+                    st["step"] = torch.zeros((), dtype=torch.int64, device=p.device) if self.capturable else 0
                     st["exp_avg"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
                     st["exp_avg_sq"] = torch.zeros_like(p, memory_format=torch.contiguous_format)
                 st["step"] += 1
-                self._ext.adamw_step(p.data, grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
-                                     group["eps"], group["weight_decay"], st["step"])
+                if self.capturable:
+                    self._ext.adamw_step(p.data, grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
+                                         group["eps"], group["weight_decay"], 1, st["step"])
+                else:
+                    self._ext.adamw_step(p.data, grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
+                                         group["eps"], group["weight_decay"], st["step"])
         return loss

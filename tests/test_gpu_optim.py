@@ -46,3 +46,48 @@ def test_adamw_reads_an_fp32_main_grad_for_bf16_parameters():
         opt_m.step()
         opt_r.step()
     assert float((mine.float() - ref).norm() / ref.norm()) < 1e-2
+
+
+def test_capturable_adamw_replays_from_a_graph_like_eager_steps():
+    """Whole training step of the fused layer captured once and replayed: parameters after three replays equal
+    three eager steps from the same start (same inputs), including the device-side step counter."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+    from ep_balance_b200.utils.graphs import GraphedStep
+    from ep_balance_b200.utils.optim import FusedAdamW
+
+    def build():
+        torch.manual_seed(0)
+        cfg = MoEConfig(hidden=256, ffn=256, num_experts=8, top_k=2, max_tokens=256)
+        layer = EmulatedCluster(cfg, world=1).layers[0]
+        opt = FusedAdamW(layer.parameters(), lr=1e-3, capturable=True)
+
+        def step(x):
+            loss = layer(x.detach().requires_grad_(True)).float().square().mean()
+            loss.backward()
+            opt.step()
+            opt.zero_grad(set_to_none=True)
+            return loss
+
+        return layer, step
+
+    xs = [torch.randn(256, 256, device="cuda", generator=torch.Generator(device="cuda").manual_seed(i)).bfloat16()
+          for i in range(6)]
+    eager_layer, eager_step = build()
+    eager_losses = [float(eager_step(x)) for x in xs]
+    graph_layer, graph_step = build()
+    g = GraphedStep(graph_step, xs[0], warmup=3)        # three warm-up steps on xs[0] inside
+    # bring the eager twin to the same state: three steps on xs[0]
+    twin_layer, twin_step = build()
+    for _ in range(3):
+        twin_step(xs[0])
+    losses = []
+    for x in xs[:3]:
+        losses.append(float(g(x)))
+        twin_step(x)
+    torch.cuda.synchronize()
+    graph_layer.check_status()
+    err = float((graph_layer.w1.float() - twin_layer.w1.float()).norm() / twin_layer.w1.float().norm())
+    assert err < 2e-3, err
+    assert float((graph_layer.w1.float() - eager_layer.w1.float()).abs().max()) > 0      # it did train
+    assert all(l == l and l > 0 for l in losses)
