@@ -130,6 +130,7 @@ def main(argv=None):
                 y16 = moe0(h0)
                 moe0._fp8_ready = True
                 err[str(nb)] = float((y8.float() - y16.float()).norm() / y16.float().norm().clamp_min(1e-12))
+                model(xb)  # first use of a kernel variant at this batch size loads it: keep that out of the timing
                 infer8[str(nb)] = timed(lambda: model(xb), a.steps)
                 if a.graphs:
                     replay, _ = graphed(xb)
