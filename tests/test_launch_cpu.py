@@ -24,3 +24,16 @@ def test_slot_sweep_monotone(tmp_path):
                            "--iterations", "1", "--warmup", "0", "--device", "cpu"])
     imb = [[r for r in pt["rows"] if r["strategy"] == "scale-eplb"][0]["quality_imbalance"] for pt in out]
     assert imb[1] <= imb[0] and (tmp_path / "s.json").exists()
+
+
+def test_env_report_runs_without_a_gpu(capsys):
+    from ep_balance_b200.launch import env_check
+    from ep_balance_b200.utils.env import describe_environment, problems
+
+    info = describe_environment()
+    assert info["torch"] and "cuda_available" in info
+    if not info["cuda_available"]:
+        assert problems(info) == ["no CUDA device is visible"]
+        assert env_check.main(["--json"]) == 1
+    out = capsys.readouterr().out
+    assert "torch" in out or info["cuda_available"]
