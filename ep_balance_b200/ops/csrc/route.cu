@@ -141,7 +141,22 @@ __global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a, int unit_
     const uint4* saved = a.saved_out ? reinterpret_cast<const uint4*>(a.saved_out) + (size_t)u * vec_per_row : nullptr;
     uint4* out = (dst >= 0 && row < a.row_capacity) ? reinterpret_cast<uint4*>(a.buf_ptrs[dst]) + (size_t)row * vec_per_row : nullptr;
     float dot = 0.f;
-    for (int v = lane; v < vec_per_row; v += 32) {
+    int v = lane;
+    // four independent 16-byte loads in flight per lane before the first store
+    for (; v + 96 < vec_per_row; v += 128) {
+      uint4 val[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) val[j] = src[v + 32 * j];
+      if (saved) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dot += dot8(val[j], saved[v + 32 * j]);
+      }
+      if (out) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) out[v + 32 * j] = a.unit_scale ? scale8(val[j], s) : val[j];
+      }
+    }
+    for (; v < vec_per_row; v += 32) {
       uint4 val = src[v];
       if (saved) dot += dot8(val, saved[v]);
       if (out) out[v] = a.unit_scale ? scale8(val, s) : val;
