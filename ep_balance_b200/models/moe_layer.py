@@ -7,7 +7,9 @@ One forward does, entirely on the device and without any host read:
   grouped GEMM2 with rows scattered back to their source rank  ->  gate-weighted reduce.
 
 and the backward mirrors it (gradient dispatch with fused gate gradients, Wgrad/Dgrad grouped
-GEMMs with the activation gradient fused, owner-side reduction of replica weight gradients).
+GEMMs, the activation gradient as one coalesced pass or fused into the Dgrad2 epilogue, owner-side
+reduction of replica weight gradients).  Forwards that run without autograd can use block-scaled fp8
+expert GEMMs (``MoEConfig.fp8_inference``) and select experts with one fused router kernel.
 This is the B200 counterpart of the reference's apply mode
 (eplb/integration/eplb_manager.py:905-1167 ``sync_free_moe_forward``, megatron_moe.py:156-215).
 
@@ -18,7 +20,8 @@ Weights use the ``[out, in]`` layout: ``w1[slot]`` is ``[2F, H]`` (gate rows the
 ``w2[slot]`` is ``[H, F]`` (reference: eplb/integration/grouped_mlp.py:117-137).
 
 Weight gradients are written straight into ``param.grad`` (a view of the symmetric gradient
-slots), overwriting the previous content; replicas' contributions are added by the owner.
+slots), overwriting the previous content; replicas' contributions are added by the owner.  With
+``MoEConfig.grad_accum_dtype`` they are accumulated over micro-batches instead.
 """
 
 from __future__ import annotations

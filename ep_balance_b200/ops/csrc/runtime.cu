@@ -2,8 +2,10 @@
 //
 // Step order (forward):  publish -> solve -> route -> dispatch -> pull -> [barrier] -> gemm1 ->
 // gemm2 (rows scattered to source ranks) -> [barrier] -> reduce_out.
-// Step order (backward): dispatch_grads (+ gate grads) -> [barrier] -> wgrad2 -> dgrad2 -> wgrad1
-// -> dgrad1 (rows scattered) -> [barrier] -> reduce_dtokens -> reduce_weight_grads.
+// Step order (backward): dispatch_grads (+ gate grads) -> [barrier] -> wgrad2 -> dgrad2 (+ SwiGLU gradient
+// pass) -> wgrad1 -> dgrad1 (rows scattered) -> [barrier] -> reduce_dtokens -> reduce_weight_grads.
+// Inference with fp8 experts: publish -> solve -> route -> dispatch fused with the 1 x 128 quantisation ->
+// fp8 replica pull -> [barrier] -> fp8 gemm1 -> SwiGLU + quantise -> fp8 gemm2 (scattered) -> [barrier] -> reduce_out.
 // This is the schedule the reference drives from Python over NCCL (eplb_manager.py:905-1167,
 // manual_block.py:127-367), restated as a fixed sequence of device-side kernels.
 #include "runtime.h"
