@@ -164,3 +164,30 @@ def test_replica_weight_channel_matches_indexing():
         worlds[0].check_status()
     finally:
         worlds[0].destroy()
+
+
+def test_module_level_facade_single_rank():
+    """``init`` / ``create_tensor`` / ``is_symmetric_tensor`` / ``get`` / ``world_fence`` / ``destroy`` on one rank
+    (the calling convention of the reference's ``nccl_gin`` module)."""
+    from ep_balance_b200.parallel import onesided
+
+    w = onesided.init(1 << 20, torch.device("cuda", 0))
+    try:
+        assert onesided.get_rank() == 0 and onesided.get_world_size() == 1
+        t = onesided.create_tensor((128, 64), torch.float32)
+        assert onesided.is_symmetric_tensor(t) and not onesided.is_symmetric_tensor(torch.zeros(4, device="cuda"))
+        t.copy_(torch.arange(128 * 64, device="cuda", dtype=torch.float32).view(128, 64))
+        dst = torch.zeros_like(t)
+        w.get(dst, t, peer=0)
+        w.world_fence(0)              # single rank: nothing to wait for
+        w.signal(0, 3, 5)
+        w.wait_signal(3, 5)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, t) and w.test_signal(3) == 5
+        w.check_status()
+        with pytest.raises(MemoryError):
+            onesided.create_tensor((1 << 20,), torch.float32)
+    finally:
+        onesided.destroy()
+    with pytest.raises(RuntimeError):
+        onesided.world()
