@@ -59,8 +59,9 @@ struct RowGroups {
   int n_groups_cap;
 };
 
-// CTA-pair variant (thread-block cluster of two SMs, 256 x 128 tiles, cta_group::2): groups must start on
-// multiples of 256 rows; `tmB` must have box_rows = 64; scale chunks are fetched through `tmSFA` / `tmSFB`.
+// CTA-pair variant (thread-block cluster of two SMs, cta_group::2): 256 x 256 tiles with one accumulator when
+// N % 256 == 0 (`tmB` box_rows = 128), else 256 x 128 tiles with two accumulators (`tmB` box_rows = 64).
+// Groups must start on multiples of 256 rows; scale chunks are fetched through `tmSFA` / `tmSFB`.
 cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmSFA,
                                          const CUtensorMap& tmSFB, const Fp8GemmArgs& args, int num_sms,
                                          cudaStream_t stream);
