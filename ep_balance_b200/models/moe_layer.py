@@ -26,6 +26,7 @@ slots), overwriting the previous content; replicas' contributions are added by t
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -70,6 +71,13 @@ class MoEConfig:
     # False: Dgrad2 is a plain GEMM into a [rows, ffn] buffer followed by one elementwise SwiGLU-gradient pass
     # (faster; costs that buffer).  True: the SwiGLU gradient runs in the GEMM epilogue, in place.
     fused_dgrad2: bool = False
+    # True: the token transport of a pass (dispatch + replica weight pull in forward, gradient dispatch in
+    # backward) runs on spare warps of the GEMM kernel that consumes the rows, so transfer and tensor-core
+    # tiles overlap.  False: a stand-alone transport kernel runs first.  ``EPLB_FUSED_COMM=0`` overrides.
+    fused_comm: bool = True
+    # Budget of every cross-rank wait inside this layer's kernels, in milliseconds (always bounded; on expiry
+    # the kernel records a status and returns).  ``EPLB_WAIT_MS`` overrides.
+    wait_ms: int = 1500
 
 
 def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
@@ -82,6 +90,8 @@ def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
     lay = HeapLayout()
     lay.add("omega", (world, E), torch.int32)
     lay.add("signals", (16,), torch.int32)
+    # arrival counters per GEMM M-tile of the receive buffers (forward, backward) + replica pull counters
+    lay.add("arrive", (2 * (cap // (128 * cfg.gemm_ctas)) + 2 * max(w_slots - home_cap, 0) + 4,), torch.int32)
     lay.add("xbuf", (cap, H), torch.bfloat16)
     lay.add("meta", (cap, 2), torch.int32)
     lay.add("ybuf", (U, H), torch.bfloat16)
@@ -241,6 +251,10 @@ class FusedMoE(nn.Module):
             "group_expert": torch.full((self.w_slots,), -1, **i32), "group_wslot": torch.zeros(self.w_slots, **i32),
             "group_off": torch.zeros(self.w_slots + 1, **i32), "group_rows": torch.zeros(self.w_slots, **i32),
             "totals": torch.zeros(2, **i32),
+            "send_off": torch.zeros((E, R), **i32), "tiles_of": torch.zeros(R, **i32),
+            "chunk_hist": torch.zeros((-(-self.max_units // 256), E), **i32), "hist_acc": torch.zeros(E + 1, **i32),
+            "exp_prefix": torch.zeros(E + 1, **i32), "sorted_units": torch.zeros(self.max_units, **i32),
+            "done_ctr": torch.zeros(4, **i32),
             "unit_dst": torch.zeros(self.max_units, **i32), "unit_row": torch.zeros(self.max_units, **i32),
             "hbuf": torch.zeros((self.row_capacity, 2 * F), dtype=torch.bfloat16, device=dev),
             "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
@@ -255,8 +269,8 @@ class FusedMoE(nn.Module):
             self._acc_gw1 = torch.zeros((self.home_cap, 2 * F, H), dtype=cfg.grad_accum_dtype, device=dev)
             self._acc_gw2 = torch.zeros((self.home_cap, H, F), dtype=cfg.grad_accum_dtype, device=dev)
             ptrs["acc_gw1"], ptrs["acc_gw2"] = self._acc_gw1.data_ptr(), self._acc_gw2.data_ptr()
-        symm_names = ["omega", "signals", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"]
-        table_names = [("omega", "omega_ptrs"), ("signals", "signal_ptrs"), ("xbuf", "xbuf_ptrs"),
+        symm_names = ["omega", "signals", "arrive", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"]
+        table_names = [("omega", "omega_ptrs"), ("signals", "signal_ptrs"), ("arrive", "arrive_ptrs"), ("xbuf", "xbuf_ptrs"),
                        ("meta", "meta_ptrs"), ("ybuf", "ybuf_ptrs"), ("dybuf", "dybuf_ptrs"),
                        ("dxbuf", "dxbuf_ptrs"), ("w1", "w1_ptrs"), ("w2", "w2_ptrs"), ("gw1", "gw1_ptrs"),
                        ("gw2", "gw2_ptrs")]
@@ -287,7 +301,9 @@ class FusedMoE(nn.Module):
                       probe=int(sc.stage2_patience_all_scales and iters > sc.stage2_stagnation_patience + 1),
                       s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync),
                       gemm_ctas=cfg.gemm_ctas, accum_fp32=int(cfg.grad_accum_dtype == torch.float32),
-                      fused_dgrad2=int(cfg.fused_dgrad2))
+                      fused_dgrad2=int(cfg.fused_dgrad2),
+                      fused_comm=int(os.environ.get("EPLB_FUSED_COMM", int(cfg.fused_comm))),
+                      wait_ms=int(os.environ.get("EPLB_WAIT_MS", cfg.wait_ms)))
         self.rt = load().MoeRuntime(rt_cfg, ptrs)
         self.bind_grads()
 

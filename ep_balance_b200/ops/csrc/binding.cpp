@@ -66,6 +66,9 @@ LayerConfig config_from_dict(const py::dict& d) {
   c.num_sms = get_int(d, "num_sms", 148);
   c.multi_rank_sync = get_int(d, "multi_rank_sync", 1);
   c.gemm_ctas = get_int(d, "gemm_ctas", 2);
+  c.fused_comm = get_int(d, "fused_comm", 1);
+  c.comm_block_rows = get_int(d, "comm_block_rows", 0);
+  c.wait_ms = get_int(d, "wait_ms", 1500);
   return c;
 }
 
@@ -440,9 +443,15 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("barrier", [](MoeRuntime& r, int slot) { r.barrier(slot, current_stream()); })
       .def("gemm1", [](MoeRuntime& r) { r.gemm1(current_stream()); })
       .def("gemm2", [](MoeRuntime& r) { r.gemm2(current_stream()); })
-      .def("reduce_out", [](MoeRuntime& r, uint64_t prob, uint64_t out, int n) {
-        r.reduce_out((const float*)cp(prob), mp(out), n, current_stream());
+      .def("gemm1_fused", [](MoeRuntime& r, uint64_t tok, int u) { r.gemm1_fused(cp(tok), u, current_stream()); })
+      .def("dgrad2_fused", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dprob, int u) {
+        r.dgrad2_fused(cp(dout), (const float*)cp(prob), (float*)mp(dprob), u, current_stream());
       })
+      .def("trace_launches", &MoeRuntime::trace_launches)
+      .def("launch_log", [](const MoeRuntime& r) { return r.launch_log(); })
+      .def("reduce_out", [](MoeRuntime& r, uint64_t prob, uint64_t out, int n, bool wait_peers) {
+        r.reduce_out((const float*)cp(prob), mp(out), n, current_stream(), wait_peers);
+      }, py::arg("prob"), py::arg("out"), py::arg("n"), py::arg("wait_peers") = false)
       .def("dispatch_grads", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dprob, int u) {
         r.dispatch_grads(cp(dout), (const float*)cp(prob), (float*)mp(dprob), u, current_stream());
       })
@@ -450,7 +459,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("dgrad2", [](MoeRuntime& r) { r.dgrad2(current_stream()); })
       .def("wgrad1", [](MoeRuntime& r) { r.wgrad1(current_stream()); })
       .def("dgrad1", [](MoeRuntime& r) { r.dgrad1(current_stream()); })
-      .def("reduce_dtokens", [](MoeRuntime& r, uint64_t dt, int n) { r.reduce_dtokens(mp(dt), n, current_stream()); })
+      .def("reduce_dtokens", [](MoeRuntime& r, uint64_t dt, int n, bool wait_peers) {
+        r.reduce_dtokens(mp(dt), n, current_stream(), wait_peers);
+      }, py::arg("dtokens"), py::arg("n"), py::arg("wait_peers") = false)
       .def("reduce_weight_grads", [](MoeRuntime& r) { r.reduce_weight_grads(current_stream()); })
       .def("has_fp8", &MoeRuntime::has_fp8)
       .def("quantize_own_weights", [](MoeRuntime& r) { r.quantize_own_weights(current_stream()); })

@@ -69,6 +69,21 @@ __device__ __forceinline__ bool wait_ge(const unsigned* p, unsigned target, unsi
 
 constexpr unsigned long long kWaitBudgetNs = 1500ull * 1000ull * 1000ull;  // 1.5 s
 
+// Host helper: "has this per-device one-time set-up been done on the current device?".  Function
+// attributes such as the dynamic shared-memory limit belong to (kernel, device), so a process that
+// drives several GPUs must set them on each.  `done` is a caller-owned table of kMaxTrackedDevices
+// flags; devices beyond the table are configured on every call.
+constexpr int kMaxTrackedDevices = 64;
+inline bool device_needs_setup(bool* done, int* dev_out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) dev = -1;
+  *dev_out = dev;
+  return dev < 0 || dev >= kMaxTrackedDevices || !done[dev];
+}
+inline void device_setup_done(bool* done, int dev) {
+  if (dev >= 0 && dev < kMaxTrackedDevices) done[dev] = true;
+}
+
 __host__ __device__ __forceinline__ int ceil_div(int a, int b) { return (a + b - 1) / b; }
 __host__ __device__ __forceinline__ int round_up(int a, int b) { return (a + b - 1) / b * b; }
 

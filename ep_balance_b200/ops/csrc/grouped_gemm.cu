@@ -17,6 +17,7 @@
 
 #include <cuda_bf16.h>
 
+#include "comm.cuh"
 #include "common.cuh"
 
 namespace epb {
@@ -30,15 +31,17 @@ constexpr int TMEM_COLS = 512;
 // two SMs) computes a 256 x 256 tile with tcgen05.mma.cta_group::2; each CTA stages its own 128
 // rows of A and its own 128 columns of B, so per-SM operand traffic drops from 48 KB to 32 KB per
 // k-block and the shared-memory ring deepens from 4 to 6 stages.
-template <int kCtas>
+// The fused-transport variants (kComm != 0) give one ring stage to the transport warps' copy rings.
+template <int kCtas, int kComm = 0>
 struct Geometry {
-  static constexpr int STAGES = kCtas == 2 ? 6 : 4;
+  static constexpr int STAGES = (kCtas == 2 ? 6 : 4) - (kComm ? 1 : 0);
   static constexpr int B_BYTES = BN * BK * 2 / kCtas;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_M = BM * kCtas;
 };
 constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
 constexpr int NUM_THREADS = 320;  // TMA warp + MMA warp + 8 epilogue warps
+constexpr int COMM_WARPS = 2;     // transport warps of the fused variants (warps 10, 11): 384 threads keep the 168-register budget
 constexpr int MAX_GROUPS = 320;  // barriers + flags + (MAX_GROUPS + 1) ints must fit in kCtrlBytes
 constexpr int kCtrlBytes = 1536;
 static_assert((6 * 2 + 4) * 8 + 8 + (MAX_GROUPS + 1) * 4 <= kCtrlBytes, "control block does not fit");
@@ -84,6 +87,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       }
     }
   }
+}
+
+// Bounded wait on a counter in global memory (kSys: peers write it over NVLink).  Followed by a
+// proxy fence: the data it guards was written through the generic proxy (peer or local stores) and is
+// read next by TMA, i.e. through the async proxy.
+template <bool kSys>
+__device__ __forceinline__ bool flag_wait(const unsigned* p, unsigned target, unsigned long long budget_ns,
+                                          volatile int* abort_flag, int* status, int site, int detail) {
+  unsigned long long t0 = 0;
+  for (unsigned spin = 0;; ++spin) {
+    const unsigned v = kSys ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if ((int)(v - target) >= 0) break;
+    if ((spin & 63u) == 63u) {
+      if (*abort_flag) return false;
+      unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) {
+        *abort_flag = 1;
+        set_status(status, kStatusSignalTimeout, site, detail);
+        return false;
+      }
+    }
+    if (spin > 16u) __nanosleep(64);
+  }
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+  return true;
 }
 
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -342,10 +371,13 @@ __device__ __forceinline__ void wide_flush(const uint4* tile, int lane, char* ro
   }
 }
 // ---------------------------------------------------------------- kernel
-template <int kMode, int kCtas>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, GemmArgs args) {
-  using G = Geometry<kCtas>;
+// kComm: 0 = GEMM only; 1 = plus two transport warps sending token rows / pulling replica weights;
+// 2 = plus two transport warps sending output gradients (scaled, with the gate-weight gradient).
+template <int kMode, int kCtas, int kComm>
+__global__ void __launch_bounds__(NUM_THREADS + (kComm ? COMM_WARPS * 32 : 0), 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ GemmArgs args) {
+  using G = Geometry<kCtas, kComm>;
   constexpr int STAGES = G::STAGES, STAGE_BYTES = G::STAGE_BYTES, TILE_M = G::TILE_M;
   constexpr bool kAMn = kMode == kWgrad;
   constexpr bool kBMn = kMode == kWgrad || kMode == kDgrad2 || kMode == kDgrad1;
@@ -405,10 +437,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int stage = 0;
     uint32_t phase = 0;
     Tile t;
+    const unsigned long long wait_ns = args.wait_ns ? args.wait_ns : kWaitBudgetNs;
+    int seen_mtile = -1, seen_group = -1, seen_slot = -1;  // waits already satisfied
     for (int ti = tile_first; ti < total_tiles; ti += tile_stride) {
       int go = 1;
       if (lane == 0) {
         if (*abort_v || !find_tile<kMode>(args, shape, tile_prefix, ti, t)) go = 0;
+        if (go && args.arrive != nullptr) {
+          // rows of this tile (kWgrad: of the whole group) must have arrived from every sender
+          const int first = t.row0 / TILE_M;
+          if (kMode == kWgrad) {
+            if (t.g != seen_group) {
+              const int n = ceil_div(min(t.rows, args.row_capacity - t.row0), TILE_M);
+              for (int i = 0; i < n && go; ++i)
+                if (!flag_wait<true>(args.arrive + first + i, args.arrive_expected, wait_ns, abort_v, args.status, 5, first + i)) go = 0;
+              seen_group = t.g;
+            }
+          } else if (first + t.mt != seen_mtile && (t.row0 + t.mt * TILE_M) < args.row_capacity) {
+            if (!flag_wait<true>(args.arrive + first + t.mt, args.arrive_expected, wait_ns, abort_v, args.status, 5, first + t.mt)) go = 0;
+            seen_mtile = first + t.mt;
+          }
+        }
+        if (go && args.pull_cnt != nullptr && t.wslot >= args.home_cap && t.wslot != seen_slot) {
+          if (!flag_wait<false>(args.pull_cnt + (t.wslot - args.home_cap), args.pull_expected, wait_ns, abort_v, args.status, 6, t.wslot)) go = 0;
+          seen_slot = t.wslot;
+        }
         if (go) {
           const int m_off = t.mt * TILE_M + cta_rank * BM;            // this CTA's rows of the tile
           const int n_off = t.nt * BN + cta_rank * (BN / 2) * (kCtas - 1);  // this CTA's columns of B
@@ -521,6 +574,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     __syncwarp();
+  } else if (kComm != 0 && warp >= NUM_THREADS / 32) {
+    // ------------------------------------------------------------ transport (warps 10, 11)
+    uint8_t* comm_smem_base = reinterpret_cast<uint8_t*>(stage_tiles) + 8 * kStageWarpBytes +
+                              (warp - NUM_THREADS / 32) * (kCommWarpBytes + kCommCtrlBytes);
+    comm_run<kComm == 2>(args.comm, (int)blockIdx.x * COMM_WARPS + (warp - NUM_THREADS / 32), (int)gridDim.x * COMM_WARPS,
+                         comm_smem_base, args.status);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
     // Each warp owns 32 accumulator rows.  Columns are processed 32 at a time: the TMEM load of
@@ -680,10 +739,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         else mbar_arrive(&acc_empty[buf]);
       }
     }
+    if (args.done_ctr != nullptr) __threadfence_system();  // this warp's (peer) stores before the completion signal
   }
 
   // ------------------------------------------------------------ teardown
   __syncthreads();
+  if (args.done_ctr != nullptr && threadIdx.x == 0) {
+    __threadfence_system();
+    if (atomicAdd(args.done_ctr, 1u) == gridDim.x - 1) {
+      // last CTA of the launch: every CTA's rows are stored and fenced
+      *args.done_ctr = 0u;
+      __threadfence_system();
+      *args.done_epoch += 1u;
+      for (int r = 0; r < args.done_R; ++r) red_release_sys_add(args.done_signal_ptrs[r] + args.done_slot, 1u);
+    }
+  }
   if (*abort_v && threadIdx.x == 0) {
     // let copies that were already issued land before the shared memory is released
     unsigned long long t0 = globaltimer_ns();
@@ -698,11 +768,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
-template <int kCtas>
+template <int kCtas, int kComm>
 constexpr size_t smem_bytes() {
-  return Geometry<kCtas>::STAGES * Geometry<kCtas>::STAGE_BYTES + 1024 /*align*/ + kCtrlBytes /*barriers, flags, tile prefix*/ +
-         8 * kStageWarpBytes /*staging*/;
+  return Geometry<kCtas, kComm>::STAGES * Geometry<kCtas, kComm>::STAGE_BYTES + 1024 /*align*/ +
+         kCtrlBytes /*barriers, flags, tile prefix*/ + 8 * kStageWarpBytes /*staging*/ +
+         (kComm ? COMM_WARPS * (kCommWarpBytes + kCommCtrlBytes) : 0) /*transport rings*/;
 }
+static_assert(smem_bytes<2, 1>() <= 232448 && smem_bytes<1, 1>() <= 232448 && smem_bytes<2, 0>() <= 232448, "shared memory budget");
 
 // ---------------------------------------------------------------- tensor maps
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -749,20 +821,21 @@ bool make_tmap_3d(CUtensorMap* out, const void* base, uint64_t slots, uint64_t r
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int kMode, int kCtas>
+template <int kMode, int kCtas, int kComm>
 static cudaError_t launch_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
                                cudaStream_t stream) {
-  static bool configured = false;
-  constexpr size_t smem = smem_bytes<kCtas>();
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode, kCtas>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  static bool configured[kMaxTrackedDevices] = {};
+  constexpr size_t smem = smem_bytes<kCtas, kComm>();
+  int dev;
+  if (device_needs_setup(configured, &dev)) {
+    cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<kMode, kCtas, kComm>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return e;
-    configured = true;
+    device_setup_done(configured, dev);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(num_sms / kCtas * kCtas));
-  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.blockDim = dim3(NUM_THREADS + (kComm ? COMM_WARPS * 32 : 0));
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -772,19 +845,27 @@ static cudaError_t launch_mode(const CUtensorMap& tmA, const CUtensorMap& tmB, c
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<kMode, kCtas>, tmA, tmB, args);
+  return cudaLaunchKernelEx(&cfg, grouped_gemm_kernel<kMode, kCtas, kComm>, tmA, tmB, args);
 }
 
 template <int kCtas>
 static cudaError_t launch_ctas(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmArgs& args, int num_sms,
                                cudaStream_t stream) {
+  const bool comm = args.comm.do_dispatch || args.comm.do_pad || args.comm.do_pull;
+  if (comm) {
+    // fused transport exists for the two GEMMs that consume freshly dispatched rows
+    const bool bwd = args.comm.unit_scale != nullptr || args.comm.saved_out != nullptr;
+    if (args.mode == kFwd1 && !bwd) return launch_mode<kFwd1, kCtas, 1>(tmA, tmB, args, num_sms, stream);
+    if (args.mode == kDgrad1 && bwd) return launch_mode<kDgrad1, kCtas, 2>(tmA, tmB, args, num_sms, stream);
+    return cudaErrorInvalidValue;
+  }
   switch (args.mode) {
-    case kFwd1: return launch_mode<kFwd1, kCtas>(tmA, tmB, args, num_sms, stream);
-    case kFwd2: return launch_mode<kFwd2, kCtas>(tmA, tmB, args, num_sms, stream);
-    case kDgrad2: return launch_mode<kDgrad2, kCtas>(tmA, tmB, args, num_sms, stream);
-    case kDgrad1: return launch_mode<kDgrad1, kCtas>(tmA, tmB, args, num_sms, stream);
-    case kWgrad: return launch_mode<kWgrad, kCtas>(tmA, tmB, args, num_sms, stream);
-    case kPlain: return launch_mode<kPlain, kCtas>(tmA, tmB, args, num_sms, stream);
+    case kFwd1: return launch_mode<kFwd1, kCtas, 0>(tmA, tmB, args, num_sms, stream);
+    case kFwd2: return launch_mode<kFwd2, kCtas, 0>(tmA, tmB, args, num_sms, stream);
+    case kDgrad2: return launch_mode<kDgrad2, kCtas, 0>(tmA, tmB, args, num_sms, stream);
+    case kDgrad1: return launch_mode<kDgrad1, kCtas, 0>(tmA, tmB, args, num_sms, stream);
+    case kWgrad: return launch_mode<kWgrad, kCtas, 0>(tmA, tmB, args, num_sms, stream);
+    case kPlain: return launch_mode<kPlain, kCtas, 0>(tmA, tmB, args, num_sms, stream);
     default: return cudaErrorInvalidValue;
   }
 }

@@ -15,6 +15,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "route.h"
+
 namespace epb {
 
 enum GemmMode : int { kFwd1 = 0, kFwd2 = 1, kDgrad2 = 2, kDgrad1 = 3, kWgrad = 4, kPlain = 5 };
@@ -41,6 +43,28 @@ struct GemmArgs {
   void* const* out_ptrs;       // scatter modes: R peer buffers [units, N] (null -> local out0)
   const int2* meta;            // scatter modes: {src rank, unit} per row
   int* status;
+  unsigned long long wait_ns;  // budget of the waits below (0: the library default)
+  // ---- operand gating (each may be null).  The TMA producer polls before the first load of a tile:
+  // the A rows of M-tile i are complete when arrive[i] >= arrive_expected (counters written by the
+  // senders' transport, CommArgs); the weights of replica slot s (wslot - home_cap) are complete when
+  // pull_cnt[s] >= pull_expected.  kWgrad waits for every M-tile of the group.
+  const unsigned* arrive;
+  unsigned arrive_expected;
+  const unsigned* pull_cnt;
+  unsigned pull_expected;
+  int home_cap;
+  // ---- completion signal of the scatter modes (null: none).  The last CTA to finish advances the
+  // local epoch word and adds 1 (release, system scope) to word `done_slot` of every peer's signal
+  // array: "all rows this rank owes you are stored".  done_ctr is zero between launches.
+  unsigned* done_ctr;
+  unsigned* done_epoch;
+  unsigned* const* done_signal_ptrs;
+  int done_slot, done_R;
+  // ---- fused transport (comm.do_* all zero: none).  Two extra warps per CTA run the item-driven
+  // transport of CommArgs while the other warps compute: kFwd1 sends token rows and pulls replica
+  // weights, kDgrad1 (used as the plain Dgrad2) sends output gradients; the producer of the same
+  // kernel -- on every rank -- gates its tiles on the arrival counters those warps advance.
+  CommArgs comm;
 };
 
 // Host-side tensor-map helpers (driver entry point fetched at run time; no -lcuda needed).

@@ -959,15 +959,16 @@ cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorM
                                          cudaStream_t stream) {
   if (args.n_groups_cap > MAX_GROUPS || args.N % BN != 0 || args.K % BK != 0 || args.K <= 0) return cudaErrorInvalidValue;
   const bool wide = args.N % 256 == 0;   // 256-column tiles when the width allows it
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxTrackedDevices] = {};
+  int dev;
+  if (device_needs_setup(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(pair::grouped_gemm_fp8_pair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)pair::Geo<128>::SMEM);
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(pair::grouped_gemm_fp8_pair_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)pair::Geo<256>::SMEM);
     if (e != cudaSuccess) return e;
-    configured = true;
+    device_setup_done(configured, dev);
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(num_sms / 2 * 2));
@@ -988,12 +989,13 @@ cudaError_t launch_grouped_gemm_fp8_pair(const CUtensorMap& tmA, const CUtensorM
 cudaError_t launch_grouped_gemm_fp8(const CUtensorMap& tmA, const CUtensorMap& tmB, const Fp8GemmArgs& args,
                                     int num_sms, cudaStream_t stream) {
   if (args.n_groups_cap > MAX_GROUPS || args.N % BN != 0 || args.K % BK != 0 || args.K <= 0) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[kMaxTrackedDevices] = {};
+  int dev;
+  if (device_needs_setup(configured, &dev)) {
     cudaError_t e = cudaFuncSetAttribute(grouped_gemm_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)kSmemBytes);
     if (e != cudaSuccess) return e;
-    configured = true;
+    device_setup_done(configured, dev);
   }
   grouped_gemm_fp8_kernel<<<num_sms, NUM_THREADS, kSmemBytes, stream>>>(tmA, tmB, args);
   return cudaGetLastError();

@@ -84,7 +84,7 @@ __device__ void copy_range(uint8_t* dst, const uint8_t* src, int64_t nbytes, int
       int64_t prev_off = -1;
       uint32_t prev_bytes = 0;
       bool ok = true;
-      int it = 0;
+      int it = 0, late_it = -1;
       for (; tile < n_tiles && ok; tile += warps_total, ++it) {
         const int s = it & 1;
         const int64_t off = tile * kTileBytes;
@@ -96,17 +96,20 @@ __device__ void copy_range(uint8_t* dst, const uint8_t* src, int64_t nbytes, int
           const int ps = (it - 1) & 1;
           ok = bar_wait(&bars[ps], ((it - 1) >> 1) & 1);
           if (ok) bulk_store(dst + prev_off, ring + ps * kTileBytes, prev_bytes);
+          else late_it = it - 1;  // this load is still in flight
         }
         prev_off = off;
         prev_bytes = bytes;
       }
       if (it >= 1) {
-        // the last issued load always lands (its source is valid memory); wait for it even after a
-        // timeout so that no copy targets this CTA's shared memory after it exits
+        // Loads always land eventually (their sources are valid memory).  Wait once more, bounded, for
+        // every load still in flight -- the last one issued and, after a timeout, the one that was late --
+        // so that no copy targets this CTA's shared memory after it exits.
         const int ps = (it - 1) & 1;
         const bool landed = bar_wait(&bars[ps], ((it - 1) >> 1) & 1);
         if (ok && landed) bulk_store(dst + prev_off, ring + ps * kTileBytes, prev_bytes);
         ok = ok && landed;
+        if (late_it >= 0) bar_wait(&bars[late_it & 1], (late_it >> 1) & 1);
       }
       bulk_wait_all();
       if (!ok) set_status(status, kStatusPipeTimeout, 71, (int)blockIdx.x);
@@ -170,11 +173,12 @@ cudaError_t launch_copy(const BatchedCopyArgs& a, int blocks_per_desc, cudaStrea
   if (a.K <= 0) return cudaSuccess;
   if (blocks_per_desc < 1) blocks_per_desc = 1;
   if (blocks_per_desc > 65535) return cudaErrorInvalidValue;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[kPut]) {
+  static bool attr_set[2][kMaxTrackedDevices] = {};
+  int dev;
+  if (device_needs_setup(attr_set[kPut], &dev)) {
     cudaError_t e = cudaFuncSetAttribute(copy_batched_kernel<kPut>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCopySmem);
     if (e != cudaSuccess) return e;
-    attr_set[kPut] = true;
+    device_setup_done(attr_set[kPut], dev);
   }
   dim3 grid(a.K, blocks_per_desc);
   copy_batched_kernel<kPut><<<grid, kCopyThreads, a.use_bulk ? kCopySmem : 0, stream>>>(a);

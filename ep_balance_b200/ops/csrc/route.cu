@@ -1,10 +1,11 @@
-// Token-path and weight-path kernels: count + publish, route assignment, dispatch, unit reduce,
-// cross-rank barrier, replica weight pull and owner-side gradient return.
+// Token-path and weight-path kernels: count + publish, route assignment, the stand-alone form of the
+// item-driven transport (comm.cuh), unit reduce, cross-rank barrier, replica weight pull and owner-side
+// gradient return.
 //
 // Replaces the reference's torch-op chains and NCCL calls on the MoE path:
 //   bincount + all_gather (eplb/distributed.py:17-61)            -> count_publish_kernel
 //   assign_physical + argsort/index_select (physical.py:30-77,
-//       eplb_manager.py:1067-1105)                                -> route_assign + dispatch
+//       eplb_manager.py:1067-1105)                                -> route_assign + comm (comm.cuh)
 //   index_add scatter with gate weight (eplb_manager.py:889-899)  -> unit_reduce_kernel
 //   dist.broadcast per expert / GIN get (overlap.py:113-148,
 //       gin_weights.py:305-341)                                   -> weight_pull_kernel
@@ -15,6 +16,7 @@
 
 #include <cuda_bf16.h>
 
+#include "comm.cuh"
 #include "common.cuh"
 
 namespace epb {
@@ -22,167 +24,154 @@ namespace {
 
 constexpr unsigned kFull = 0xffffffffu;
 
+// SM count of the current device (the runtime caches device attributes; this is a cheap host call).
+int sm_count() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+      sms <= 0)
+    return 132;
+  return sms;
+}
+
 // ------------------------------------------------------------------ count + publish
-__global__ void __launch_bounds__(1024) count_publish_kernel(const int64_t* __restrict__ unit_expert, int U, int E,
-                                                            int R, int me, int32_t* const* omega_ptrs,
-                                                            unsigned* const* signal_ptrs, unsigned* epoch_word) {
-  extern __shared__ int hist[];
-  for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+// One CTA per chunk of kRouteChunk units.  Each CTA keeps its chunk's histogram for the route
+// assignment and adds it to the running histogram; the last CTA to finish publishes.
+__global__ void __launch_bounds__(kRouteChunk) count_publish_kernel(CountArgs a) {
+  extern __shared__ int hist[];  // [E]
+  __shared__ int is_last;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int E = a.E, R = a.R;
+  for (int e = tid; e < E; e += nt) hist[e] = 0;
   __syncthreads();
-  for (int u = threadIdx.x; u < U; u += blockDim.x) {
-    int e = (int)unit_expert[u];
+  const int u = blockIdx.x * kRouteChunk + tid;
+  if (u < a.num_units) {
+    const int e = (int)a.unit_expert[u];
     if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < E * R; idx += blockDim.x) {
-    int peer = idx / E, e = idx - peer * E;
-    omega_ptrs[peer][(size_t)me * E + e] = hist[e];
+  for (int e = tid; e < E; e += nt) {
+    const int c = hist[e];
+    a.chunk_hist[(size_t)blockIdx.x * E + e] = c;
+    if (c) atomicAdd(&a.hist_acc[e], c);
   }
-  if (threadIdx.x == 0 && epoch_word != nullptr) *epoch_word += 1u;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) is_last = atomicAdd(&a.hist_acc[E], 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // ---- last CTA: take (and clear) the full histogram, publish it, clear the arrival counters
+  for (int e = tid; e < E; e += nt) hist[e] = atomicExch(&a.hist_acc[e], 0);
+  if (tid == 0) a.hist_acc[E] = 0;
+  __syncthreads();
+  if (tid < 32) {  // exclusive prefix over experts by one warp
+    int run = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + tid;
+      const int c = e < E ? hist[e] : 0;
+      int incl = c;
+      for (int off = 1; off < 32; off <<= 1) {
+        const int o = __shfl_up_sync(kFull, incl, off);
+        if (tid >= off) incl += o;
+      }
+      if (e < E) a.exp_prefix[e] = run + incl - c;
+      run += __shfl_sync(kFull, incl, 31);
+    }
+    if (tid == 0) a.exp_prefix[E] = run;
+  }
+  for (int idx = tid; idx < E * R; idx += nt) {
+    const int peer = idx / E, e = idx - peer * E;
+    a.omega_ptrs[peer][(size_t)a.me * E + e] = hist[e];
+  }
+  for (int i = tid; i < a.clear_words; i += nt) a.clear[i] = 0u;
+  if (tid == 0 && a.epoch_word != nullptr) *a.epoch_word += 1u;
   __threadfence_system();
   __syncthreads();
-  if (signal_ptrs != nullptr && threadIdx.x < R) red_release_sys_add(signal_ptrs[threadIdx.x], 1u);
+  if (a.signal_ptrs != nullptr)
+    for (int r = tid; r < R; r += nt) red_release_sys_add(a.signal_ptrs[r], 1u);
 }
 
 // ------------------------------------------------------------------ route assignment
-// One CTA per expert.  Units of the expert are ranked in their original order with a block-wide
-// ballot scan; the j-th unit goes to the host whose quota prefix covers j.
-__global__ void __launch_bounds__(1024) route_assign_kernel(const int64_t* __restrict__ unit_expert, int U, int E,
-                                                           int R, const int32_t* __restrict__ q_me,
-                                                           const int32_t* __restrict__ row_base,
-                                                           int32_t* __restrict__ unit_dst,
-                                                           int32_t* __restrict__ unit_row, int* status) {
+// One CTA per chunk.  A unit's rank within its expert (original order) = units of that expert in
+// earlier chunks + in earlier warps of this chunk + in earlier lanes of its warp; the j-th unit goes
+// to the host whose quota prefix covers j.
+__global__ void __launch_bounds__(kRouteChunk) route_assign_kernel(RouteArgs a) {
   extern __shared__ int sm[];
-  int* qpre = sm;               // [R + 1] exclusive prefix of q_me[e, :]
-  int* base = sm + (R + 1);     // [R]
-  int* warp_cnt = base + R;     // [32]
-  __shared__ int running;
-  const int e = blockIdx.x;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
-  if (tid == 0) {
-    int acc = 0;
-    for (int r = 0; r < R; ++r) {
-      qpre[r] = acc;
-      acc += q_me[(size_t)e * R + r];
-      base[r] = row_base[(size_t)e * R + r];
-    }
-    qpre[R] = acc;
-    running = 0;
-  }
+  constexpr int kWarps = kRouteChunk / 32;
+  const int E = a.E, R = a.R;
+  int* before = sm;             // [E] units of each expert in earlier chunks
+  int* warp_cnt = sm + E;       // [kWarps, E]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nt = blockDim.x;
+  for (int i = tid; i < E * (1 + kWarps); i += nt) sm[i] = 0;
   __syncthreads();
-  const int total = qpre[R];
-  for (int start = 0; start < U; start += blockDim.x) {
-    const int u = start + tid;
-    const bool hit = u < U && (int)unit_expert[u] == e;
-    const unsigned m = __ballot_sync(kFull, hit);
-    if (lane == 0) warp_cnt[warp] = __popc(m);
-    __syncthreads();
-    int before = running;
-    for (int w = 0; w < warp; ++w) before += warp_cnt[w];
-    if (hit) {
-      const int j = before + __popc(m & ((1u << lane) - 1u));
-      int dst = 0;
-      while (dst + 1 < R && j >= qpre[dst + 1]) ++dst;
-      if (j >= total) {
-        set_status(status, kStatusBadArgument, 40, e);
-        unit_dst[u] = -1;
-        unit_row[u] = -1;
-      } else {
-        unit_dst[u] = dst;
-        unit_row[u] = base[dst] + (j - qpre[dst]);
-      }
+  // earlier chunks: the threads split (expert, chunk residue) pairs
+  {
+    const int parts = nt / E > 0 ? nt / E : 1;
+    for (int idx = tid; idx < E * parts; idx += nt) {
+      const int e = idx % E, part = idx / E;
+      int acc = 0;
+      for (int c = part; c < (int)blockIdx.x; c += parts) acc += a.chunk_hist[(size_t)c * E + e];
+      if (acc) atomicAdd(&before[e], acc);
     }
-    __syncthreads();
-    if (tid == 0) {
-      int add = 0;
-      for (int w = 0; w < nwarps; ++w) add += warp_cnt[w];
-      running += add;
-    }
-    __syncthreads();
   }
-}
-
-// ------------------------------------------------------------------ dispatch
-// One warp per unit: 16-byte loads of the token row, 16-byte stores into the destination rank's
-// receive buffer.  Blocks past the unit range zero this rank's padding rows.
-__device__ __forceinline__ float dot8(const uint4& a, const uint4& b) {
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-  float acc = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
-    acc += fa.x * fb.x + fa.y * fb.y;
+  const int u = blockIdx.x * kRouteChunk + tid;
+  int e = u < a.num_units ? (int)a.unit_expert[u] : -1;
+  if (e >= E) e = -1;
+  const unsigned peers = __match_any_sync(kFull, e);
+  const int rank_in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (e >= 0 && rank_in_warp == 0) warp_cnt[warp * E + e] = __popc(peers);
+  __syncthreads();
+  if (e < 0) {
+    if (u < a.num_units) {
+      a.unit_dst[u] = -1;
+      a.unit_row[u] = -1;
+    }
+    return;
   }
-  return acc;
-}
-__device__ __forceinline__ uint4 scale8(const uint4& a, float s) {
-  uint4 out;
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(pa[i]);
-    po[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
+  int j = before[e] + rank_in_warp;
+  for (int w = 0; w < warp; ++w) j += warp_cnt[w * E + e];
+  const int32_t* qrow = a.q_me + (size_t)e * R;
+  int dst = 0, pre = 0, have = qrow[0];
+  while (dst + 1 < R && j >= pre + have) {
+    pre += have;
+    ++dst;
+    have = qrow[dst];
   }
-  return out;
-}
-
-__global__ void __launch_bounds__(256) dispatch_kernel(DispatchArgs a, int unit_blocks) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
-  const int vec_per_row = a.H / 8;  // uint4 = 8 bf16
-  if ((int)blockIdx.x < unit_blocks) {
-    const int u = blockIdx.x * wpb + warp;
-    if (u >= a.num_units) return;
-    const int dst = a.unit_dst[u], row = a.unit_row[u];
-    const int t = u / a.topk;
-    const uint4* src = reinterpret_cast<const uint4*>(a.rows) + (size_t)t * vec_per_row;
-    const float s = a.unit_scale ? a.unit_scale[u] : 1.f;
-    const uint4* saved = a.saved_out ? reinterpret_cast<const uint4*>(a.saved_out) + (size_t)u * vec_per_row : nullptr;
-    uint4* out = (dst >= 0 && row < a.row_capacity) ? reinterpret_cast<uint4*>(a.buf_ptrs[dst]) + (size_t)row * vec_per_row : nullptr;
-    float dot = 0.f;
-    int v = lane;
-    // four independent 16-byte loads in flight per lane before the first store
-    for (; v + 96 < vec_per_row; v += 128) {
-      uint4 val[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) val[j] = src[v + 32 * j];
-      if (saved) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) dot += dot8(val[j], saved[v + 32 * j]);
-      }
-      if (out) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) out[v + 32 * j] = a.unit_scale ? scale8(val[j], s) : val[j];
-      }
-    }
-    for (; v < vec_per_row; v += 32) {
-      uint4 val = src[v];
-      if (saved) dot += dot8(val, saved[v]);
-      if (out) out[v] = a.unit_scale ? scale8(val, s) : val;
-    }
-    if (saved) {
-      for (int off = 16; off > 0; off >>= 1) dot += __shfl_down_sync(kFull, dot, off);
-      if (lane == 0) a.unit_dot[u] = dot;
-    }
-    if (lane == 0 && out != nullptr && a.meta_ptrs != nullptr) a.meta_ptrs[dst][row] = make_int2(a.me, u);
+  if (j >= pre + have) {
+    set_status(a.status, kStatusBadArgument, 40, e);
+    a.unit_dst[u] = -1;
+    a.unit_row[u] = -1;
   } else {
-    // padding rows of slot g: [off + rows, next off)
-    const int g = blockIdx.x - unit_blocks;
-    if (g >= a.n_slot) return;
-    const int lo = min(a.slot_off[g] + a.slot_rows[g], a.row_capacity), hi = min(a.slot_off[g + 1], a.row_capacity);
-    uint4* buf = reinterpret_cast<uint4*>(a.local_buf);
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    const size_t begin = (size_t)lo * vec_per_row, end = (size_t)hi * vec_per_row;
-    for (size_t i = begin + threadIdx.x; i < end; i += blockDim.x) buf[i] = zero;
+    a.unit_dst[u] = dst;
+    a.unit_row[u] = a.row_base[(size_t)e * R + dst] + (j - pre);
   }
+  if (a.sorted_units != nullptr) a.sorted_units[a.exp_prefix[e] + j] = u;
+}
+
+// ------------------------------------------------------------------ stand-alone transport
+constexpr int kCommKernelWarps = 8;
+constexpr int kCommKernelSmem = kCommKernelWarps * (kCommWarpBytes + kCommCtrlBytes) + 128;
+
+template <bool kBwd>
+__global__ void __launch_bounds__(kCommKernelWarps * 32) comm_kernel(const __grid_constant__ CommArgs a, int* status) {
+  extern __shared__ uint8_t comm_smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 127) & ~(uintptr_t)127);
+  const int warp = threadIdx.x >> 5;
+  comm_run<kBwd>(a, (int)blockIdx.x * kCommKernelWarps + warp, (int)gridDim.x * kCommKernelWarps,
+                 base + warp * (kCommWarpBytes + kCommCtrlBytes), status);
 }
 
 // ------------------------------------------------------------------ unit reduce
 __global__ void __launch_bounds__(256) unit_reduce_kernel(const uint4* __restrict__ unit_rows,
                                                          const float* __restrict__ unit_scale,
                                                          uint4* __restrict__ out, int num_tokens, int topk,
-                                                         int vec_per_row) {
+                                                         int vec_per_row, UnitReduceWait wait) {
+  if (wait.signal != nullptr) {
+    // rows come from the peers' GEMM epilogues: wait until every rank has signalled completion
+    if (threadIdx.x == 0 && !wait_ge<true>(wait.signal, *wait.epoch * (unsigned)wait.R, wait.budget_ns))
+      set_status(wait.status, kStatusSignalTimeout, 51);
+    __syncthreads();
+  }
   // one warp per (token, 32-vector chunk of the row): small batches still fill the machine
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
   const int chunks = (vec_per_row + 31) / 32;
@@ -261,6 +250,8 @@ __global__ void __launch_bounds__(512) weight_pull_kernel(WeightPullArgs a) {
   for (; i < n_vec; i += stride) dst[i] = src[i];
 }
 
+constexpr int kMaxGradHosts = 64;  // replica hosts of one expert a gradient-return CTA can list (ranks R <= 64)
+
 __device__ __forceinline__ void add8(float* acc, const uint4& v) {
   const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -276,8 +267,8 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   const int home = blockIdx.y;
   __shared__ int expert;
   __shared__ int n_hosts;
-  __shared__ int host_rank[64];
-  __shared__ int host_slot[64];
+  __shared__ int host_rank[kMaxGradHosts];
+  __shared__ int host_slot[kMaxGradHosts];
   if (threadIdx.x == 0) {
     expert = -1;
     n_hosts = 0;
@@ -290,7 +281,7 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   if (e < 0) return;
   if (threadIdx.x == 0) {
     int n = 0;
-    for (int h = 0; h < a.R && n < 64; ++h) {
+    for (int h = 0; h < a.R && n < kMaxGradHosts; ++h) {
       int s = a.slot_of[(size_t)e * a.R + h];
       if ((h != a.me || a.include_self) && s >= 0) {
         host_rank[n] = h;
@@ -372,38 +363,51 @@ __global__ void wait_probe_kernel(const unsigned* flag, unsigned target, unsigne
 
 }  // namespace
 
-cudaError_t launch_count_publish(const int64_t* unit_expert, int num_units, int E, int R, int me,
-                                 int32_t* const* omega_ptrs, unsigned* const* signal_ptrs, unsigned* epoch_word,
-                                 cudaStream_t stream) {
-  count_publish_kernel<<<1, 1024, sizeof(int) * E, stream>>>(unit_expert, num_units, E, R, me, omega_ptrs, signal_ptrs,
-                                                            epoch_word);
+cudaError_t launch_count_publish(const CountArgs& a, cudaStream_t stream) {
+  const int chunks = route_chunks(a.num_units);
+  if (chunks <= 0 || a.E <= 0) return cudaErrorInvalidValue;
+  count_publish_kernel<<<chunks, kRouteChunk, sizeof(int) * a.E, stream>>>(a);
   return cudaGetLastError();
 }
 
-cudaError_t launch_route_assign(const int64_t* unit_expert, int num_units, int E, int R, const int32_t* q_me,
-                                const int32_t* row_base, int32_t* unit_dst, int32_t* unit_row, int* status,
-                                cudaStream_t stream) {
-  const size_t smem = sizeof(int) * (2 * R + 1 + 32);
-  route_assign_kernel<<<E, 1024, smem, stream>>>(unit_expert, num_units, E, R, q_me, row_base, unit_dst, unit_row, status);
+cudaError_t launch_route_assign(const RouteArgs& a, cudaStream_t stream) {
+  const int chunks = route_chunks(a.num_units);
+  if (chunks <= 0) return cudaErrorInvalidValue;
+  const size_t smem = sizeof(int) * (size_t)a.E * (1 + kRouteChunk / 32);
+  if (smem > 48 * 1024) return cudaErrorInvalidValue;  // E <= 1365
+  route_assign_kernel<<<chunks, kRouteChunk, smem, stream>>>(a);
   return cudaGetLastError();
 }
 
-cudaError_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream) {
-  if (a.H % 8 != 0) return cudaErrorInvalidValue;
-  const int wpb = 8;
-  const int unit_blocks = ceil_div(a.num_units, wpb);
-  dispatch_kernel<<<unit_blocks + a.n_slot, wpb * 32, 0, stream>>>(a, unit_blocks);
+cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_t stream) {
+  if (a.H % 8 != 0 || a.block_rows <= 0 || a.tile_rows % a.block_rows != 0 || a.tile_rows % 32 != 0) return cudaErrorInvalidValue;
+  if (a.w1_elems % 8 != 0 || a.w2_elems % 8 != 0) return cudaErrorInvalidValue;
+  if (num_sms <= 0) num_sms = sm_count();
+  const bool bwd = a.unit_scale != nullptr || a.saved_out != nullptr;
+  static bool configured[2][kMaxTrackedDevices] = {};
+  int dev;
+  if (device_needs_setup(configured[bwd], &dev)) {
+    cudaError_t e = bwd ? cudaFuncSetAttribute(comm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommKernelSmem)
+                        : cudaFuncSetAttribute(comm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommKernelSmem);
+    if (e != cudaSuccess) return e;
+    device_setup_done(configured[bwd], dev);
+  }
+  // one CTA per SM: 8 warps x 3 segments of 4 KB in flight
+  if (bwd) comm_kernel<true><<<num_sms, kCommKernelWarps * 32, kCommKernelSmem, stream>>>(a, status);
+  else comm_kernel<false><<<num_sms, kCommKernelWarps * 32, kCommKernelSmem, stream>>>(a, status);
   return cudaGetLastError();
 }
 
 cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, void* out, int num_tokens, int topk,
-                               int H, cudaStream_t stream) {
+                               int H, const UnitReduceWait* wait, cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
   const int wpb = 8;
   const long long items = (long long)num_tokens * ceil_div(H / 8, 32);
   if (items == 0) return cudaSuccess;
+  UnitReduceWait w{};
+  if (wait != nullptr) w = *wait;
   unit_reduce_kernel<<<(unsigned)((items + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
-      reinterpret_cast<const uint4*>(unit_rows), unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8);
+      reinterpret_cast<const uint4*>(unit_rows), unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8, w);
   return cudaGetLastError();
 }
 
@@ -420,7 +424,7 @@ cudaError_t launch_weight_pull(const WeightPullArgs& a, cudaStream_t stream) {
   if (a.elems_per_slot % 8 != 0) return cudaErrorInvalidValue;
   // about two waves of CTAs over all replica slots: a pull of one or two experts must still keep
   // enough 16-byte peer loads in flight to fill NVLink
-  int gx = (2 * 148 + replica_slots - 1) / replica_slots;
+  int gx = (2 * sm_count() + replica_slots - 1) / replica_slots;
   if (gx < 32) gx = 32;
   if (gx > 160) gx = 160;
   dim3 grid(gx, replica_slots);
@@ -430,8 +434,8 @@ cudaError_t launch_weight_pull(const WeightPullArgs& a, cudaStream_t stream) {
 
 cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream) {
   if (a.home_cap <= 0) return cudaSuccess;
-  if (a.elems_per_slot % 8 != 0 || a.R > 64) return cudaErrorInvalidValue;
-  int gx = (2 * 148 + a.home_cap - 1) / a.home_cap;  // about two waves of CTAs in total
+  if (a.elems_per_slot % 8 != 0 || a.R > kMaxGradHosts) return cudaErrorInvalidValue;
+  int gx = (2 * sm_count() + a.home_cap - 1) / a.home_cap;  // about two waves of CTAs in total
   if (gx < 64) gx = 64;
   if (gx > 256) gx = 256;
   dim3 grid(gx, a.home_cap);
@@ -443,7 +447,7 @@ cudaError_t launch_swiglu_backward(const void* dact, void* h, int rows, int F, c
                                    cudaStream_t stream) {
   if (F % 8 != 0) return cudaErrorInvalidValue;
   if (rows <= 0) return cudaSuccess;
-  swiglu_backward_kernel<<<148 * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(dact), reinterpret_cast<uint4*>(h), rows,
+  swiglu_backward_kernel<<<sm_count() * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(dact), reinterpret_cast<uint4*>(h), rows,
                                                      F, row_limit);
   return cudaGetLastError();
 }

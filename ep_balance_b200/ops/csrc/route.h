@@ -9,44 +9,115 @@
 
 namespace epb {
 
-// Histogram of this rank's routed expert ids, stored as row `me` of omega on every peer,
-// followed by one release-add on every peer's signal word.
+// Units are counted and ranked in chunks of kRouteChunk consecutive units, one CTA per chunk.
+constexpr int kRouteChunk = 256;
+inline int route_chunks(int num_units) { return (num_units + kRouteChunk - 1) / kRouteChunk; }
+
+// Histogram of this rank's routed expert ids (one CTA per chunk; per-chunk histograms are kept for the
+// route assignment).  The last CTA to finish stores the histogram as row `me` of omega on every peer,
+// writes its exclusive prefix to `exp_prefix`, clears this rank's arrival counters (`clear_words`
+// 32-bit words at `clear`, may be null) and then adds 1 (release) to every peer's signal word.
 // `epoch_word` (local, may be null) is advanced by one per call.
-cudaError_t launch_count_publish(const int64_t* unit_expert, int num_units, int E, int R, int me,
-                                 int32_t* const* omega_ptrs, unsigned* const* signal_ptrs, unsigned* epoch_word,
-                                 cudaStream_t stream);
-
-// Unit -> (dst rank, row in dst's receive buffers).  q_me = q[me] as [E, R]; row_base from the
-// solver's RankTables.
-cudaError_t launch_route_assign(const int64_t* unit_expert, int num_units, int E, int R,
-                                const int32_t* q_me, const int32_t* row_base, int32_t* unit_dst,
-                                int32_t* unit_row, int* status, cudaStream_t stream);
-
-// Copy (optionally scale) token rows into the peers' receive buffers and write {src rank, unit}
-// beside each row.  Also zero-fills this rank's own padding rows (slot_off/slot_rows layout).
-// With `saved_out != nullptr` also computes unit_dot[u] = <rows[t(u)], saved_out[u]> (the gate
-// weight gradient) in the same pass.
-struct DispatchArgs {
-  const void* rows;             // bf16 [num_tokens, H]
-  const float* unit_scale;      // [U] or null
-  const void* saved_out;        // bf16 [U, H] or null
-  float* unit_dot;              // [U] or null
-  int num_units, topk, H, R, me;
-  const int32_t* unit_dst;      // [U]
-  const int32_t* unit_row;      // [U]
-  void* const* buf_ptrs;        // R peers: bf16 [row_capacity, H]
-  int2* const* meta_ptrs;       // R peers: int2 [row_capacity] or null
-  void* local_buf;              // this rank's receive buffer (pad rows are zeroed here)
-  const int32_t* slot_off;      // [n_slot + 1]
-  const int32_t* slot_rows;     // [n_slot]
-  int n_slot;
-  int row_capacity;              // rows of every peer buffer; rows past it are dropped
+struct CountArgs {
+  const int64_t* unit_expert;   // [U]
+  int num_units, E, R, me;
+  int32_t* chunk_hist;          // [route_chunks(U), E]
+  int32_t* hist_acc;            // [E + 1]: running histogram (zero between calls) and, last, the CTA ticket
+  int32_t* exp_prefix;          // [E + 1]
+  int32_t* const* omega_ptrs;   // R peers: int32 [R, E]
+  unsigned* const* signal_ptrs; // R peers (may be null)
+  unsigned* epoch_word;
+  unsigned* clear;
+  int clear_words;
 };
-cudaError_t launch_dispatch(const DispatchArgs& a, cudaStream_t stream);
+cudaError_t launch_count_publish(const CountArgs& a, cudaStream_t stream);
+
+// Unit -> (dst rank, row in dst's receive buffers), plus the units ordered by expert.  The j-th unit
+// (original order) of expert e goes to the host whose quota prefix covers j (eplb/integration/
+// physical.py:30-77).  q_me = q[me] as [E, R]; row_base from the solver's RankTables; chunk_hist and
+// exp_prefix from launch_count_publish over the same units.  O(U) work: one CTA per chunk of units.
+struct RouteArgs {
+  const int64_t* unit_expert;
+  int num_units, E, R;
+  const int32_t* q_me;
+  const int32_t* row_base;
+  const int32_t* chunk_hist;
+  const int32_t* exp_prefix;
+  int32_t* unit_dst;            // [U]
+  int32_t* unit_row;            // [U]
+  int32_t* sorted_units;        // [U] (may be null)
+  int* status;
+};
+cudaError_t launch_route_assign(const RouteArgs& a, cudaStream_t stream);
+
+// ---------------------------------------------------------------------------------------------
+// Item-driven token transport ("comm"), run either by a stand-alone kernel or by the spare warps of
+// the grouped GEMM kernel that consumes the rows (grouped_gemm.cu), so that the transfer overlaps
+// the tensor-core tiles.
+//
+// The sender walks the RECEIVERS' buffers block by block (block = `block_rows` consecutive rows of a
+// peer's receive buffer, lowest rows first, peers visited round-robin starting with itself).  For
+// every block it stores the rows it owes there -- the plan fixes the final row of every unit, so no
+// size exchange is needed -- and then adds 1 (release, system scope) to the peer's arrival counter of
+// the GEMM M-tile holding the block.  Every sender signals every block of every used tile, also when
+// it owes no row there, so a tile is complete when its counter reaches R * (tile_rows / block_rows).
+// Rows therefore arrive in the order the consuming GEMM walks its tile list.
+// The same walk moves replica weights (peer loads from the owner's home slot, one counter per
+// replica slot and weight tensor) and zero-fills this rank's own padding rows.
+// Reference counterparts: all_to_all_single dispatch + slot sort (eplb/integration/comm.py:18-36,
+// eplb_manager.py:1067-1105), replica broadcast (overlap.py:113-148).
+struct CommArgs {
+  int do_dispatch, do_pad, do_pull;
+  int R, me, E, H, topk, row_capacity;
+  int tile_rows;                 // rows of a GEMM M-tile (arrival-counter granularity)
+  int block_rows;                // rows of a transport block; divides tile_rows
+  // ---- rows to send
+  const void* rows;              // bf16 [num_tokens, H]
+  const float* unit_scale;       // [U] or null: rows are multiplied by it (gate weight, backward)
+  const void* saved_out;         // bf16 [U, H] or null: unit_dot[u] = <rows[t(u)], saved_out[u]>
+  float* unit_dot;               // [U] or null
+  const int32_t* sorted_units;   // [U] this rank's units ordered by expert (stable)
+  const int32_t* exp_prefix;     // [E + 1] first position of each expert in sorted_units
+  const int32_t* q_me;           // [E, R] units (me, e) -> dst
+  const int32_t* row_base;       // [E, R] first row in dst's buffer for (me, e) -> dst, -1 if none
+  const int32_t* send_off;       // [E, R] units of expert e that go to ranks below dst
+  const int32_t* tiles_of;       // [R] used M-tiles of every rank's receive buffer
+  void* const* buf_ptrs;         // R peers: bf16 [row_capacity, H]
+  int2* const* meta_ptrs;        // R peers: int2 [row_capacity] ({src rank, unit}) or null
+  unsigned* const* arrive_ptrs;  // R peers: base of the counter region
+  int arrive_off;                // first word of the arrival counters [row_capacity / tile_rows] in that region
+  // ---- padding rows of this rank
+  void* local_buf;
+  const int32_t* group_off;      // [n_groups_cap + 1]
+  const int32_t* group_rows;     // [n_groups_cap]
+  int n_groups_cap;
+  // ---- replica weights
+  int home_cap, w_slots;
+  const int32_t* group_expert;   // [n_groups_cap]
+  const int32_t* group_wslot;    // [n_groups_cap]
+  const int32_t* main_rank;      // [E]
+  const int32_t* home_index;     // [E]
+  void* const* w1_ptrs;          // R peers: bf16 [w_slots, w1_elems]
+  void* const* w2_ptrs;
+  size_t w1_elems, w2_elems;     // elements per slot (multiples of 8)
+  unsigned* pull_cnt;            // local [2, w_slots - home_cap]: chunks landed per weight tensor and replica slot
+};
+constexpr int kPullChunkBytes = 32768;
+__host__ __device__ inline unsigned pull_chunks(size_t elems) { return (unsigned)((elems * 2 + kPullChunkBytes - 1) / kPullChunkBytes); }
+cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_t stream);
 
 // out[t] = sum_k scale[t*topk+k] * rows[t*topk+k]   (scale may be null: plain sum)
+// With `wait_signal != nullptr` every CTA first waits (bounded) until *wait_signal >= *wait_epoch * R:
+// the peers' "all my rows are stored" signals of the producing GEMM (GemmArgs::done_*).
+struct UnitReduceWait {
+  const unsigned* signal;       // this rank's signal word
+  const unsigned* epoch;        // local epoch word
+  int R;
+  unsigned long long budget_ns;
+  int* status;
+};
 cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, void* out, int num_tokens,
-                               int topk, int H, cudaStream_t stream);
+                               int topk, int H, const UnitReduceWait* wait, cudaStream_t stream);
 
 // Cross-rank barrier on symmetric signal words: every rank adds 1 to word `slot` of every peer,
 // then waits (bounded) until its own word reaches (epoch+1)*R.  `epoch_word` lives in local

@@ -1,13 +1,18 @@
 // MoeRuntime: wires one layer's buffers into the solver, routing and grouped-GEMM kernels.
 //
-// Step order (forward):  publish -> solve -> route -> dispatch -> pull -> [barrier] -> gemm1 ->
-// gemm2 (rows scattered to source ranks) -> [barrier] -> reduce_out.
-// Step order (backward): dispatch_grads (+ gate grads) -> [barrier] -> wgrad2 -> dgrad2 (+ SwiGLU gradient
-// pass) -> wgrad1 -> dgrad1 (rows scattered) -> [barrier] -> reduce_dtokens -> reduce_weight_grads.
+// Forward:  count+publish -> solve -> route -> [dispatch + replica pull + GEMM1, one kernel] -> GEMM2
+// (rows stored to their source ranks, completion signalled to every peer by the last CTA) ->
+// reduce_out (waits in the kernel for the peers' signals).
+// Backward: [gradient dispatch + gate gradients + Dgrad2, one kernel] -> SwiGLU-gradient pass -> Wgrad2 ->
+// Wgrad1 -> Dgrad1 (rows stored to sources, completion signalled) -> reduce_dtokens (waits); beside
+// Dgrad1, on the runtime's side stream: cross-rank barrier -> owners add their replicas' weight gradients.
+// There is no stand-alone barrier on the critical path: consumers of transferred rows wait per M-tile
+// on arrival counters that the senders advance, consumers of combined rows on one signal per peer.
 // Inference with fp8 experts: publish -> solve -> route -> dispatch fused with the 1 x 128 quantisation ->
 // fp8 replica pull -> [barrier] -> fp8 gemm1 -> SwiGLU + quantise -> fp8 gemm2 (scattered) -> [barrier] -> reduce_out.
-// This is the schedule the reference drives from Python over NCCL (eplb_manager.py:905-1167,
-// manual_block.py:127-367), restated as a fixed sequence of device-side kernels.
+// This is the schedule the reference drives from Python over NCCL on three streams
+// (eplb_manager.py:710-886, 905-1167, manual_block.py:127-367, overlap.py:257-328), restated as
+// device-side kernels that overlap transfer and compute tile by tile.
 #include "runtime.h"
 
 #include <stdexcept>
@@ -26,7 +31,15 @@ T* MoeRuntime::ptr(const char* name, bool required) const {
 
 void MoeRuntime::check(cudaError_t e, const char* what) {
   ++launches_;
+  if (trace_) launch_log_.emplace_back(on_side_ ? std::string("side:") + what : std::string(what));
   if (e != cudaSuccess) throw std::runtime_error(std::string("MoeRuntime: ") + what + ": " + cudaGetErrorString(e));
+}
+
+MoeRuntime::~MoeRuntime() {
+  for (auto& m : marks_) cudaEventDestroy(m.second);
+  if (ev_fork_) cudaEventDestroy(ev_fork_);
+  if (ev_join_) cudaEventDestroy(ev_join_);
+  if (side_) cudaStreamDestroy(side_);
 }
 
 void MoeRuntime::tmap2(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br) {
@@ -42,6 +55,23 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
   if (c.H % 64 || c.F % 128) throw std::runtime_error("MoeRuntime: need H % 64 == 0 and F % 128 == 0");
   if (c.gemm_ctas != 1 && c.gemm_ctas != 2) throw std::runtime_error("MoeRuntime: gemm_ctas must be 1 or 2");
   if (c.row_capacity % (128 * c.gemm_ctas)) throw std::runtime_error("MoeRuntime: row_capacity must be a multiple of the GEMM M tile");
+  if (c.R > 64) throw std::runtime_error("MoeRuntime: the fused layer supports at most 64 expert-parallel ranks (gradient-return host lists)");
+  tile_rows_ = 128 * c.gemm_ctas;
+  n_tiles_ = c.row_capacity / tile_rows_;
+  block_rows_ = c.comm_block_rows;
+  if (block_rows_ <= 0) {
+    block_rows_ = 32;
+    while (block_rows_ * 2 <= tile_rows_ && block_rows_ * 2 <= 32 * c.R) block_rows_ *= 2;
+  }
+  if (block_rows_ % 32 || tile_rows_ % block_rows_) throw std::runtime_error("MoeRuntime: comm_block_rows must be a multiple of 32 that divides the GEMM M tile");
+  if (c.wait_ms <= 0 || c.wait_ms > 60000) throw std::runtime_error("MoeRuntime: wait_ms must be in (0, 60000]");
+  wait_ns_ = (unsigned long long)c.wait_ms * 1000000ull;
+  if (c.multi_rank_sync && c.R > 1) {
+    if (cudaStreamCreateWithFlags(&side_, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming) != cudaSuccess)
+      throw std::runtime_error("MoeRuntime: could not create the side stream");
+  }
 
   sp_.omega = ptr<const int32_t>("omega");
   sp_.dom = ptr<const int32_t>("dom");
@@ -84,6 +114,9 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
   tables_.group_off = ptr<int32_t>("group_off");
   tables_.group_rows = ptr<int32_t>("group_rows");
   tables_.totals = ptr<int32_t>("totals");
+  tables_.send_off = ptr<int32_t>("send_off");
+  tables_.tiles_of = ptr<int32_t>("tiles_of");
+  for (const char* name : {"arrive", "arrive_ptrs", "chunk_hist", "hist_acc", "exp_prefix", "sorted_units", "done_ctr"}) ptr<void>(name);
 
   const uint64_t T = c.row_capacity, H = c.H, F = c.F, S = c.w_slots;
   // K-major A operands: box {64 k, 128 rows}
@@ -130,58 +163,98 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
 
 // ------------------------------------------------------------------ forward pieces
 void MoeRuntime::publish(const int64_t* topk_idx, int num_units, cudaStream_t stream) {
-  check(launch_count_publish(topk_idx, num_units, cfg_.E, cfg_.R, cfg_.me, ptr<int32_t* const>("omega_ptrs"),
-                             ptr<unsigned* const>("signal_ptrs"), ptr<unsigned>("epochs"), stream),
-        "count_publish");
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  CountArgs a{};
+  a.unit_expert = topk_idx;
+  a.num_units = num_units;
+  a.E = cfg_.E;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.chunk_hist = ptr<int32_t>("chunk_hist");
+  a.hist_acc = ptr<int32_t>("hist_acc");
+  a.exp_prefix = ptr<int32_t>("exp_prefix");
+  a.omega_ptrs = ptr<int32_t* const>("omega_ptrs");
+  a.signal_ptrs = ptr<unsigned* const>("signal_ptrs");
+  a.epoch_word = ptr<unsigned>("epochs");
+  // arrival counters (forward, backward) and replica pull counters of this rank start every step at zero;
+  // peers add to them only after their solver has seen this rank's signal
+  a.clear = ptr<unsigned>("arrive");
+  a.clear_words = 2 * n_tiles_ + 2 * (cfg_.w_slots - cfg_.home_cap);
+  check(launch_count_publish(a, stream), "count_publish");
 }
 
 void MoeRuntime::solve(cudaStream_t stream) { check(launch_solver(sp_, tables_, stream), "solver"); }
 
 void MoeRuntime::route(const int64_t* topk_idx, int num_units, cudaStream_t stream) {
   if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
-  const int32_t* q_me = sp_.q + (size_t)cfg_.me * cfg_.E * cfg_.R;
-  check(launch_route_assign(topk_idx, num_units, cfg_.E, cfg_.R, q_me, tables_.row_base, ptr<int32_t>("unit_dst"),
-                            ptr<int32_t>("unit_row"), sp_.status, stream),
-        "route_assign");
+  RouteArgs a{};
+  a.unit_expert = topk_idx;
+  a.num_units = num_units;
+  a.E = cfg_.E;
+  a.R = cfg_.R;
+  a.q_me = sp_.q + (size_t)cfg_.me * cfg_.E * cfg_.R;
+  a.row_base = tables_.row_base;
+  a.chunk_hist = ptr<const int32_t>("chunk_hist");
+  a.exp_prefix = ptr<const int32_t>("exp_prefix");
+  a.unit_dst = ptr<int32_t>("unit_dst");
+  a.unit_row = ptr<int32_t>("unit_row");
+  a.sorted_units = ptr<int32_t>("sorted_units");
+  a.status = sp_.status;
+  check(launch_route_assign(a, stream), "route_assign");
+}
+
+CommArgs MoeRuntime::comm_args(bool dispatch, bool pad, bool pull) const {
+  CommArgs a{};
+  a.do_dispatch = dispatch;
+  a.do_pad = pad;
+  a.do_pull = pull && cfg_.w_slots > cfg_.home_cap;
+  a.R = cfg_.R;
+  a.me = cfg_.me;
+  a.E = cfg_.E;
+  a.H = cfg_.H;
+  a.topk = cfg_.topk;
+  a.row_capacity = cfg_.row_capacity;
+  a.tile_rows = tile_rows_;
+  a.block_rows = block_rows_;
+  a.sorted_units = ptr<const int32_t>("sorted_units");
+  a.exp_prefix = ptr<const int32_t>("exp_prefix");
+  a.q_me = sp_.q + (size_t)cfg_.me * cfg_.E * cfg_.R;
+  a.row_base = tables_.row_base;
+  a.send_off = tables_.send_off;
+  a.tiles_of = tables_.tiles_of;
+  a.arrive_ptrs = ptr<unsigned* const>("arrive_ptrs");
+  a.group_off = tables_.group_off;
+  a.group_rows = tables_.group_rows;
+  a.n_groups_cap = cfg_.w_slots;
+  a.home_cap = cfg_.home_cap;
+  a.w_slots = cfg_.w_slots;
+  a.group_expert = tables_.group_expert;
+  a.group_wslot = tables_.group_wslot;
+  a.main_rank = sp_.main_rank;
+  a.home_index = tables_.home_index;
+  a.w1_ptrs = ptr<void* const>("w1_ptrs");
+  a.w2_ptrs = ptr<void* const>("w2_ptrs");
+  a.w1_elems = (size_t)2 * cfg_.F * cfg_.H;
+  a.w2_elems = (size_t)cfg_.F * cfg_.H;
+  a.pull_cnt = ptr<unsigned>("arrive") + 2 * n_tiles_;
+  return a;
 }
 
 void MoeRuntime::dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream, bool zero_pad) {
-  DispatchArgs a{};
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  CommArgs a = comm_args(true, zero_pad, false);
   a.rows = tokens;
-  a.num_units = num_units;
-  a.topk = cfg_.topk;
-  a.H = cfg_.H;
-  a.R = cfg_.R;
-  a.me = cfg_.me;
-  a.unit_dst = ptr<const int32_t>("unit_dst");
-  a.unit_row = ptr<const int32_t>("unit_row");
   a.buf_ptrs = ptr<void* const>("xbuf_ptrs");
   a.meta_ptrs = ptr<int2* const>("meta_ptrs");
   a.local_buf = ptr<void>("xbuf");
-  a.slot_off = tables_.group_off;
-  a.slot_rows = tables_.group_rows;
-  a.n_slot = zero_pad ? cfg_.w_slots : 0;
-  a.row_capacity = cfg_.row_capacity;
-  check(launch_dispatch(a, stream), "dispatch");
+  a.arrive_off = 0;
+  check(launch_comm(a, cfg_.num_sms, sp_.status, stream), "dispatch");
 }
 
 void MoeRuntime::pull_weights(cudaStream_t stream) {
   if (cfg_.w_slots <= cfg_.home_cap) return;
-  WeightPullArgs a{};
-  a.slot_of = tables_.slot_of;
-  a.main_rank = sp_.main_rank;
-  a.home_index = tables_.home_index;
-  a.E = cfg_.E;
-  a.R = cfg_.R;
-  a.me = cfg_.me;
-  a.home_cap = cfg_.home_cap;
-  a.n_slot = cfg_.w_slots;
-  a.w_ptrs = ptr<void* const>("w1_ptrs");
-  a.elems_per_slot = (size_t)2 * cfg_.F * cfg_.H;
-  check(launch_weight_pull(a, stream), "weight_pull(w1)");
-  a.w_ptrs = ptr<void* const>("w2_ptrs");
-  a.elems_per_slot = (size_t)cfg_.F * cfg_.H;
-  check(launch_weight_pull(a, stream), "weight_pull(w2)");
+  CommArgs a = comm_args(false, false, true);
+  check(launch_comm(a, cfg_.num_sms, sp_.status, stream), "weight_pull");
 }
 
 void MoeRuntime::barrier(int slot, cudaStream_t stream) {
@@ -192,7 +265,7 @@ void MoeRuntime::barrier(int slot, cudaStream_t stream) {
 }
 
 void MoeRuntime::gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int N, int K, int M_out, void* out0,
-                      void* out1, void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
+                      void* out1, void* const* out_ptrs, const int2* meta, cudaStream_t stream, const GemmExtra& extra) {
   GemmArgs g{};
   g.mode = mode;
   g.ctas = cfg_.gemm_ctas;
@@ -210,18 +283,67 @@ void MoeRuntime::gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int 
   g.out_ptrs = out_ptrs;
   g.meta = meta;
   g.status = sp_.status;
-  check(launch_grouped_gemm(a, b, g, cfg_.num_sms, stream), "grouped_gemm");
+  g.wait_ns = wait_ns_;
+  if (extra.gate) {
+    g.arrive = ptr<const unsigned>("arrive") + (extra.gate == 2 ? n_tiles_ : 0);
+    g.arrive_expected = (unsigned)(cfg_.R * (tile_rows_ / block_rows_));
+  }
+  if (extra.gate_pull && cfg_.w_slots > cfg_.home_cap) {
+    g.pull_cnt = ptr<const unsigned>("arrive") + 2 * n_tiles_;  // counters of w1 (the B operand of GEMM1)
+    g.pull_expected = pull_chunks((size_t)2 * cfg_.F * cfg_.H);
+    g.home_cap = cfg_.home_cap;
+  }
+  if (extra.done_slot > 0 && peers()) {
+    g.done_ctr = ptr<unsigned>("done_ctr");
+    g.done_epoch = ptr<unsigned>("epochs") + extra.done_slot;
+    g.done_signal_ptrs = ptr<unsigned* const>("signal_ptrs");
+    g.done_slot = extra.done_slot;
+    g.done_R = cfg_.R;
+  }
+  if (extra.comm != nullptr) g.comm = *extra.comm;
+  check(launch_grouped_gemm(a, b, g, cfg_.num_sms, stream), extra.comm ? "grouped_gemm+transport" : "grouped_gemm");
 }
 
 void MoeRuntime::gemm1(cudaStream_t stream) {
-  gemm(kFwd1, tm_x_k_, tm_w1_k_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), ptr<void>("act"), nullptr, nullptr, stream);
+  GemmExtra x;
+  x.gate = 1;
+  x.gate_pull = true;
+  gemm(kFwd1, tm_x_k_, tm_w1_k_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), ptr<void>("act"), nullptr, nullptr, stream, x);
+}
+void MoeRuntime::gemm1_fused(const void* tokens, int num_units, cudaStream_t stream) {
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  CommArgs a = comm_args(true, true, true);
+  a.rows = tokens;
+  a.buf_ptrs = ptr<void* const>("xbuf_ptrs");
+  a.meta_ptrs = ptr<int2* const>("meta_ptrs");
+  a.local_buf = ptr<void>("xbuf");
+  a.arrive_off = 0;
+  GemmExtra x;
+  x.gate = 1;
+  x.gate_pull = true;
+  x.comm = &a;
+  gemm(kFwd1, tm_x_k_, tm_w1_k_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), ptr<void>("act"), nullptr, nullptr, stream, x);
 }
 void MoeRuntime::gemm2(cudaStream_t stream) {
+  GemmExtra x;
+  x.done_slot = 2;
   gemm(kFwd2, tm_act_k_, tm_w2_k_, cfg_.H, cfg_.F, 0, nullptr, nullptr, ptr<void* const>("ybuf_ptrs"),
-       ptr<const int2>("meta"), stream);
+       ptr<const int2>("meta"), stream, x);
 }
-void MoeRuntime::reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream) {
-  check(launch_unit_reduce(ptr<void>("ybuf"), topk_prob, out, num_tokens, cfg_.topk, cfg_.H, stream), "unit_reduce");
+UnitReduceWait MoeRuntime::reduce_wait(int slot) const {
+  UnitReduceWait w{};
+  w.signal = ptr<const unsigned>("signals") + slot;
+  w.epoch = ptr<const unsigned>("epochs") + slot;
+  w.R = cfg_.R;
+  w.budget_ns = wait_ns_;
+  w.status = sp_.status;
+  return w;
+}
+void MoeRuntime::reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream, bool wait_peers) {
+  const UnitReduceWait w = reduce_wait(2);
+  check(launch_unit_reduce(ptr<void>("ybuf"), topk_prob, out, num_tokens, cfg_.topk, cfg_.H,
+                           wait_peers && peers() ? &w : nullptr, stream),
+        "unit_reduce");
 }
 
 // ------------------------------------------------------------------ block-scaled fp8 forward
@@ -342,41 +464,61 @@ void MoeRuntime::forward_fp8(const void* tokens, const int64_t* topk_idx, const 
 // ------------------------------------------------------------------ backward pieces
 void MoeRuntime::dispatch_grads(const void* dout, const float* topk_prob, float* dprob, int num_units,
                                 cudaStream_t stream) {
-  DispatchArgs a{};
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  CommArgs a = comm_args(true, true, false);
   a.rows = dout;
   a.unit_scale = topk_prob;
   a.saved_out = ptr<void>("ybuf");
   a.unit_dot = dprob;
-  a.num_units = num_units;
-  a.topk = cfg_.topk;
-  a.H = cfg_.H;
-  a.R = cfg_.R;
-  a.me = cfg_.me;
-  a.unit_dst = ptr<const int32_t>("unit_dst");
-  a.unit_row = ptr<const int32_t>("unit_row");
   a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
   a.meta_ptrs = nullptr;
   a.local_buf = ptr<void>("dybuf");
-  a.slot_off = tables_.group_off;
-  a.slot_rows = tables_.group_rows;
-  a.n_slot = cfg_.w_slots;
-  a.row_capacity = cfg_.row_capacity;
-  check(launch_dispatch(a, stream), "dispatch_grads");
+  a.arrive_off = n_tiles_;
+  check(launch_comm(a, cfg_.num_sms, sp_.status, stream), "dispatch_grads");
 }
 void MoeRuntime::wgrad2(cudaStream_t stream) {
-  gemm(kWgrad, tm_dy_mn_, tm_act_mn_, cfg_.F, 0, cfg_.H, ptr<void>("gw2"), nullptr, nullptr, nullptr, stream);
+  GemmExtra x;
+  x.gate = 2;
+  gemm(kWgrad, tm_dy_mn_, tm_act_mn_, cfg_.F, 0, cfg_.H, ptr<void>("gw2"), nullptr, nullptr, nullptr, stream, x);
 }
 void MoeRuntime::dgrad2(cudaStream_t stream) {
+  GemmExtra x;
+  x.gate = 2;
   void* dact = ptr<void>("dact", false);
   if (dact == nullptr || cfg_.fused_dgrad2) {
     // SwiGLU gradient inside the GEMM epilogue (reads and rewrites the saved pre-activations row by row)
-    gemm(kDgrad2, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), nullptr, nullptr, nullptr, stream);
+    gemm(kDgrad2, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), nullptr, nullptr, nullptr, stream, x);
     return;
   }
   // Plain Dgrad GEMM into `dact`, then one coalesced elementwise pass: the fused epilogue's per-row
   // global loads of the pre-activations are latency-bound and keep the tensor pipe at ~40 %, so the two
   // launches together are faster than the fused one.
-  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, dact, nullptr, nullptr, nullptr, stream);
+  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, dact, nullptr, nullptr, nullptr, stream, x);
+  check(launch_swiglu_backward(dact, ptr<void>("hbuf"), cfg_.row_capacity, cfg_.F, tables_.totals, stream),
+        "swiglu_backward");
+}
+void MoeRuntime::dgrad2_fused(const void* dout, const float* topk_prob, float* dprob, int num_units,
+                              cudaStream_t stream) {
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  void* dact = ptr<void>("dact", false);
+  if (dact == nullptr || cfg_.fused_dgrad2) {  // no plain-Dgrad2 buffer: transport first, then the in-place variant
+    dispatch_grads(dout, topk_prob, dprob, num_units, stream);
+    dgrad2(stream);
+    return;
+  }
+  CommArgs a = comm_args(true, true, false);
+  a.rows = dout;
+  a.unit_scale = topk_prob;
+  a.saved_out = ptr<void>("ybuf");
+  a.unit_dot = dprob;
+  a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
+  a.meta_ptrs = nullptr;
+  a.local_buf = ptr<void>("dybuf");
+  a.arrive_off = n_tiles_;
+  GemmExtra x;
+  x.gate = 2;
+  x.comm = &a;
+  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, dact, nullptr, nullptr, nullptr, stream, x);
   check(launch_swiglu_backward(dact, ptr<void>("hbuf"), cfg_.row_capacity, cfg_.F, tables_.totals, stream),
         "swiglu_backward");
 }
@@ -384,11 +526,16 @@ void MoeRuntime::wgrad1(cudaStream_t stream) {
   gemm(kWgrad, tm_dh_mn_, tm_x_mn_, cfg_.H, 0, 2 * cfg_.F, ptr<void>("gw1"), nullptr, nullptr, nullptr, stream);
 }
 void MoeRuntime::dgrad1(cudaStream_t stream) {
+  GemmExtra x;
+  x.done_slot = 4;
   gemm(kDgrad1, tm_dh_k_, tm_w1_mn_, cfg_.H, 2 * cfg_.F, 0, nullptr, nullptr, ptr<void* const>("dxbuf_ptrs"),
-       ptr<const int2>("meta"), stream);
+       ptr<const int2>("meta"), stream, x);
 }
-void MoeRuntime::reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream) {
-  check(launch_unit_reduce(ptr<void>("dxbuf"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H, stream), "unit_reduce(bwd)");
+void MoeRuntime::reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream, bool wait_peers) {
+  const UnitReduceWait w = reduce_wait(4);
+  check(launch_unit_reduce(ptr<void>("dxbuf"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H,
+                           wait_peers && peers() ? &w : nullptr, stream),
+        "unit_reduce(bwd)");
 }
 void MoeRuntime::reduce_weight_grads(cudaStream_t stream) {
   void* acc1 = ptr<void>("acc_gw1", false);
@@ -452,19 +599,19 @@ void MoeRuntime::forward(const void* tokens, const int64_t* topk_idx, const floa
   mark("solve", stream);
   route(topk_idx, U, stream);
   mark("route", stream);
-  dispatch_tokens(tokens, U, stream);
-  mark("dispatch", stream);
-  pull_weights(stream);
-  mark("pull_weights", stream);
-  barrier(1, stream);
-  mark("barrier1", stream);
-  gemm1(stream);
-  mark("gemm1", stream);
+  if (cfg_.fused_comm) {
+    gemm1_fused(tokens, U, stream);
+    mark("dispatch+pull+gemm1", stream);
+  } else {
+    dispatch_tokens(tokens, U, stream);
+    pull_weights(stream);
+    mark("dispatch+pull", stream);
+    gemm1(stream);
+    mark("gemm1", stream);
+  }
   gemm2(stream);
   mark("gemm2", stream);
-  barrier(2, stream);
-  mark("barrier2", stream);
-  reduce_out(topk_prob, out, num_tokens, stream);
+  reduce_out(topk_prob, out, num_tokens, stream, true);
   mark("reduce_out", stream);
   mark("fwd_end", stream);
 }
@@ -473,23 +620,41 @@ void MoeRuntime::backward(const void* dout, const float* topk_prob, void* dtoken
                           cudaStream_t stream) {
   const int U = num_tokens * cfg_.topk;
   mark("bwd_begin", stream);
-  dispatch_grads(dout, topk_prob, dprob, U, stream);
-  mark("dispatch_grads", stream);
-  barrier(3, stream);
-  mark("barrier3", stream);
+  if (cfg_.fused_comm) {
+    dgrad2_fused(dout, topk_prob, dprob, U, stream);
+    mark("dispatch_grads+dgrad2", stream);
+  } else {
+    dispatch_grads(dout, topk_prob, dprob, U, stream);
+    mark("dispatch_grads", stream);
+    dgrad2(stream);
+    mark("dgrad2", stream);
+  }
   wgrad2(stream);
   mark("wgrad2", stream);
-  dgrad2(stream);
-  mark("dgrad2", stream);
   wgrad1(stream);
   mark("wgrad1", stream);
+  const bool side = peers() && side_ != nullptr;
+  if (side) {
+    // Gradient return beside Dgrad1: once every rank has finished its weight-gradient GEMMs (barrier on
+    // the side stream), each owner adds its replicas' slots with peer loads.  Dgrad1 is bound by its
+    // outbound row stores, the return by inbound loads, so the two share the link without competing.
+    if (cudaEventRecord(ev_fork_, stream) != cudaSuccess || cudaStreamWaitEvent(side_, ev_fork_, 0) != cudaSuccess)
+      throw std::runtime_error("MoeRuntime: could not fork the side stream");
+    on_side_ = true;
+    barrier(5, side_);
+    reduce_weight_grads(side_);
+    on_side_ = false;
+    if (cudaEventRecord(ev_join_, side_) != cudaSuccess) throw std::runtime_error("MoeRuntime: could not record the join event");
+  }
   dgrad1(stream);
   mark("dgrad1", stream);
-  barrier(4, stream);
-  mark("barrier4", stream);
-  reduce_dtokens(dtokens, num_tokens, stream);
+  reduce_dtokens(dtokens, num_tokens, stream, true);
   mark("reduce_dtokens", stream);
-  reduce_weight_grads(stream);
+  if (side) {
+    if (cudaStreamWaitEvent(stream, ev_join_, 0) != cudaSuccess) throw std::runtime_error("MoeRuntime: could not join the side stream");
+  } else {
+    reduce_weight_grads(stream);
+  }
   mark("reduce_weight_grads", stream);
 }
 

@@ -33,6 +33,11 @@ struct LayerConfig {
   int fused_dgrad2 = 0;     // 1: SwiGLU gradient in the Dgrad2 epilogue; 0: plain GEMM + elementwise pass (needs 'dact')
   int accum_fp32 = 0;       // dtype of the optional gradient accumulation buffers (acc_gw1/acc_gw2)
   int multi_rank_sync = 1;  // 0: one process emulates all ranks, kernels are ordered by the stream
+  int fused_comm = 1;       // 1: forward()/backward() run the token transport on spare warps of the consuming
+                            //    GEMM (dispatch + GEMM1, gradient dispatch + Dgrad2 in one kernel each);
+                            //    0: a stand-alone transport kernel runs first (the GEMM is gated either way)
+  int comm_block_rows = 0;  // rows per transport block; 0: min(M tile, 32 * R) rounded down to a power of two
+  int wait_ms = 1500;       // budget of every cross-rank wait of this layer's kernels, in milliseconds (bounded)
 };
 
 class MoeRuntime {
@@ -43,20 +48,29 @@ class MoeRuntime {
   void publish(const int64_t* topk_idx, int num_units, cudaStream_t stream);
   void solve(cudaStream_t stream);
   void route(const int64_t* topk_idx, int num_units, cudaStream_t stream);
+  // Stand-alone transport of the token rows (CommArgs in route.h): rows stored into the hosts' buffers at
+  // their final position, arrival counters advanced per M-tile.
   // zero_pad: clear the padding rows behind every group (needed when a backward pass will contract over them)
   void dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream, bool zero_pad = true);
-  void pull_weights(cudaStream_t stream);
+  void pull_weights(cudaStream_t stream);   // stand-alone replica weight pull (per-slot counters advanced)
   void barrier(int slot, cudaStream_t stream);
-  void gemm1(cudaStream_t stream);
-  void gemm2(cudaStream_t stream);
-  void reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream);
+  void gemm1(cudaStream_t stream);          // gated per M-tile on the arrival counters, per replica slot on the pull counters
+  // One kernel: transport warps send this rank's rows and pull its replica weights while the other
+  // warps run GEMM1 on the tiles whose rows have arrived.
+  void gemm1_fused(const void* tokens, int num_units, cudaStream_t stream);
+  void gemm2(cudaStream_t stream);          // rows stored to their source ranks; the last CTA signals every peer
+  // wait_peers: first wait (bounded, in the kernel) for every rank's completion signal of gemm2
+  void reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream, bool wait_peers = false);
   // ---- backward pieces
   void dispatch_grads(const void* dout, const float* topk_prob, float* dprob, int num_units, cudaStream_t stream);
   void wgrad2(cudaStream_t stream);
   void dgrad2(cudaStream_t stream);
+  // One kernel: transport warps send dout (scaled by the gate weight, with the gate-weight gradient)
+  // while the other warps run the plain Dgrad2 GEMM; followed by the SwiGLU-gradient pass.
+  void dgrad2_fused(const void* dout, const float* topk_prob, float* dprob, int num_units, cudaStream_t stream);
   void wgrad1(cudaStream_t stream);
   void dgrad1(cudaStream_t stream);
-  void reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream);
+  void reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream, bool wait_peers = false);
   void reduce_weight_grads(cudaStream_t stream);
 
   // ---- block-scaled fp8 forward (inference): present when the fp8 weight regions were given
@@ -84,13 +98,33 @@ class MoeRuntime {
   int launches() const { return launches_; }
   void reset_launches() { launches_ = 0; }
   const LayerConfig& config() const { return cfg_; }
+  // Optional launch log: the name of every kernel enqueued since trace_launches(true), in issue order
+  // ("side:" prefix for launches on the runtime's own side stream).
+  void trace_launches(bool on) { trace_ = on; launch_log_.clear(); }
+  const std::vector<std::string>& launch_log() const { return launch_log_; }
+  ~MoeRuntime();
+  MoeRuntime(const MoeRuntime&) = delete;
+  MoeRuntime& operator=(const MoeRuntime&) = delete;
 
  private:
   template <typename T>
   T* ptr(const char* name, bool required = true) const;
   void check(cudaError_t e, const char* what);
+  struct GemmExtra {
+    int gate = 0;        // 1: gate A on the forward arrival counters, 2: on the backward ones
+    bool gate_pull = false;
+    int done_slot = 0;   // > 0: signal every peer on this slot when the launch is complete
+    const CommArgs* comm = nullptr;
+  };
   void gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int N, int K, int M_out, void* out0, void* out1,
-            void* const* out_ptrs, const int2* meta, cudaStream_t stream);
+            void* const* out_ptrs, const int2* meta, cudaStream_t stream, const GemmExtra& extra);
+  void gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int N, int K, int M_out, void* out0, void* out1,
+            void* const* out_ptrs, const int2* meta, cudaStream_t stream) {
+    gemm(mode, a, b, N, K, M_out, out0, out1, out_ptrs, meta, stream, GemmExtra{});
+  }
+  CommArgs comm_args(bool dispatch, bool pad, bool pull) const;
+  bool peers() const { return cfg_.multi_rank_sync && cfg_.R > 1; }
+  UnitReduceWait reduce_wait(int slot) const;
   void tmap2(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br);
   void tmap3(CUtensorMap* m, const void* base, uint64_t slots, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br);
 
@@ -99,6 +133,13 @@ class MoeRuntime {
   SolverParams sp_{};
   RankTables tables_{};
   int launches_ = 0;
+  bool trace_ = false;
+  bool on_side_ = false;
+  std::vector<std::string> launch_log_;
+  int tile_rows_ = 256, block_rows_ = 32, n_tiles_ = 0;
+  unsigned long long wait_ns_ = 0;
+  cudaStream_t side_ = nullptr;            // gradient return runs here, beside the last GEMM of backward
+  cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr;
   bool timing_ = false;
   std::vector<std::pair<std::string, cudaEvent_t>> marks_;
   void mark(const char* name, cudaStream_t stream);

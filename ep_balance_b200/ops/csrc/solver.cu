@@ -562,6 +562,16 @@ __device__ void build_tables(const SolverParams& p, const RankTables& t, int me)
   const int R = p.R, E = p.E;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const unsigned lt = (1u << lane) - 1u;
+  if (t.send_off != nullptr && me >= 0) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int* qrow = p.q + ((size_t)me * E + e) * R;
+      int acc = 0;
+      for (int d = 0; d < R; ++d) {
+        t.send_off[(size_t)e * R + d] = acc;
+        acc += qrow[d];
+      }
+    }
+  }
   for (int h = warp; h < R; h += nwarps) {
     int groups = 0, replicas = 0, rows = 0;  // running counts / padded row offset on rank h
     for (int base = 0; base < E; base += kWarp) {
@@ -600,6 +610,10 @@ __device__ void build_tables(const SolverParams& p, const RankTables& t, int me)
       groups += __popc(m);
       replicas += __popc(mr);
       rows += __shfl_sync(kFull, incl, kWarp - 1);
+    }
+    if (t.tiles_of != nullptr && lane == 0) {
+      const int used = t.row_capacity > 0 && rows > t.row_capacity ? t.row_capacity : rows;
+      t.tiles_of[h] = used / t.row_align;
     }
     if (h == me) {
       for (int g = groups + lane; g < t.n_slot; g += kWarp) {
@@ -729,11 +743,15 @@ cudaError_t launch_solver(const SolverParams& p, const RankTables& tables, cudaS
   pc.cache_stage2 = base + solver_cache_smem(p.R, p.E) <= kCacheBudget ? 1 : 0;
   pc.cache_q = pc.cache_stage2 && base + solver_cache_smem(p.R, p.E) + solver_qcache_smem(p.R, p.E) <= kCacheBudget ? 1 : 0;
   const size_t smem = base + (pc.cache_stage2 ? solver_cache_smem(p.R, p.E) : 0) + (pc.cache_q ? solver_qcache_smem(p.R, p.E) : 0);
-  static size_t configured_smem = 48 * 1024;  // raise the kernel's dynamic shared memory limit only when needed
-  if (smem > configured_smem) {
+  // The dynamic shared-memory limit is an attribute of (kernel, device): raise it per device, only when needed.
+  constexpr int kMaxDevices = 64;
+  static size_t configured_smem[kMaxDevices] = {};
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  const size_t have = tracked && configured_smem[dev] ? configured_smem[dev] : 48 * 1024;
+  if (smem > have || (!tracked && smem > 48 * 1024)) {
     err = cudaFuncSetAttribute(solver_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return err;
-    configured_smem = smem;
+    if (tracked) configured_smem[dev] = smem;
   }
   int grid = p.D < sms ? p.D : sms;
   if (grid < 1) grid = 1;

@@ -57,6 +57,9 @@ struct RankTables {
   int32_t* group_off;     // [n_slot + 1] first row of each group; last = padded total
   int32_t* group_rows;    // [n_slot] real rows in each group
   int32_t* totals;        // [2] padded rows, number of groups
+  // optional, for the senders' transport (route.h, CommArgs):
+  int32_t* send_off;      // [E, R] units (me, e) sent to ranks below dst = sum_{d < dst} q[me, e, d] (may be null)
+  int32_t* tiles_of;      // [R] row_align-row tiles in use in every rank's receive buffer, clamped to row_capacity (may be null)
 };
 
 cudaError_t launch_solver(const SolverParams& p, const RankTables& tables, cudaStream_t stream);
