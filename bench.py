@@ -355,18 +355,18 @@ def phase_table(layer, x):
     phases = [
         ("publish", lambda: rt.publish(idx.data_ptr(), n * K)), ("solve", rt.solve),
         ("route", lambda: rt.route(idx.data_ptr(), n * K)),
-        ("dispatch", lambda: rt.dispatch_tokens(x.data_ptr(), n * K)), ("pull_weights", rt.pull_weights),
+        ("dispatch", lambda: rt.dispatch_tokens(x.data_ptr(), prob.data_ptr(), n * K)), ("pull_weights", rt.pull_weights),
         ("gemm1", rt.gemm1), ("gemm2", rt.gemm2),
-        ("reduce_out", lambda: rt.reduce_out(prob.data_ptr(), out.data_ptr(), n)),
-        ("dispatch_grads", lambda: rt.dispatch_grads(out.data_ptr(), prob.data_ptr(), dprob.data_ptr(), n * K)),
-        ("wgrad2", rt.wgrad2), ("dgrad2", rt.dgrad2), ("wgrad1", rt.wgrad1), ("dgrad1", rt.dgrad1),
-        ("reduce_dtokens", lambda: rt.reduce_dtokens(out.data_ptr(), n)),
+        ("reduce_out", lambda: rt.reduce_out(out.data_ptr(), n)),
+        ("dispatch_grads", lambda: rt.dispatch_grads(out.data_ptr(), n * K)),
+        ("dgrad2 + swiglu pass", rt.dgrad2), ("wgrad2", rt.wgrad2), ("wgrad1", rt.wgrad1), ("dgrad1", rt.dgrad1),
+        ("reduce_dtokens", lambda: rt.reduce_dtokens(out.data_ptr(), dprob.data_ptr(), n)),
         # the one-kernel forms the step itself uses (each needs fresh arrival counters: publish clears them)
         ("publish+solve+route", lambda: (rt.publish(idx.data_ptr(), n * K), rt.solve(), rt.route(idx.data_ptr(), n * K))),
         ("psr+dispatch+gemm1 fused", lambda: (rt.publish(idx.data_ptr(), n * K), rt.solve(), rt.route(idx.data_ptr(), n * K),
-                                              rt.gemm1_fused(x.data_ptr(), n * K))),
+                                              rt.gemm1_fused(x.data_ptr(), prob.data_ptr(), n * K))),
         ("psr+dispatch_grads+dgrad2 fused", lambda: (rt.publish(idx.data_ptr(), n * K), rt.solve(), rt.route(idx.data_ptr(), n * K),
-                                                     rt.dgrad2_fused(out.data_ptr(), prob.data_ptr(), dprob.data_ptr(), n * K))),
+                                                     rt.dgrad2_fused(out.data_ptr(), n * K))),
     ]
     if layer.world > 1:
         return  # phases that wait on peers cannot be timed one rank at a time

@@ -1,7 +1,10 @@
 """Multi-GPU correctness check of the fused MoE layer (one process per GPU, NCCL for bootstrap).
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29517 -m ep_balance_b200.launch.check_multi [--steps 3]
+        --master-port 29517 -m ep_balance_b200.launch.check_multi [--steps 3] [--headline]
+
+``--headline`` runs the shape of the headline benchmark (hidden 2048, SwiGLU 1408, 64 experts, top-6,
+8192 tokens per rank, router skew tuned to expert max/mean 3.5, two logical domains from four ranks on).
 
 Every rank runs forward+backward through the native path, then recomputes its own tokens through
 the plain PyTorch oracle with the full set of expert weights (all-gathered).  Outputs, token
@@ -31,7 +34,11 @@ def main() -> int:
     ap.add_argument("--ffn", type=int, default=256)
     ap.add_argument("--experts", type=int, default=16)
     ap.add_argument("--topk", type=int, default=2)
+    ap.add_argument("--headline", action="store_true", help="the headline benchmark's shape and router skew")
+    ap.add_argument("--out", default=None, help="rank 0 also writes its report lines to this file")
     a = ap.parse_args()
+    if a.headline:
+        a.tokens, a.hidden, a.ffn, a.experts, a.topk = 8192, 2048, 1408, 64, 6
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -43,14 +50,20 @@ def main() -> int:
 
     domains = 2 if world % 2 == 0 and world >= 4 else 1
     cfg = MoEConfig(hidden=a.hidden, ffn=a.ffn, num_experts=a.experts, top_k=a.topk, max_tokens=a.tokens,
-                    extra_slots=2, num_domains=domains, capacity_factor=float(world))
+                    extra_slots=2, num_domains=domains, capacity_factor=2.0 if a.headline else float(world))
     heap = SymmetricHeap(heap_layout(cfg, world), dev)
     layer = FusedMoE(cfg, heap, rank, world)
     dist.broadcast(layer.router.data, src=0)
-    bias = torch.zeros(a.experts, device=dev)
-    bias[:3] = 1.0  # three hot experts; the router's own logits (std ~0.3) still reach every expert
+    if a.headline:
+        from ..utils.workload import router_bias_for_imbalance
+
+        bias = router_bias_for_imbalance(a.experts, a.topk, 0.02 * a.hidden ** 0.5, 3.5).to(dev)
+    else:
+        bias = torch.zeros(a.experts, device=dev)
+        bias[:3] = 1.0  # three hot experts; the router's own logits (std ~0.3) still reach every expert
     layer.router_bias = bias
     ok = True
+    report = []
     for step in range(a.steps):
         g = torch.Generator(device="cpu").manual_seed(100 * step + rank)
         tokens = torch.randn(a.tokens, a.hidden, generator=g).to(dev, torch.bfloat16)
@@ -61,7 +74,7 @@ def main() -> int:
         dtok = torch.empty_like(tokens)
         dprob = torch.empty_like(prob)
         layer.rt.forward(tokens.data_ptr(), idx.data_ptr(), prob.data_ptr(), out.data_ptr(), a.tokens)
-        layer.rt.backward(dout.data_ptr(), prob.data_ptr(), dtok.data_ptr(), dprob.data_ptr(), a.tokens)
+        layer.rt.backward(dout.data_ptr(), dtok.data_ptr(), dprob.data_ptr(), a.tokens)
         torch.cuda.synchronize()
         layer.check_status()
         dist.barrier()
@@ -91,14 +104,25 @@ def main() -> int:
         replicas = int(layer.last_plan().x.sum()) - a.experts
         good = all(v < 3e-2 for v in errs.values()) and same_plan
         ok = ok and good
-        print(f"[rank {rank}] step {step} {'PASS' if good else 'FAIL'} plan_identical={same_plan} replicas={replicas} "
-              + " ".join(f"{k}={v:.2e}" for k, v in errs.items()), flush=True)
+        loads = layer.rank_loads().float()
+        line = (f"[rank {rank}/{world}] step {step} {'PASS' if good else 'FAIL'} plan_identical={same_plan} replicas={replicas} "
+                f"rank_load_max_over_mean={float(loads.max() / loads.mean()):.3f} "
+                + " ".join(f"{k}={v:.2e}" for k, v in errs.items()))
+        print(line, flush=True)
+        lines = [None] * world
+        dist.all_gather_object(lines, line)
+        report += lines
     flag = torch.tensor([1 if ok else 0], device=dev)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:
-        print("CHECK_MULTI " + ("PASS" if int(flag) else "FAIL"), flush=True)
+        verdict = "CHECK_MULTI " + ("PASS" if int(flag) else "FAIL")
+        print(verdict, flush=True)
+        if a.out:
+            shape = f"tokens/rank {a.tokens} hidden {a.hidden} ffn {a.ffn} experts {a.experts} top-{a.topk} ranks {world} domains {domains}"
+            with open(a.out, "w") as fh:
+                fh.write("\n".join([shape] + report + [verdict]) + "\n")
     return 0 if int(flag) else 1
 
 

@@ -55,25 +55,25 @@ class EmulatedCluster:
             l.rt.solve()
         for l, (idx, _), m in zip(L, routing, n):
             l.rt.route(idx.data_ptr(), m * K)
-        for l, t, m in zip(L, tokens, n):
-            l.rt.dispatch_tokens(t.data_ptr(), m * K)
+        for l, t, (_, p), m in zip(L, tokens, routing, n):
+            l.rt.dispatch_tokens(t.data_ptr(), p.data_ptr(), m * K)
         for l in L:
             l.rt.pull_weights()
         for l in L:
             l.rt.gemm1()
         for l in L:
             l.rt.gemm2()
-        for l, (_, p), o, m in zip(L, routing, outs, n):
-            l.rt.reduce_out(p.data_ptr(), o.data_ptr(), m)
-        for l, d, (_, p), dp, m in zip(L, douts, routing, dprob, n):
-            l.rt.dispatch_grads(d.data_ptr(), p.data_ptr(), dp.data_ptr(), m * K)
+        for l, o, m in zip(L, outs, n):
+            l.rt.reduce_out(o.data_ptr(), m)
+        for l, d, m in zip(L, douts, n):
+            l.rt.dispatch_grads(d.data_ptr(), m * K)
         for l in L:
-            l.rt.wgrad2()
             l.rt.dgrad2()
+            l.rt.wgrad2()
             l.rt.wgrad1()
             l.rt.dgrad1()
-        for l, dt, m in zip(L, dtok, n):
-            l.rt.reduce_dtokens(dt.data_ptr(), m)
+        for l, dt, dp, m in zip(L, dtok, dprob, n):
+            l.rt.reduce_dtokens(dt.data_ptr(), dp.data_ptr(), m)
         for l in L:
             l.rt.reduce_weight_grads()
         return [(outs[r], dtok[r], dprob[r], routing[r][0], routing[r][1]) for r in range(self.world)]
@@ -103,5 +103,5 @@ class EmulatedCluster:
         for l in L:
             l.rt.gemm2_fp8()
         for l, (_, p), o, m in zip(L, routing, outs, n):
-            l.rt.reduce_out(p.data_ptr(), o.data_ptr(), m)
+            l.rt.reduce_out(o.data_ptr(), m, False, p.data_ptr())
         return outs, routing

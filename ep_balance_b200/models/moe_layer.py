@@ -8,7 +8,10 @@ One forward does, entirely on the device and without any host read:
 
 and the backward mirrors it (gradient dispatch with fused gate gradients, Wgrad/Dgrad grouped
 GEMMs, the activation gradient as one coalesced pass or fused into the Dgrad2 epilogue, owner-side
-reduction of replica weight gradients).  Forwards that run without autograd can use block-scaled fp8
+reduction of replica weight gradients).  A unit's gate weight travels with its token row and is folded
+into the activation by GEMM1's epilogue, so GEMM2 produces weighted rows, the combine is a plain sum and
+the backward pass sends the output gradient unscaled; the hosts apply the weight and compute the
+gate-weight gradients in their SwiGLU-gradient pass and store them back to the units' source ranks.  Forwards that run without autograd can use block-scaled fp8
 expert GEMMs (``MoEConfig.fp8_inference``) and select experts with one fused router kernel.
 This is the B200 counterpart of the reference's apply mode
 (eplb/integration/eplb_manager.py:905-1167 ``sync_free_moe_forward``, megatron_moe.py:156-215).
@@ -68,9 +71,6 @@ class MoEConfig:
     # activation scales, 128 x 128 weight scales, power-of-two scale factors).  Call
     # ``FusedMoE.quantize_weights()`` after the weights change; replicas then pull the fp8 copies.
     fp8_inference: bool = False
-    # False: Dgrad2 is a plain GEMM into a [rows, ffn] buffer followed by one elementwise SwiGLU-gradient pass
-    # (faster; costs that buffer).  True: the SwiGLU gradient runs in the GEMM epilogue, in place.
-    fused_dgrad2: bool = False
     # True: the token transport of a pass (dispatch + replica weight pull in forward, gradient dispatch in
     # backward) runs on spare warps of the GEMM kernel that consumes the rows, so transfer and tensor-core
     # tiles overlap.  False: a stand-alone transport kernel runs first.  ``EPLB_FUSED_COMM=0`` overrides.
@@ -94,6 +94,8 @@ def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
     lay.add("arrive", (2 * (cap // (128 * cfg.gemm_ctas)) + 2 * max(w_slots - home_cap, 0) + 4,), torch.int32)
     lay.add("xbuf", (cap, H), torch.bfloat16)
     lay.add("meta", (cap, 2), torch.int32)
+    lay.add("rowp", (cap,), torch.float32)     # gate weight of every received row (stored by its sender)
+    lay.add("dprob", (U,), torch.float32)      # gate-weight gradients of this rank's units (stored by their hosts)
     lay.add("ybuf", (U, H), torch.bfloat16)
     lay.add("dybuf", (cap, H), torch.bfloat16)
     lay.add("dxbuf", (U, H), torch.bfloat16)
@@ -182,7 +184,7 @@ class _FusedMoEFunction(torch.autograd.Function):
         dout = dout.contiguous()
         dtokens = torch.empty_like(dout)
         dprob = torch.empty_like(topk_prob)
-        layer.rt.backward(dout.data_ptr(), topk_prob.data_ptr(), dtokens.data_ptr(), dprob.data_ptr(), ctx.n)
+        layer.rt.backward(dout.data_ptr(), dtokens.data_ptr(), dprob.data_ptr(), ctx.n)
         layer.bind_grads()
         return dtokens, None, dprob, None
 
@@ -259,8 +261,7 @@ class FusedMoE(nn.Module):
             "hbuf": torch.zeros((self.row_capacity, 2 * F), dtype=torch.bfloat16, device=dev),
             "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
         }
-        if not cfg.fused_dgrad2:
-            self.loc["dact"] = torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev)
+        self.loc["dact"] = torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev)
         ptrs = {k: v.data_ptr() for k, v in self.loc.items()}
         self._acc_gw1 = self._acc_gw2 = None
         if cfg.grad_accum_dtype is not None:
@@ -269,9 +270,9 @@ class FusedMoE(nn.Module):
             self._acc_gw1 = torch.zeros((self.home_cap, 2 * F, H), dtype=cfg.grad_accum_dtype, device=dev)
             self._acc_gw2 = torch.zeros((self.home_cap, H, F), dtype=cfg.grad_accum_dtype, device=dev)
             ptrs["acc_gw1"], ptrs["acc_gw2"] = self._acc_gw1.data_ptr(), self._acc_gw2.data_ptr()
-        symm_names = ["omega", "signals", "arrive", "xbuf", "meta", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"]
+        symm_names = ["omega", "signals", "arrive", "xbuf", "meta", "rowp", "dprob", "ybuf", "dybuf", "dxbuf", "w1", "w2", "gw1", "gw2"]
         table_names = [("omega", "omega_ptrs"), ("signals", "signal_ptrs"), ("arrive", "arrive_ptrs"), ("xbuf", "xbuf_ptrs"),
-                       ("meta", "meta_ptrs"), ("ybuf", "ybuf_ptrs"), ("dybuf", "dybuf_ptrs"),
+                       ("meta", "meta_ptrs"), ("rowp", "rowp_ptrs"), ("dprob", "dprob_ptrs"), ("ybuf", "ybuf_ptrs"), ("dybuf", "dybuf_ptrs"),
                        ("dxbuf", "dxbuf_ptrs"), ("w1", "w1_ptrs"), ("w2", "w2_ptrs"), ("gw1", "gw1_ptrs"),
                        ("gw2", "gw2_ptrs")]
         self._fp8_ready = False
@@ -301,7 +302,6 @@ class FusedMoE(nn.Module):
                       probe=int(sc.stage2_patience_all_scales and iters > sc.stage2_stagnation_patience + 1),
                       s_tok=H * 2, num_sms=props.multi_processor_count, multi_rank_sync=int(multi_rank_sync),
                       gemm_ctas=cfg.gemm_ctas, accum_fp32=int(cfg.grad_accum_dtype == torch.float32),
-                      fused_dgrad2=int(cfg.fused_dgrad2),
                       fused_comm=int(os.environ.get("EPLB_FUSED_COMM", int(cfg.fused_comm))),
                       wait_ms=int(os.environ.get("EPLB_WAIT_MS", cfg.wait_ms)))
         self.rt = load().MoeRuntime(rt_cfg, ptrs)

@@ -61,7 +61,6 @@ LayerConfig config_from_dict(const py::dict& d) {
   c.allow_cross = get_int(d, "allow_cross", 1);
   c.probe = get_int(d, "probe", 0);
   c.accum_fp32 = get_int(d, "accum_fp32", 0);
-  c.fused_dgrad2 = get_int(d, "fused_dgrad2", 0);
   c.s_tok = d.contains("s_tok") ? d["s_tok"].cast<int64_t>() : 0;
   c.num_sms = get_int(d, "num_sms", 148);
   c.multi_rank_sync = get_int(d, "multi_rank_sync", 1);
@@ -438,30 +437,30 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("publish", [](MoeRuntime& r, uint64_t idx, int u) { r.publish((const int64_t*)cp(idx), u, current_stream()); })
       .def("solve", [](MoeRuntime& r) { r.solve(current_stream()); })
       .def("route", [](MoeRuntime& r, uint64_t idx, int u) { r.route((const int64_t*)cp(idx), u, current_stream()); })
-      .def("dispatch_tokens", [](MoeRuntime& r, uint64_t tok, int u) { r.dispatch_tokens(cp(tok), u, current_stream()); })
+      .def("dispatch_tokens", [](MoeRuntime& r, uint64_t tok, uint64_t prob, int u) {
+        r.dispatch_tokens(cp(tok), (const float*)cp(prob), u, current_stream());
+      })
       .def("pull_weights", [](MoeRuntime& r) { r.pull_weights(current_stream()); })
       .def("barrier", [](MoeRuntime& r, int slot) { r.barrier(slot, current_stream()); })
       .def("gemm1", [](MoeRuntime& r) { r.gemm1(current_stream()); })
       .def("gemm2", [](MoeRuntime& r) { r.gemm2(current_stream()); })
-      .def("gemm1_fused", [](MoeRuntime& r, uint64_t tok, int u) { r.gemm1_fused(cp(tok), u, current_stream()); })
-      .def("dgrad2_fused", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dprob, int u) {
-        r.dgrad2_fused(cp(dout), (const float*)cp(prob), (float*)mp(dprob), u, current_stream());
+      .def("gemm1_fused", [](MoeRuntime& r, uint64_t tok, uint64_t prob, int u) {
+        r.gemm1_fused(cp(tok), (const float*)cp(prob), u, current_stream());
       })
+      .def("dgrad2_fused", [](MoeRuntime& r, uint64_t dout, int u) { r.dgrad2_fused(cp(dout), u, current_stream()); })
       .def("trace_launches", &MoeRuntime::trace_launches)
       .def("launch_log", [](const MoeRuntime& r) { return r.launch_log(); })
-      .def("reduce_out", [](MoeRuntime& r, uint64_t prob, uint64_t out, int n, bool wait_peers) {
-        r.reduce_out((const float*)cp(prob), mp(out), n, current_stream(), wait_peers);
-      }, py::arg("prob"), py::arg("out"), py::arg("n"), py::arg("wait_peers") = false)
-      .def("dispatch_grads", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dprob, int u) {
-        r.dispatch_grads(cp(dout), (const float*)cp(prob), (float*)mp(dprob), u, current_stream());
-      })
+      .def("reduce_out", [](MoeRuntime& r, uint64_t out, int n, bool wait_peers, uint64_t unit_scale) {
+        r.reduce_out(mp(out), n, current_stream(), wait_peers, (const float*)cp(unit_scale));
+      }, py::arg("out"), py::arg("n"), py::arg("wait_peers") = false, py::arg("unit_scale") = 0)
+      .def("dispatch_grads", [](MoeRuntime& r, uint64_t dout, int u) { r.dispatch_grads(cp(dout), u, current_stream()); })
       .def("wgrad2", [](MoeRuntime& r) { r.wgrad2(current_stream()); })
       .def("dgrad2", [](MoeRuntime& r) { r.dgrad2(current_stream()); })
       .def("wgrad1", [](MoeRuntime& r) { r.wgrad1(current_stream()); })
       .def("dgrad1", [](MoeRuntime& r) { r.dgrad1(current_stream()); })
-      .def("reduce_dtokens", [](MoeRuntime& r, uint64_t dt, int n, bool wait_peers) {
-        r.reduce_dtokens(mp(dt), n, current_stream(), wait_peers);
-      }, py::arg("dtokens"), py::arg("n"), py::arg("wait_peers") = false)
+      .def("reduce_dtokens", [](MoeRuntime& r, uint64_t dt, uint64_t dprob, int n, bool wait_peers) {
+        r.reduce_dtokens(mp(dt), (float*)mp(dprob), n, current_stream(), wait_peers);
+      }, py::arg("dtokens"), py::arg("dprob"), py::arg("n"), py::arg("wait_peers") = false)
       .def("reduce_weight_grads", [](MoeRuntime& r) { r.reduce_weight_grads(current_stream()); })
       .def("has_fp8", &MoeRuntime::has_fp8)
       .def("quantize_own_weights", [](MoeRuntime& r) { r.quantize_own_weights(current_stream()); })
@@ -476,7 +475,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
       .def("forward", [](MoeRuntime& r, uint64_t tok, uint64_t idx, uint64_t prob, uint64_t out, int n) {
         r.forward(cp(tok), (const int64_t*)cp(idx), (const float*)cp(prob), mp(out), n, current_stream());
       })
-      .def("backward", [](MoeRuntime& r, uint64_t dout, uint64_t prob, uint64_t dtok, uint64_t dprob, int n) {
-        r.backward(cp(dout), (const float*)cp(prob), mp(dtok), (float*)mp(dprob), n, current_stream());
+      .def("backward", [](MoeRuntime& r, uint64_t dout, uint64_t dtok, uint64_t dprob, int n) {
+        r.backward(cp(dout), mp(dtok), (float*)mp(dprob), n, current_stream());
       });
 }

@@ -6,10 +6,8 @@
 // segments: one lane issues a bulk async load (global -> shared, completion on the slot's mbarrier) and,
 // once a segment has landed, a bulk async store (shared -> global, possibly a peer's memory).  Several
 // segments per warp are in flight with no register traffic, so two warps beside a running GEMM keep
-// enough bytes outstanding to cover memory and NVLink latency.  Gradient rows are transformed in shared
-// memory between load and store (scaled by the gate weight; their dot product with the saved forward
-// output is the gate-weight gradient).  No load names a cluster multicast; sources and destinations may
-// be another GPU's memory.
+// enough bytes outstanding to cover memory and NVLink latency.  No load names a cluster multicast;
+// sources and destinations may be another GPU's memory.
 //
 // Nothing here waits on another CTA or rank, so a warp running it always makes progress; only the
 // consumers of its signals wait, and those waits are bounded.  The waits on the warp's own copies are
@@ -24,16 +22,13 @@
 namespace epb {
 
 constexpr int kCommSlots = 4;          // ring slots per warp
-constexpr int kCommSlotBytes = 4096;   // forward: one 4 KB segment; backward: 2 KB of gradient + 2 KB of saved output
+constexpr int kCommSlotBytes = 4096;   // one segment
 constexpr int kCommWarpBytes = kCommSlots * kCommSlotBytes;   // ring bytes per warp
 constexpr int kCommCtrlBytes = 192;    // per warp: kCommSlots mbarriers + kCommSlots slot records
 
 struct CommSlot {
   void* dst;       // where the segment goes
-  float* dot_out;  // backward: where the row's dot product goes once its last segment is done (null otherwise)
-  float scale;
   int bytes;
-  int last;        // last segment of its row
   int pad;
 };
 static_assert(kCommSlots * 8 + kCommSlots * sizeof(CommSlot) <= kCommCtrlBytes, "per-warp control block too small");
@@ -71,39 +66,14 @@ __device__ __forceinline__ void comm_bulk_store(void* gdst, const void* smem_src
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
-__device__ __forceinline__ float comm_dot8(const uint4& a, const uint4& b) {
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
-  float acc = 0.f;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
-    acc += fa.x * fb.x + fa.y * fb.y;
-  }
-  return acc;
-}
-__device__ __forceinline__ uint4 comm_scale8(const uint4& a, float s) {
-  uint4 out;
-  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
-  __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&out);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __bfloat1622float2(pa[i]);
-    po[i] = __floats2bfloat162_rn(f.x * s, f.y * s);
-  }
-  return out;
-}
-
 // The per-warp copy pipeline.  `smem` is the warp's private region: kCommWarpBytes of ring (16-byte
 // aligned) followed by kCommCtrlBytes of control data.  All 32 lanes call every member together.
-template <bool kBwd>
 struct CommPipe {
-  static constexpr int kSeg = kBwd ? kCommSlotBytes / 2 : kCommSlotBytes;  // bytes of one segment
+  static constexpr int kSeg = kCommSlotBytes;  // bytes of one segment
   uint8_t* ring;
   uint64_t* bars;
   CommSlot* slots;
   unsigned pushed, popped;
-  float dot;
   int lane;
   bool failed;
   int* status;
@@ -113,7 +83,6 @@ struct CommPipe {
     bars = reinterpret_cast<uint64_t*>(smem + kCommWarpBytes);
     slots = reinterpret_cast<CommSlot*>(bars + kCommSlots);
     pushed = popped = 0u;
-    dot = 0.f;
     lane = threadIdx.x & 31;
     failed = false;
     status = status_word;
@@ -125,7 +94,7 @@ struct CommPipe {
     __syncwarp();
   }
 
-  // Oldest segment in flight: wait for its load, transform it (backward), store it.
+  // Oldest segment in flight: wait for its load, store it.
   __device__ __forceinline__ void pop() {
     const int s = (int)(popped % kCommSlots);
     const uint32_t parity = (popped / kCommSlots) & 1u;
@@ -146,42 +115,22 @@ struct CommPipe {
     }
     const CommSlot rec = slots[s];
     uint8_t* seg = ring + (size_t)s * kCommSlotBytes;
-    if (kBwd && !failed) {
-      uint4* g = reinterpret_cast<uint4*>(seg);
-      const uint4* y = reinterpret_cast<const uint4*>(seg + kSeg);
-      const int nvec = rec.bytes / 16;
-      for (int v = lane; v < nvec; v += 32) {
-        const uint4 a = g[v];
-        dot += comm_dot8(a, y[v]);
-        g[v] = comm_scale8(a, rec.scale);
-      }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this lane's writes before the bulk store reads them
-      if (rec.last) {
-        float d = dot;
-        for (int off = 16; off > 0; off >>= 1) d += __shfl_down_sync(0xffffffffu, d, off);
-        if (lane == 0 && rec.dot_out != nullptr) *rec.dot_out = d;
-        dot = 0.f;
-      }
-    }
     __syncwarp();
     if (lane == 0 && !failed) comm_bulk_store(rec.dst, seg, (uint32_t)rec.bytes);
     ++popped;
   }
 
-  // Start moving `bytes` (<= kSeg, multiple of 16) from `src` (and, backward, the matching bytes of the
-  // saved output from `src2`) to `dst`.
-  __device__ __forceinline__ void push(const void* src, const void* src2, void* dst, int bytes, float scale, float* dot_out,
-                                       int last) {
+  // Start moving `bytes` (<= kSeg, multiple of 16) from `src` to `dst`.
+  __device__ __forceinline__ void push(const void* src, void* dst, int bytes) {
     if (pushed - popped >= (unsigned)(kCommSlots - 1)) pop();
     const int s = (int)(pushed % kCommSlots);
     if (lane == 0 && !failed) {
       // every store but the most recent one has finished reading its slot; slot s was stored two pops ago
       asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      slots[s] = CommSlot{dst, dot_out, scale, bytes, last, 0};
+      slots[s] = CommSlot{dst, bytes, 0};
       uint8_t* seg = ring + (size_t)s * kCommSlotBytes;
-      comm_bar_expect(&bars[s], (uint32_t)(kBwd && src2 != nullptr ? 2 * bytes : bytes));
+      comm_bar_expect(&bars[s], (uint32_t)bytes);
       comm_bulk_load(seg, src, (uint32_t)bytes, &bars[s]);
-      if (kBwd && src2 != nullptr) comm_bulk_load(seg + kSeg, src2, (uint32_t)bytes, &bars[s]);
     }
     __syncwarp();
     ++pushed;
@@ -199,42 +148,35 @@ struct CommPipe {
 };
 
 // The warp sends rows [row0, row0 + nrow) (nrow <= 32) of peer buffer `dbuf`; lane i holds the unit of
-// row row0 + i in `my_u`.
-template <bool kBwd>
-__device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe<kBwd>& pipe, int my_u, int nrow, int row0,
-                                               uint8_t* dbuf, int2* dmeta, int lane) {
+// row row0 + i in `my_u`.  Forward also stores {source rank, unit} and the unit's gate weight beside the row.
+__device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe& pipe, int my_u, int nrow, int row0,
+                                               uint8_t* dbuf, int2* dmeta, float* drowp, int lane) {
   constexpr unsigned kAll = 0xffffffffu;
-  constexpr int kSeg = CommPipe<kBwd>::kSeg;
+  constexpr int kSeg = CommPipe::kSeg;
   const int row_bytes = a.H * 2;
-  const bool with_dot = kBwd && a.saved_out != nullptr;
+  if (lane < nrow) {
+    if (dmeta != nullptr) dmeta[row0 + lane] = make_int2(a.me, my_u);
+    if (drowp != nullptr) drowp[row0 + lane] = a.unit_prob[my_u];
+  }
   for (int i = 0; i < nrow; ++i) {
     const int u = __shfl_sync(kAll, my_u, i);
     const uint8_t* src = reinterpret_cast<const uint8_t*>(a.rows) + (size_t)(u / a.topk) * row_bytes;
-    const uint8_t* saved = with_dot ? reinterpret_cast<const uint8_t*>(a.saved_out) + (size_t)u * row_bytes : nullptr;
     uint8_t* dst = dbuf + (size_t)(row0 + i) * row_bytes;
-    const float s = (kBwd && a.unit_scale != nullptr) ? a.unit_scale[u] : 1.f;
-    for (int off = 0; off < row_bytes; off += kSeg) {
-      const int bytes = min(kSeg, row_bytes - off);
-      const int last = off + kSeg >= row_bytes;
-      pipe.push(src + off, saved ? saved + off : nullptr, dst + off, bytes, s,
-                (with_dot && a.unit_dot != nullptr) ? a.unit_dot + u : nullptr, last);
-    }
-    if (!kBwd && dmeta != nullptr && lane == 0) dmeta[row0 + i] = make_int2(a.me, u);
+    for (int off = 0; off < row_bytes; off += kSeg) pipe.push(src + off, dst + off, min(kSeg, row_bytes - off));
   }
 }
 
 // Warp `worker` of `n_workers` takes items worker, worker + n_workers, ... of each item list.
 // Called by whole warps (all 32 lanes active); `smem` = the warp's kCommWarpBytes + kCommCtrlBytes.
-template <bool kBwd>
-__device__ void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* smem, int* status) {
+__device__ inline void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* smem, int* status) {
   constexpr unsigned kAll = 0xffffffffu;
   const int lane = threadIdx.x & 31;
-  CommPipe<kBwd> pipe;
+  CommPipe pipe;
   pipe.init(smem, status);
 
   // ---------------------------------------------------------------- replica weights (peer loads)
-  if (!kBwd && a.do_pull && a.w_slots > a.home_cap) {
-    constexpr int kSeg = CommPipe<kBwd>::kSeg;
+  if (a.do_pull && a.w_slots > a.home_cap) {
+    constexpr int kSeg = CommPipe::kSeg;
     const int rs = a.w_slots - a.home_cap;
     const int c1 = (int)pull_chunks(a.w1_elems), c2 = (int)pull_chunks(a.w2_elems);
     const int n_items = rs * (c1 + c2);
@@ -258,7 +200,7 @@ __device__ void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* 
         const int n = (int)(slot_bytes - first < (size_t)kPullChunkBytes ? slot_bytes - first : (size_t)kPullChunkBytes);
         const uint8_t* src = reinterpret_cast<const uint8_t*>(ptrs[a.main_rank[e]]) + (size_t)a.home_index[e] * slot_bytes + first;
         uint8_t* dst = reinterpret_cast<uint8_t*>(ptrs[a.me]) + (size_t)(a.home_cap + s) * slot_bytes + first;
-        for (int off = 0; off < n; off += kSeg) pipe.push(src + off, nullptr, dst + off, min(kSeg, n - off), 1.f, nullptr, 0);
+        for (int off = 0; off < n; off += kSeg) pipe.push(src + off, dst + off, min(kSeg, n - off));
         pipe.drain();
       }
       __threadfence();
@@ -282,6 +224,7 @@ __device__ void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* 
       const int r0 = b * a.block_rows, r1 = r0 + a.block_rows;
       uint8_t* dbuf = reinterpret_cast<uint8_t*>(a.buf_ptrs[dst]);
       int2* dmeta = a.meta_ptrs != nullptr ? a.meta_ptrs[dst] : nullptr;
+      float* drowp = (a.rowp_ptrs != nullptr && a.unit_prob != nullptr) ? a.rowp_ptrs[dst] : nullptr;
       for (int e0 = 0; e0 < a.E; e0 += 32) {
         const int e = e0 + lane;
         int base = -1, cnt = 0;
@@ -300,7 +243,7 @@ __device__ void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* 
           for (int row0 = slo; row0 < shi; row0 += 32) {
             const int nrow = min(32, shi - row0);
             const int my_u = lane < nrow ? a.sorted_units[pos + lane] : 0;
-            comm_send_rows<kBwd>(a, pipe, my_u, nrow, row0, dbuf, dmeta, lane);
+            comm_send_rows(a, pipe, my_u, nrow, row0, dbuf, dmeta, drowp, lane);
             pos += nrow;
           }
         }
@@ -326,6 +269,7 @@ __device__ void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* 
       const int lo = min(a.group_off[g] + a.group_rows[g] + 32 * s, end), hi = min(lo + 32, end);
       const size_t first = (size_t)lo * vec_per_row, last = (size_t)hi * vec_per_row;
       for (size_t i = first + lane; i < last; i += 32) buf[i] = zero;
+      if (a.local_meta != nullptr && lo + lane < hi) a.local_meta[lo + lane] = make_int2(-1, -1);
     }
   }
   pipe.drain();

@@ -371,8 +371,7 @@ __device__ __forceinline__ void wide_flush(const uint4* tile, int lane, char* ro
   }
 }
 // ---------------------------------------------------------------- kernel
-// kComm: 0 = GEMM only; 1 = plus two transport warps sending token rows / pulling replica weights;
-// 2 = plus two transport warps sending output gradients (scaled, with the gate-weight gradient).
+// kComm: 0 = GEMM only; 1 = plus two transport warps (token or gradient rows to their hosts, replica weights in).
 template <int kMode, int kCtas, int kComm>
 __global__ void __launch_bounds__(NUM_THREADS + (kComm ? COMM_WARPS * 32 : 0), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -578,7 +577,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ------------------------------------------------------------ transport (warps 10, 11)
     uint8_t* comm_smem_base = reinterpret_cast<uint8_t*>(stage_tiles) + 8 * kStageWarpBytes +
                               (warp - NUM_THREADS / 32) * (kCommWarpBytes + kCommCtrlBytes);
-    comm_run<kComm == 2>(args.comm, (int)blockIdx.x * COMM_WARPS + (warp - NUM_THREADS / 32), (int)gridDim.x * COMM_WARPS,
+    comm_run(args.comm, (int)blockIdx.x * COMM_WARPS + (warp - NUM_THREADS / 32), (int)gridDim.x * COMM_WARPS,
                          comm_smem_base, args.status);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
@@ -610,6 +609,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int F = args.N;
         char* hrow = in_buf ? out0 + (row * (size_t)(2 * F) + t.nt * 128) * 2 : nullptr;
         char* arow = in_buf ? out1 + (row * (size_t)F + t.nt * 128) * 2 : nullptr;
+        const float rs = (real && args.row_scale != nullptr) ? __ldcg(args.row_scale + row) : 1.f;  // the row's gate weight
         uint32_t g[2][32], u[2][32];
         const int cb = half * 2;  // this warp's two 32-column chunks of the gate (and up) half
         tmem_ld32(taddr + cb * 32, g[0]);
@@ -631,7 +631,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int i = 0; i < 16; ++i) {
             // activation from the bf16-rounded pre-activations, exactly what backward will read
             float2 g2 = unpack_bf16((&pg[0].x)[i]), u2 = unpack_bf16((&pu[0].x)[i]);
-            (&pa[0].x)[i] = pack_bf16(g2.x * sigmoidf_fast(g2.x) * u2.x, g2.y * sigmoidf_fast(g2.y) * u2.y);
+            (&pa[0].x)[i] = pack_bf16(rs * g2.x * sigmoidf_fast(g2.x) * u2.x, rs * g2.y * sigmoidf_fast(g2.y) * u2.y);
           }
           stage_store(stg, lane, pg);
           stage_flush(stg, lane, hrow, c * 64);
@@ -854,9 +854,8 @@ static cudaError_t launch_ctas(const CUtensorMap& tmA, const CUtensorMap& tmB, c
   const bool comm = args.comm.do_dispatch || args.comm.do_pad || args.comm.do_pull;
   if (comm) {
     // fused transport exists for the two GEMMs that consume freshly dispatched rows
-    const bool bwd = args.comm.unit_scale != nullptr || args.comm.saved_out != nullptr;
-    if (args.mode == kFwd1 && !bwd) return launch_mode<kFwd1, kCtas, 1>(tmA, tmB, args, num_sms, stream);
-    if (args.mode == kDgrad1 && bwd) return launch_mode<kDgrad1, kCtas, 2>(tmA, tmB, args, num_sms, stream);
+    if (args.mode == kFwd1) return launch_mode<kFwd1, kCtas, 1>(tmA, tmB, args, num_sms, stream);
+    if (args.mode == kDgrad1) return launch_mode<kDgrad1, kCtas, 1>(tmA, tmB, args, num_sms, stream);
     return cudaErrorInvalidValue;
   }
   switch (args.mode) {

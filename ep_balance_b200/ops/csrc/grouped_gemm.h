@@ -40,6 +40,7 @@ struct GemmArgs {
   void* out0;                  // kFwd1: h [T, 2N];  kDgrad2: h (in/out);  kWgrad: dW [slots, M_out, N];
                                // kPlain: C [T, N];  scatter modes with out_ptrs == null: local [T, N]
   void* out1;                  // kFwd1: act [T, N]
+  const float* row_scale;      // kFwd1: optional [T] factor folded into act (the row's gate weight); null: 1
   void* const* out_ptrs;       // scatter modes: R peer buffers [units, N] (null -> local out0)
   const int2* meta;            // scatter modes: {src rank, unit} per row
   int* status;
@@ -61,9 +62,9 @@ struct GemmArgs {
   unsigned* const* done_signal_ptrs;
   int done_slot, done_R;
   // ---- fused transport (comm.do_* all zero: none).  Two extra warps per CTA run the item-driven
-  // transport of CommArgs while the other warps compute: kFwd1 sends token rows and pulls replica
-  // weights, kDgrad1 (used as the plain Dgrad2) sends output gradients; the producer of the same
-  // kernel -- on every rank -- gates its tiles on the arrival counters those warps advance.
+  // transport of CommArgs while the other warps compute: with kFwd1 they send token rows and pull
+  // replica weights, with kDgrad1 (used as the plain Dgrad2) they send output gradients; the producer
+  // of the same kernel -- on every rank -- gates its tiles on the arrival counters those warps advance.
   CommArgs comm;
 };
 

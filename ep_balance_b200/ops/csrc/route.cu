@@ -152,12 +152,11 @@ __global__ void __launch_bounds__(kRouteChunk) route_assign_kernel(RouteArgs a) 
 constexpr int kCommKernelWarps = 8;
 constexpr int kCommKernelSmem = kCommKernelWarps * (kCommWarpBytes + kCommCtrlBytes) + 128;
 
-template <bool kBwd>
 __global__ void __launch_bounds__(kCommKernelWarps * 32) comm_kernel(const __grid_constant__ CommArgs a, int* status) {
   extern __shared__ uint8_t comm_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 127) & ~(uintptr_t)127);
   const int warp = threadIdx.x >> 5;
-  comm_run<kBwd>(a, (int)blockIdx.x * kCommKernelWarps + warp, (int)gridDim.x * kCommKernelWarps,
+  comm_run(a, (int)blockIdx.x * kCommKernelWarps + warp, (int)gridDim.x * kCommKernelWarps,
                  base + warp * (kCommWarpBytes + kCommCtrlBytes), status);
 }
 
@@ -165,12 +164,17 @@ __global__ void __launch_bounds__(kCommKernelWarps * 32) comm_kernel(const __gri
 __global__ void __launch_bounds__(256) unit_reduce_kernel(const uint4* __restrict__ unit_rows,
                                                          const float* __restrict__ unit_scale,
                                                          uint4* __restrict__ out, int num_tokens, int topk,
-                                                         int vec_per_row, UnitReduceWait wait) {
+                                                         int vec_per_row, UnitReduceWait wait,
+                                                         const float* __restrict__ copy_src, float* __restrict__ copy_dst) {
   if (wait.signal != nullptr) {
     // rows come from the peers' GEMM epilogues: wait until every rank has signalled completion
     if (threadIdx.x == 0 && !wait_ge<true>(wait.signal, *wait.epoch * (unsigned)wait.R, wait.budget_ns))
       set_status(wait.status, kStatusSignalTimeout, 51);
     __syncthreads();
+  }
+  if (copy_dst != nullptr) {
+    const size_t n = (size_t)num_tokens * topk;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) copy_dst[i] = copy_src[i];
   }
   // one warp per (token, 32-vector chunk of the row): small batches still fill the machine
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -328,32 +332,48 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   }
 }
 
-__global__ void __launch_bounds__(256) swiglu_backward_kernel(const uint4* __restrict__ dact, uint4* __restrict__ h,
-                                                             int rows, int F, const int32_t* __restrict__ row_limit) {
-  if (row_limit != nullptr && *row_limit < rows) rows = *row_limit;
-  const int vec_per_row = F / 8;
-  const size_t total = (size_t)rows * vec_per_row;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-    const size_t r = i / vec_per_row;
-    const int v = (int)(i - r * vec_per_row);
-    uint4* hrow = h + r * (size_t)(2 * vec_per_row);
-    const uint4 d4 = dact[i], g4 = hrow[v], u4 = hrow[vec_per_row + v];
-    const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d4);
-    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
-    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
-    uint4 og, ou;
-    __nv_bfloat162* ogp = reinterpret_cast<__nv_bfloat162*>(&og);
-    __nv_bfloat162* oup = reinterpret_cast<__nv_bfloat162*>(&ou);
+// One warp per row: the row's gate-weight gradient is a dot product over the row, reduced by shuffles.
+__global__ void __launch_bounds__(256) swiglu_backward_kernel(SwigluBwdArgs a) {
+  int rows = a.rows;
+  if (a.row_limit != nullptr && *a.row_limit < rows) rows = *a.row_limit;
+  const int lane = threadIdx.x & 31;
+  const int vec_per_row = a.F / 8;
+  const uint4* dact = reinterpret_cast<const uint4*>(a.dact);
+  uint4* h = reinterpret_cast<uint4*>(a.h);
+  const int warps = (int)((gridDim.x * blockDim.x) >> 5);
+  for (int r = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5); r < rows; r += warps) {
+    const float p = a.rowp != nullptr ? a.rowp[r] : 1.f;
+    uint4* hrow = h + (size_t)r * (2 * vec_per_row);
+    const uint4* drow = dact + (size_t)r * vec_per_row;
+    float dot = 0.f;
+    for (int v = lane; v < vec_per_row; v += 32) {
+      const uint4 d4 = drow[v], g4 = hrow[v], u4 = hrow[vec_per_row + v];
+      const __nv_bfloat162* dp = reinterpret_cast<const __nv_bfloat162*>(&d4);
+      const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g4);
+      const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u4);
+      uint4 og, ou;
+      __nv_bfloat162* ogp = reinterpret_cast<__nv_bfloat162*>(&og);
+      __nv_bfloat162* oup = reinterpret_cast<__nv_bfloat162*>(&ou);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const float2 d = __bfloat1622float2(dp[k]), g = __bfloat1622float2(gp[k]), u = __bfloat1622float2(up[k]);
-      const float s0 = __fdividef(1.f, 1.f + __expf(-g.x)), s1 = __fdividef(1.f, 1.f + __expf(-g.y));
-      ogp[k] = __floats2bfloat162_rn(d.x * u.x * (s0 + g.x * s0 * (1.f - s0)), d.y * u.y * (s1 + g.y * s1 * (1.f - s1)));
-      oup[k] = __floats2bfloat162_rn(d.x * g.x * s0, d.y * g.y * s1);
+      for (int k = 0; k < 4; ++k) {
+        const float2 d = __bfloat1622float2(dp[k]), g = __bfloat1622float2(gp[k]), u = __bfloat1622float2(up[k]);
+        const float s0 = __fdividef(1.f, 1.f + __expf(-g.x)), s1 = __fdividef(1.f, 1.f + __expf(-g.y));
+        const float a0 = g.x * s0, a1 = g.y * s1;  // silu(g)
+        dot += d.x * a0 * u.x + d.y * a1 * u.y;
+        const float pd0 = p * d.x, pd1 = p * d.y;
+        ogp[k] = __floats2bfloat162_rn(pd0 * u.x * (s0 + a0 * (1.f - s0)), pd1 * u.y * (s1 + a1 * (1.f - s1)));
+        oup[k] = __floats2bfloat162_rn(pd0 * a0, pd1 * a1);
+      }
+      hrow[v] = og;
+      hrow[vec_per_row + v] = ou;
     }
-    hrow[v] = og;
-    hrow[vec_per_row + v] = ou;
+    if (a.dprob_ptrs != nullptr) {
+      for (int off = 16; off > 0; off >>= 1) dot += __shfl_down_sync(kFull, dot, off);
+      if (lane == 0) {
+        const int2 m = a.meta[r];
+        if (m.x >= 0) a.dprob_ptrs[m.x][m.y] = dot;
+      }
+    }
   }
 }
 
@@ -383,23 +403,21 @@ cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_
   if (a.H % 8 != 0 || a.block_rows <= 0 || a.tile_rows % a.block_rows != 0 || a.tile_rows % 32 != 0) return cudaErrorInvalidValue;
   if (a.w1_elems % 8 != 0 || a.w2_elems % 8 != 0) return cudaErrorInvalidValue;
   if (num_sms <= 0) num_sms = sm_count();
-  const bool bwd = a.unit_scale != nullptr || a.saved_out != nullptr;
-  static bool configured[2][kMaxTrackedDevices] = {};
+  static bool configured[kMaxTrackedDevices] = {};
   int dev;
-  if (device_needs_setup(configured[bwd], &dev)) {
-    cudaError_t e = bwd ? cudaFuncSetAttribute(comm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommKernelSmem)
-                        : cudaFuncSetAttribute(comm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommKernelSmem);
+  if (device_needs_setup(configured, &dev)) {
+    cudaError_t e = cudaFuncSetAttribute(comm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kCommKernelSmem);
     if (e != cudaSuccess) return e;
-    device_setup_done(configured[bwd], dev);
+    device_setup_done(configured, dev);
   }
   // one CTA per SM: 8 warps x 3 segments of 4 KB in flight
-  if (bwd) comm_kernel<true><<<num_sms, kCommKernelWarps * 32, kCommKernelSmem, stream>>>(a, status);
-  else comm_kernel<false><<<num_sms, kCommKernelWarps * 32, kCommKernelSmem, stream>>>(a, status);
+  comm_kernel<<<num_sms, kCommKernelWarps * 32, kCommKernelSmem, stream>>>(a, status);
   return cudaGetLastError();
 }
 
 cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, void* out, int num_tokens, int topk,
-                               int H, const UnitReduceWait* wait, cudaStream_t stream) {
+                               int H, const UnitReduceWait* wait, const float* copy_src, float* copy_dst,
+                               cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
   const int wpb = 8;
   const long long items = (long long)num_tokens * ceil_div(H / 8, 32);
@@ -407,7 +425,8 @@ cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, v
   UnitReduceWait w{};
   if (wait != nullptr) w = *wait;
   unit_reduce_kernel<<<(unsigned)((items + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
-      reinterpret_cast<const uint4*>(unit_rows), unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8, w);
+      reinterpret_cast<const uint4*>(unit_rows), unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8, w,
+      copy_src, copy_src != nullptr ? copy_dst : nullptr);
   return cudaGetLastError();
 }
 
@@ -443,12 +462,10 @@ cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
-cudaError_t launch_swiglu_backward(const void* dact, void* h, int rows, int F, const int32_t* row_limit,
-                                   cudaStream_t stream) {
-  if (F % 8 != 0) return cudaErrorInvalidValue;
-  if (rows <= 0) return cudaSuccess;
-  swiglu_backward_kernel<<<sm_count() * 8, 256, 0, stream>>>(reinterpret_cast<const uint4*>(dact), reinterpret_cast<uint4*>(h), rows,
-                                                     F, row_limit);
+cudaError_t launch_swiglu_backward(const SwigluBwdArgs& a, cudaStream_t stream) {
+  if (a.F % 8 != 0) return cudaErrorInvalidValue;
+  if (a.rows <= 0) return cudaSuccess;
+  swiglu_backward_kernel<<<sm_count() * 8, 256, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

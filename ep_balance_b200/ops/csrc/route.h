@@ -64,6 +64,10 @@ cudaError_t launch_route_assign(const RouteArgs& a, cudaStream_t stream);
 // Rows therefore arrive in the order the consuming GEMM walks its tile list.
 // The same walk moves replica weights (peer loads from the owner's home slot, one counter per
 // replica slot and weight tensor) and zero-fills this rank's own padding rows.
+// The transport is a pure copy in both directions.  The gate weight of a unit travels with its token
+// row in the forward pass (`unit_prob` -> the receiver's `rowp`), where GEMM1's epilogue folds it into
+// the activation, so the backward pass sends the output gradient unscaled and the receiver applies
+// the weight (and computes the gate-weight gradient) in its SwiGLU-gradient pass.
 // Reference counterparts: all_to_all_single dispatch + slot sort (eplb/integration/comm.py:18-36,
 // eplb_manager.py:1067-1105), replica broadcast (overlap.py:113-148).
 struct CommArgs {
@@ -73,9 +77,7 @@ struct CommArgs {
   int block_rows;                // rows of a transport block; divides tile_rows
   // ---- rows to send
   const void* rows;              // bf16 [num_tokens, H]
-  const float* unit_scale;       // [U] or null: rows are multiplied by it (gate weight, backward)
-  const void* saved_out;         // bf16 [U, H] or null: unit_dot[u] = <rows[t(u)], saved_out[u]>
-  float* unit_dot;               // [U] or null
+  const float* unit_prob;        // [U] or null: gate weight of every unit, stored beside its row (forward)
   const int32_t* sorted_units;   // [U] this rank's units ordered by expert (stable)
   const int32_t* exp_prefix;     // [E + 1] first position of each expert in sorted_units
   const int32_t* q_me;           // [E, R] units (me, e) -> dst
@@ -84,10 +86,12 @@ struct CommArgs {
   const int32_t* tiles_of;       // [R] used M-tiles of every rank's receive buffer
   void* const* buf_ptrs;         // R peers: bf16 [row_capacity, H]
   int2* const* meta_ptrs;        // R peers: int2 [row_capacity] ({src rank, unit}) or null
+  float* const* rowp_ptrs;       // R peers: float [row_capacity] (gate weight of the row's unit) or null
   unsigned* const* arrive_ptrs;  // R peers: base of the counter region
   int arrive_off;                // first word of the arrival counters [row_capacity / tile_rows] in that region
-  // ---- padding rows of this rank
+  // ---- padding rows of this rank (zero-filled; their meta entries, if given, become {-1, -1})
   void* local_buf;
+  int2* local_meta;
   const int32_t* group_off;      // [n_groups_cap + 1]
   const int32_t* group_rows;     // [n_groups_cap]
   int n_groups_cap;
@@ -107,6 +111,8 @@ __host__ __device__ inline unsigned pull_chunks(size_t elems) { return (unsigned
 cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_t stream);
 
 // out[t] = sum_k scale[t*topk+k] * rows[t*topk+k]   (scale may be null: plain sum)
+// `copy_src`/`copy_dst` (may be null): num_tokens * topk floats copied alongside (the gate-weight gradients
+// that the peers stored into this rank's symmetric buffer, handed to the caller's tensor).
 // With `wait_signal != nullptr` every CTA first waits (bounded) until *wait_signal >= *wait_epoch * R:
 // the peers' "all my rows are stored" signals of the producing GEMM (GemmArgs::done_*).
 struct UnitReduceWait {
@@ -117,7 +123,8 @@ struct UnitReduceWait {
   int* status;
 };
 cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, void* out, int num_tokens,
-                               int topk, int H, const UnitReduceWait* wait, cudaStream_t stream);
+                               int topk, int H, const UnitReduceWait* wait, const float* copy_src, float* copy_dst,
+                               cudaStream_t stream);
 
 // Cross-rank barrier on symmetric signal words: every rank adds 1 to word `slot` of every peer,
 // then waits (bounded) until its own word reaches (epoch+1)*R.  `epoch_word` lives in local
@@ -157,11 +164,21 @@ struct GradReduceArgs {
 };
 cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream);
 
-// SwiGLU backward over the first *row_limit rows, in place over the saved pre-activations:
-//   h[:, :F] <- dact * up * d/dg[g * sigmoid(g)],   h[:, F:] <- dact * g * sigmoid(g)
-// One fully coalesced pass (16-byte accesses); used after a plain Dgrad2 GEMM that wrote dact.
-cudaError_t launch_swiglu_backward(const void* dact, void* h, int rows, int F, const int32_t* row_limit,
-                                   cudaStream_t stream);
+// SwiGLU backward over the first *row_limit rows, in place over the saved pre-activations, one warp per
+// row (16-byte accesses), after a plain Dgrad2 GEMM that wrote dact = dY W2 for the UNWEIGHTED gradient:
+//   h[:, :F] <- p * dact * up * d/dg[g * sigmoid(g)],   h[:, F:] <- p * dact * g * sigmoid(g)
+// with p = rowp[row] (null: 1).  With `dprob_ptrs != nullptr` the row's gate-weight gradient
+// <dact, g * sigmoid(g) * up> is stored to dprob_ptrs[meta[row].x][meta[row].y] (the unit's source rank).
+struct SwigluBwdArgs {
+  const void* dact;             // bf16 [rows, F]
+  void* h;                      // bf16 [rows, 2F] in/out
+  int rows, F;
+  const int32_t* row_limit;     // device: rows in use (may be null)
+  const float* rowp;            // [rows] or null
+  const int2* meta;             // [rows] {src rank, unit}; rows with src < 0 are padding
+  float* const* dprob_ptrs;     // R peers: float [U] or null
+};
+cudaError_t launch_swiglu_backward(const SwigluBwdArgs& a, cudaStream_t stream);
 
 // Wait on a flag nobody sets: exercises the bounded-wait / error-status path on one GPU.
 cudaError_t launch_wait_probe(const unsigned* flag, unsigned target, unsigned long long budget_ns, int* status,

@@ -3,8 +3,9 @@
 // Forward:  count+publish -> solve -> route -> [dispatch + replica pull + GEMM1, one kernel] -> GEMM2
 // (rows stored to their source ranks, completion signalled to every peer by the last CTA) ->
 // reduce_out (waits in the kernel for the peers' signals).
-// Backward: [gradient dispatch + gate gradients + Dgrad2, one kernel] -> SwiGLU-gradient pass -> Wgrad2 ->
-// Wgrad1 -> Dgrad1 (rows stored to sources, completion signalled) -> reduce_dtokens (waits); beside
+// Backward: [gradient dispatch + Dgrad2, one kernel] -> SwiGLU-gradient pass (applies the gate weight, stores
+// the gate-weight gradients to the units' source ranks) -> Wgrad2 -> Wgrad1 -> Dgrad1 (rows stored to
+// sources, completion signalled) -> reduce_dtokens (waits); beside
 // Dgrad1, on the runtime's side stream: cross-rank barrier -> owners add their replicas' weight gradients.
 // There is no stand-alone barrier on the critical path: consumers of transferred rows wait per M-tile
 // on arrival counters that the senders advance, consumers of combined rows on one signal per peer.
@@ -116,7 +117,9 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
   tables_.totals = ptr<int32_t>("totals");
   tables_.send_off = ptr<int32_t>("send_off");
   tables_.tiles_of = ptr<int32_t>("tiles_of");
-  for (const char* name : {"arrive", "arrive_ptrs", "chunk_hist", "hist_acc", "exp_prefix", "sorted_units", "done_ctr"}) ptr<void>(name);
+  for (const char* name : {"arrive", "arrive_ptrs", "chunk_hist", "hist_acc", "exp_prefix", "sorted_units", "done_ctr", "rowp",
+                           "rowp_ptrs", "dprob", "dprob_ptrs", "dact", "meta"})
+    ptr<void>(name);
 
   const uint64_t T = c.row_capacity, H = c.H, F = c.F, S = c.w_slots;
   // K-major A operands: box {64 k, 128 rows}
@@ -240,14 +243,30 @@ CommArgs MoeRuntime::comm_args(bool dispatch, bool pad, bool pull) const {
   return a;
 }
 
-void MoeRuntime::dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream, bool zero_pad) {
-  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
-  CommArgs a = comm_args(true, zero_pad, false);
+CommArgs MoeRuntime::comm_forward(const void* tokens, const float* topk_prob, bool pad, bool pull) const {
+  CommArgs a = comm_args(true, pad, pull);
   a.rows = tokens;
+  a.unit_prob = topk_prob;
   a.buf_ptrs = ptr<void* const>("xbuf_ptrs");
   a.meta_ptrs = ptr<int2* const>("meta_ptrs");
+  a.rowp_ptrs = ptr<float* const>("rowp_ptrs");
   a.local_buf = ptr<void>("xbuf");
+  a.local_meta = ptr<int2>("meta");
   a.arrive_off = 0;
+  return a;
+}
+CommArgs MoeRuntime::comm_backward(const void* dout) const {
+  CommArgs a = comm_args(true, true, false);
+  a.rows = dout;
+  a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
+  a.local_buf = ptr<void>("dybuf");
+  a.arrive_off = n_tiles_;
+  return a;
+}
+
+void MoeRuntime::dispatch_tokens(const void* tokens, const float* topk_prob, int num_units, cudaStream_t stream, bool zero_pad) {
+  if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
+  const CommArgs a = comm_forward(tokens, topk_prob, zero_pad, false);
   check(launch_comm(a, cfg_.num_sms, sp_.status, stream), "dispatch");
 }
 
@@ -300,6 +319,7 @@ void MoeRuntime::gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int 
     g.done_slot = extra.done_slot;
     g.done_R = cfg_.R;
   }
+  g.row_scale = extra.row_scale;
   if (extra.comm != nullptr) g.comm = *extra.comm;
   check(launch_grouped_gemm(a, b, g, cfg_.num_sms, stream), extra.comm ? "grouped_gemm+transport" : "grouped_gemm");
 }
@@ -308,19 +328,16 @@ void MoeRuntime::gemm1(cudaStream_t stream) {
   GemmExtra x;
   x.gate = 1;
   x.gate_pull = true;
+  x.row_scale = ptr<const float>("rowp");
   gemm(kFwd1, tm_x_k_, tm_w1_k_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), ptr<void>("act"), nullptr, nullptr, stream, x);
 }
-void MoeRuntime::gemm1_fused(const void* tokens, int num_units, cudaStream_t stream) {
+void MoeRuntime::gemm1_fused(const void* tokens, const float* topk_prob, int num_units, cudaStream_t stream) {
   if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
-  CommArgs a = comm_args(true, true, true);
-  a.rows = tokens;
-  a.buf_ptrs = ptr<void* const>("xbuf_ptrs");
-  a.meta_ptrs = ptr<int2* const>("meta_ptrs");
-  a.local_buf = ptr<void>("xbuf");
-  a.arrive_off = 0;
+  const CommArgs a = comm_forward(tokens, topk_prob, true, true);
   GemmExtra x;
   x.gate = 1;
   x.gate_pull = true;
+  x.row_scale = ptr<const float>("rowp");
   x.comm = &a;
   gemm(kFwd1, tm_x_k_, tm_w1_k_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), ptr<void>("act"), nullptr, nullptr, stream, x);
 }
@@ -339,10 +356,10 @@ UnitReduceWait MoeRuntime::reduce_wait(int slot) const {
   w.status = sp_.status;
   return w;
 }
-void MoeRuntime::reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream, bool wait_peers) {
+void MoeRuntime::reduce_out(void* out, int num_tokens, cudaStream_t stream, bool wait_peers, const float* unit_scale) {
   const UnitReduceWait w = reduce_wait(2);
-  check(launch_unit_reduce(ptr<void>("ybuf"), topk_prob, out, num_tokens, cfg_.topk, cfg_.H,
-                           wait_peers && peers() ? &w : nullptr, stream),
+  check(launch_unit_reduce(ptr<void>("ybuf"), unit_scale, out, num_tokens, cfg_.topk, cfg_.H,
+                           wait_peers && peers() ? &w : nullptr, nullptr, nullptr, stream),
         "unit_reduce");
 }
 
@@ -458,22 +475,13 @@ void MoeRuntime::forward_fp8(const void* tokens, const int64_t* topk_idx, const 
   act_fp8(stream);
   gemm2_fp8(stream);
   barrier(2, stream);
-  reduce_out(topk_prob, out, num_tokens, stream);
+  reduce_out(out, num_tokens, stream, false, topk_prob);
 }
 
 // ------------------------------------------------------------------ backward pieces
-void MoeRuntime::dispatch_grads(const void* dout, const float* topk_prob, float* dprob, int num_units,
-                                cudaStream_t stream) {
+void MoeRuntime::dispatch_grads(const void* dout, int num_units, cudaStream_t stream) {
   if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
-  CommArgs a = comm_args(true, true, false);
-  a.rows = dout;
-  a.unit_scale = topk_prob;
-  a.saved_out = ptr<void>("ybuf");
-  a.unit_dot = dprob;
-  a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
-  a.meta_ptrs = nullptr;
-  a.local_buf = ptr<void>("dybuf");
-  a.arrive_off = n_tiles_;
+  const CommArgs a = comm_backward(dout);
   check(launch_comm(a, cfg_.num_sms, sp_.status, stream), "dispatch_grads");
 }
 void MoeRuntime::wgrad2(cudaStream_t stream) {
@@ -481,46 +489,32 @@ void MoeRuntime::wgrad2(cudaStream_t stream) {
   x.gate = 2;
   gemm(kWgrad, tm_dy_mn_, tm_act_mn_, cfg_.F, 0, cfg_.H, ptr<void>("gw2"), nullptr, nullptr, nullptr, stream, x);
 }
+void MoeRuntime::swiglu_pass(cudaStream_t stream) {
+  SwigluBwdArgs a{};
+  a.dact = ptr<void>("dact");
+  a.h = ptr<void>("hbuf");
+  a.rows = cfg_.row_capacity;
+  a.F = cfg_.F;
+  a.row_limit = tables_.totals;
+  a.rowp = ptr<const float>("rowp");
+  a.meta = ptr<const int2>("meta");
+  a.dprob_ptrs = ptr<float* const>("dprob_ptrs");
+  check(launch_swiglu_backward(a, stream), "swiglu_backward");
+}
 void MoeRuntime::dgrad2(cudaStream_t stream) {
   GemmExtra x;
   x.gate = 2;
-  void* dact = ptr<void>("dact", false);
-  if (dact == nullptr || cfg_.fused_dgrad2) {
-    // SwiGLU gradient inside the GEMM epilogue (reads and rewrites the saved pre-activations row by row)
-    gemm(kDgrad2, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("hbuf"), nullptr, nullptr, nullptr, stream, x);
-    return;
-  }
-  // Plain Dgrad GEMM into `dact`, then one coalesced elementwise pass: the fused epilogue's per-row
-  // global loads of the pre-activations are latency-bound and keep the tensor pipe at ~40 %, so the two
-  // launches together are faster than the fused one.
-  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, dact, nullptr, nullptr, nullptr, stream, x);
-  check(launch_swiglu_backward(dact, ptr<void>("hbuf"), cfg_.row_capacity, cfg_.F, tables_.totals, stream),
-        "swiglu_backward");
+  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("dact"), nullptr, nullptr, nullptr, stream, x);
+  swiglu_pass(stream);
 }
-void MoeRuntime::dgrad2_fused(const void* dout, const float* topk_prob, float* dprob, int num_units,
-                              cudaStream_t stream) {
+void MoeRuntime::dgrad2_fused(const void* dout, int num_units, cudaStream_t stream) {
   if (num_units > cfg_.max_units) throw std::runtime_error("MoeRuntime: more routing units than max_units");
-  void* dact = ptr<void>("dact", false);
-  if (dact == nullptr || cfg_.fused_dgrad2) {  // no plain-Dgrad2 buffer: transport first, then the in-place variant
-    dispatch_grads(dout, topk_prob, dprob, num_units, stream);
-    dgrad2(stream);
-    return;
-  }
-  CommArgs a = comm_args(true, true, false);
-  a.rows = dout;
-  a.unit_scale = topk_prob;
-  a.saved_out = ptr<void>("ybuf");
-  a.unit_dot = dprob;
-  a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
-  a.meta_ptrs = nullptr;
-  a.local_buf = ptr<void>("dybuf");
-  a.arrive_off = n_tiles_;
+  const CommArgs a = comm_backward(dout);
   GemmExtra x;
   x.gate = 2;
   x.comm = &a;
-  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, dact, nullptr, nullptr, nullptr, stream, x);
-  check(launch_swiglu_backward(dact, ptr<void>("hbuf"), cfg_.row_capacity, cfg_.F, tables_.totals, stream),
-        "swiglu_backward");
+  gemm(kDgrad1, tm_dy_k_, tm_w2_mn_, cfg_.F, cfg_.H, 0, ptr<void>("dact"), nullptr, nullptr, nullptr, stream, x);
+  swiglu_pass(stream);
 }
 void MoeRuntime::wgrad1(cudaStream_t stream) {
   gemm(kWgrad, tm_dh_mn_, tm_x_mn_, cfg_.H, 0, 2 * cfg_.F, ptr<void>("gw1"), nullptr, nullptr, nullptr, stream);
@@ -531,10 +525,10 @@ void MoeRuntime::dgrad1(cudaStream_t stream) {
   gemm(kDgrad1, tm_dh_k_, tm_w1_mn_, cfg_.H, 2 * cfg_.F, 0, nullptr, nullptr, ptr<void* const>("dxbuf_ptrs"),
        ptr<const int2>("meta"), stream, x);
 }
-void MoeRuntime::reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream, bool wait_peers) {
+void MoeRuntime::reduce_dtokens(void* dtokens, float* dprob, int num_tokens, cudaStream_t stream, bool wait_peers) {
   const UnitReduceWait w = reduce_wait(4);
   check(launch_unit_reduce(ptr<void>("dxbuf"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H,
-                           wait_peers && peers() ? &w : nullptr, stream),
+                           wait_peers && peers() ? &w : nullptr, ptr<const float>("dprob"), dprob, stream),
         "unit_reduce(bwd)");
 }
 void MoeRuntime::reduce_weight_grads(cudaStream_t stream) {
@@ -600,10 +594,10 @@ void MoeRuntime::forward(const void* tokens, const int64_t* topk_idx, const floa
   route(topk_idx, U, stream);
   mark("route", stream);
   if (cfg_.fused_comm) {
-    gemm1_fused(tokens, U, stream);
+    gemm1_fused(tokens, topk_prob, U, stream);
     mark("dispatch+pull+gemm1", stream);
   } else {
-    dispatch_tokens(tokens, U, stream);
+    dispatch_tokens(tokens, topk_prob, U, stream);
     pull_weights(stream);
     mark("dispatch+pull", stream);
     gemm1(stream);
@@ -611,20 +605,19 @@ void MoeRuntime::forward(const void* tokens, const int64_t* topk_idx, const floa
   }
   gemm2(stream);
   mark("gemm2", stream);
-  reduce_out(topk_prob, out, num_tokens, stream, true);
+  reduce_out(out, num_tokens, stream, true);
   mark("reduce_out", stream);
   mark("fwd_end", stream);
 }
 
-void MoeRuntime::backward(const void* dout, const float* topk_prob, void* dtokens, float* dprob, int num_tokens,
-                          cudaStream_t stream) {
+void MoeRuntime::backward(const void* dout, void* dtokens, float* dprob, int num_tokens, cudaStream_t stream) {
   const int U = num_tokens * cfg_.topk;
   mark("bwd_begin", stream);
   if (cfg_.fused_comm) {
-    dgrad2_fused(dout, topk_prob, dprob, U, stream);
+    dgrad2_fused(dout, U, stream);
     mark("dispatch_grads+dgrad2", stream);
   } else {
-    dispatch_grads(dout, topk_prob, dprob, U, stream);
+    dispatch_grads(dout, U, stream);
     mark("dispatch_grads", stream);
     dgrad2(stream);
     mark("dgrad2", stream);
@@ -648,7 +641,7 @@ void MoeRuntime::backward(const void* dout, const float* topk_prob, void* dtoken
   }
   dgrad1(stream);
   mark("dgrad1", stream);
-  reduce_dtokens(dtokens, num_tokens, stream, true);
+  reduce_dtokens(dtokens, dprob, num_tokens, stream, true);
   mark("reduce_dtokens", stream);
   if (side) {
     if (cudaStreamWaitEvent(stream, ev_join_, 0) != cudaSuccess) throw std::runtime_error("MoeRuntime: could not join the side stream");

@@ -30,7 +30,6 @@ struct LayerConfig {
   int64_t s_tok = 0;
   int num_sms = 148;
   int gemm_ctas = 2;        // 2: grouped GEMMs run on CTA pairs (256-row tiles); 1: single CTAs (128-row tiles)
-  int fused_dgrad2 = 0;     // 1: SwiGLU gradient in the Dgrad2 epilogue; 0: plain GEMM + elementwise pass (needs 'dact')
   int accum_fp32 = 0;       // dtype of the optional gradient accumulation buffers (acc_gw1/acc_gw2)
   int multi_rank_sync = 1;  // 0: one process emulates all ranks, kernels are ordered by the stream
   int fused_comm = 1;       // 1: forward()/backward() run the token transport on spare warps of the consuming
@@ -51,26 +50,30 @@ class MoeRuntime {
   // Stand-alone transport of the token rows (CommArgs in route.h): rows stored into the hosts' buffers at
   // their final position, arrival counters advanced per M-tile.
   // zero_pad: clear the padding rows behind every group (needed when a backward pass will contract over them)
-  void dispatch_tokens(const void* tokens, int num_units, cudaStream_t stream, bool zero_pad = true);
+  void dispatch_tokens(const void* tokens, const float* topk_prob, int num_units, cudaStream_t stream, bool zero_pad = true);
   void pull_weights(cudaStream_t stream);   // stand-alone replica weight pull (per-slot counters advanced)
   void barrier(int slot, cudaStream_t stream);
   void gemm1(cudaStream_t stream);          // gated per M-tile on the arrival counters, per replica slot on the pull counters
   // One kernel: transport warps send this rank's rows and pull its replica weights while the other
   // warps run GEMM1 on the tiles whose rows have arrived.
-  void gemm1_fused(const void* tokens, int num_units, cudaStream_t stream);
+  void gemm1_fused(const void* tokens, const float* topk_prob, int num_units, cudaStream_t stream);
   void gemm2(cudaStream_t stream);          // rows stored to their source ranks; the last CTA signals every peer
-  // wait_peers: first wait (bounded, in the kernel) for every rank's completion signal of gemm2
-  void reduce_out(const float* topk_prob, void* out, int num_tokens, cudaStream_t stream, bool wait_peers = false);
+  // Sum of every token's unit rows (already gate-weighted: the weight was folded into the activation).
+  // wait_peers: first wait (bounded, in the kernel) for every rank's completion signal of gemm2.
+  // unit_scale (fp8 inference path only): the rows are unweighted and scaled here.
+  void reduce_out(void* out, int num_tokens, cudaStream_t stream, bool wait_peers = false, const float* unit_scale = nullptr);
   // ---- backward pieces
-  void dispatch_grads(const void* dout, const float* topk_prob, float* dprob, int num_units, cudaStream_t stream);
+  void dispatch_grads(const void* dout, int num_units, cudaStream_t stream);   // pure copy of the gradient rows
   void wgrad2(cudaStream_t stream);
+  // Plain Dgrad2 GEMM, then the SwiGLU-gradient pass, which also applies the row's gate weight and stores
+  // the row's gate-weight gradient into the source rank's symmetric `dprob` buffer.
   void dgrad2(cudaStream_t stream);
-  // One kernel: transport warps send dout (scaled by the gate weight, with the gate-weight gradient)
-  // while the other warps run the plain Dgrad2 GEMM; followed by the SwiGLU-gradient pass.
-  void dgrad2_fused(const void* dout, const float* topk_prob, float* dprob, int num_units, cudaStream_t stream);
+  // One kernel: transport warps send dout while the other warps run the plain Dgrad2 GEMM; then the pass.
+  void dgrad2_fused(const void* dout, int num_units, cudaStream_t stream);
   void wgrad1(cudaStream_t stream);
   void dgrad1(cudaStream_t stream);
-  void reduce_dtokens(void* dtokens, int num_tokens, cudaStream_t stream, bool wait_peers = false);
+  // Also hands the gate-weight gradients (stored by the hosts into this rank's symmetric buffer) to `dprob`.
+  void reduce_dtokens(void* dtokens, float* dprob, int num_tokens, cudaStream_t stream, bool wait_peers = false);
   void reduce_weight_grads(cudaStream_t stream);
 
   // ---- block-scaled fp8 forward (inference): present when the fp8 weight regions were given
@@ -87,8 +90,7 @@ class MoeRuntime {
   // ---- whole passes
   void forward(const void* tokens, const int64_t* topk_idx, const float* topk_prob, void* out, int num_tokens,
                cudaStream_t stream);
-  void backward(const void* dout, const float* topk_prob, void* dtokens, float* dprob, int num_tokens,
-                cudaStream_t stream);
+  void backward(const void* dout, void* dtokens, float* dprob, int num_tokens, cudaStream_t stream);
 
   // Optional per-phase device timing: events are recorded around every phase of forward() and
   // backward(); phase_times() synchronises and returns (name, ms) pairs of the last pass pair.
@@ -114,6 +116,7 @@ class MoeRuntime {
     int gate = 0;        // 1: gate A on the forward arrival counters, 2: on the backward ones
     bool gate_pull = false;
     int done_slot = 0;   // > 0: signal every peer on this slot when the launch is complete
+    const float* row_scale = nullptr;
     const CommArgs* comm = nullptr;
   };
   void gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int N, int K, int M_out, void* out0, void* out1,
@@ -123,6 +126,9 @@ class MoeRuntime {
     gemm(mode, a, b, N, K, M_out, out0, out1, out_ptrs, meta, stream, GemmExtra{});
   }
   CommArgs comm_args(bool dispatch, bool pad, bool pull) const;
+  CommArgs comm_forward(const void* tokens, const float* topk_prob, bool pad, bool pull) const;
+  CommArgs comm_backward(const void* dout) const;
+  void swiglu_pass(cudaStream_t stream);
   bool peers() const { return cfg_.multi_rank_sync && cfg_.R > 1; }
   UnitReduceWait reduce_wait(int slot) const;
   void tmap2(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t bc, uint32_t br);

@@ -26,14 +26,14 @@ def _oracle(tokens, idx, prob, w1, w2, dout):
     return out.detach(), x.grad, p.grad, a.grad, b.grad
 
 
-@pytest.mark.parametrize("ctas,fused_dgrad2", [(1, False), (2, False), (2, True)])
-def test_single_rank_forward_backward(ctas, fused_dgrad2):
+@pytest.mark.parametrize("ctas,fused_comm", [(1, True), (2, True), (2, False)])
+def test_single_rank_forward_backward(ctas, fused_comm):
     from ep_balance_b200.models.emulated import EmulatedCluster
     from ep_balance_b200.models.moe_layer import MoEConfig
 
     torch.manual_seed(0)
     cfg = MoEConfig(hidden=256, ffn=384, num_experts=8, top_k=2, max_tokens=512, gemm_ctas=ctas,
-                    fused_dgrad2=fused_dgrad2)
+                    fused_comm=fused_comm)
     cl = EmulatedCluster(cfg, world=1)
     layer = cl.layers[0]
     tokens = torch.randn(512, 256, device="cuda").bfloat16()
