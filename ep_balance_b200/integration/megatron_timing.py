@@ -1,103 +1,113 @@
 """Region timing around an unmodified Megatron ``MoELayer`` (``native/*`` regions).
 
-The layer's leaf methods are wrapped, not re-implemented; ``remove()`` restores every one of them.
-Reference: eplb/integration/megatron_timing.py:26-144.
+The layer keeps running its own code.  A declarative list names the calls to time (attribute path on
+the layer, region name, required or optional); each is shadowed on its owner *instance* by a timed
+forwarder, and every shadow registers its own undo step on an ``ExitStack``, so ``remove()`` (or a
+failure half-way through binding) unwinds exactly what was installed, newest first.
+Reference: eplb/integration/megatron_timing.py:26-144 (same public names and regions).
 """
 
 from __future__ import annotations
 
+import contextlib
 import functools
-import types
-from typing import Callable, List, Optional
+from typing import Callable, List, Optional, Tuple
 
 import torch
 
 from ..utils import profiling
 
+# (path of the owner below the layer, method, region, required)
+TIMED_CALLS: Tuple[Tuple[str, str, str, bool], ...] = (
+    ("router", "forward", "native/route", True),
+    ("", "dispatch", "native/dispatch", True),
+    ("experts", "forward", "native/expert_gemm", True),
+    ("", "combine", "native/combine", True),
+    ("shared_experts", "forward", "native/shared_expert", False),
+)
+_MARK = "_eplb_native_timing"
 
-def _first_device(args, kwargs):
-    for v in (*args, *kwargs.values()):
+
+def _device_of(values) -> Optional[torch.device]:
+    """Device of the first tensor among the call's arguments (one level into tuples and lists)."""
+    stack = list(values)
+    for v in stack:
         if isinstance(v, torch.Tensor):
             return v.device
         if isinstance(v, (tuple, list)):
-            for item in v:
-                if isinstance(item, torch.Tensor):
-                    return item.device
+            for inner in v:
+                if isinstance(inner, torch.Tensor):
+                    return inner.device
     return None
+
+
+def _shadow(undo: contextlib.ExitStack, owner, name: str, replacement: Callable) -> None:
+    """Install ``replacement`` as instance attribute ``owner.name`` and register how to take it off again."""
+    instance_dict = vars(owner)
+    if name in instance_dict:
+        previous = instance_dict[name]
+        undo.callback(setattr, owner, name, previous)
+    else:
+        undo.callback(lambda: vars(owner).pop(name, None))
+    setattr(owner, name, replacement)
 
 
 class NativeMoETimingBinding:
     def __init__(self, moe_layer, *, layer_id: int, mode: str, logger: Optional[Callable[[str], None]]) -> None:
         if mode not in ("off", "observe"):
             raise ValueError("native MoE timing mode must be 'off' or 'observe'")
-        if getattr(moe_layer, "_eplb_native_timing", None) is not None:
+        if getattr(moe_layer, _MARK, None) is not None:
             raise RuntimeError("native MoE timing is already bound to this layer")
         self.moe_layer, self.layer_id, self.mode, self.logger = moe_layer, int(layer_id), mode, logger
         self.micro_batch_id = 0
-        self._undo = []
-        try:
-            self._time(moe_layer.router, "forward", "native/route")
-            self._time(moe_layer, "dispatch", "native/dispatch")
-            self._time(moe_layer.experts, "forward", "native/expert_gemm")
-            self._time(moe_layer, "combine", "native/combine")
-            shared = getattr(moe_layer, "shared_experts", None)
-            if shared is not None and callable(getattr(shared, "forward", None)):
-                self._time(shared, "forward", "native/shared_expert")
-            self._wrap_forward()
-            moe_layer._eplb_native_timing = self
-        except Exception:
-            self.remove()
-            raise
+        self._undo = contextlib.ExitStack()
+        with contextlib.ExitStack() as guard:
+            guard.push(self._undo)  # a failure below unwinds whatever was installed so far
+            for path, method, region, required in TIMED_CALLS:
+                owner = moe_layer if not path else getattr(moe_layer, path, None)
+                target = getattr(owner, method, None) if owner is not None else None
+                if not callable(target):
+                    if not required:
+                        continue
+                    raise RuntimeError(f"cannot time {type(moe_layer).__name__}.{path + '.' if path else ''}{method}: "
+                                       "no such callable on this Megatron version")
+                _shadow(self._undo, owner, method, self._timed(target, region))
+            _shadow(self._undo, moe_layer, "forward", self._windowed(moe_layer.forward))
+            setattr(moe_layer, _MARK, self)
+            self._undo.callback(lambda: vars(moe_layer).pop(_MARK, None))
+            guard.pop_all()  # keep everything installed; remove() closes self._undo later
 
-    def _swap(self, owner, name: str, new) -> None:
-        ns = vars(owner)
-        self._undo.append((owner, name, name in ns, ns.get(name)))
-        setattr(owner, name, new)
+    @staticmethod
+    def _timed(bound_call: Callable, region: str) -> Callable:
+        @functools.wraps(bound_call)
+        def forwarder(*args, **kwargs):
+            with profiling.record(region, time_it=True, device=_device_of((*args, *kwargs.values()))):
+                return bound_call(*args, **kwargs)
 
-    def _time(self, owner, name: str, region: str) -> None:
-        original = getattr(owner, name, None)
-        if not callable(original):
-            who = type(owner).__name__ if owner is not None else "None"
-            raise RuntimeError(f"native MoE timing requires callable {who}.{name}; "
-                               "the installed Megatron MoE API is incompatible")
+        return forwarder
 
-        @functools.wraps(original)
-        def timed(_self, *args, **kwargs):
-            with profiling.record(region, time_it=True, device=_first_device(args, kwargs)):
-                return original(*args, **kwargs)
+    def _windowed(self, bound_forward: Callable) -> Callable:
+        placeholders = {"expert_transfer": "n/a"}
+        if self.mode == "off":
+            placeholders.update(solver="n/a", omega_gather="n/a")
 
-        self._swap(owner, name, types.MethodType(timed, owner))
-
-    def _wrap_forward(self) -> None:
-        original = self.moe_layer.forward
-
-        @functools.wraps(original)
-        def timed_forward(_self, *args, **kwargs):
-            mb = self.micro_batch_id
-            self.micro_batch_id += 1
+        @functools.wraps(bound_forward)
+        def forwarder(*args, **kwargs):
+            mb, self.micro_batch_id = self.micro_batch_id, self.micro_batch_id + 1
             profiling.begin_debug_window()
-            out = original(*args, **kwargs)
-            missing = {"expert_transfer": "n/a"}
-            if self.mode == "off":
-                missing.update({"solver": "n/a", "omega_gather": "n/a"})
+            result = bound_forward(*args, **kwargs)
             profiling.maybe_summary(self.logger, context=f"mode={self.mode} layer={self.layer_id} mb={mb}",
-                                    missing=missing)
-            return out
+                                    missing=placeholders)
+            return result
 
-        self._swap(self.moe_layer, "forward", types.MethodType(timed_forward, self.moe_layer))
+        return forwarder
 
     def remove(self) -> None:
-        for owner, name, had, old in reversed(self._undo):
-            if had:
-                setattr(owner, name, old)
-            elif name in vars(owner):
-                delattr(owner, name)
-        self._undo.clear()
-        if getattr(self.moe_layer, "_eplb_native_timing", None) is self:
-            delattr(self.moe_layer, "_eplb_native_timing")
+        """Take every forwarder off again; the layer is as it was before binding."""
+        self._undo.close()
 
 
 def bind_native_moe_timing(model, *, mode: str, logger: Optional[Callable[[str], None]] = print
                            ) -> List[NativeMoETimingBinding]:
     layers = [m for m in model.modules() if type(m).__name__ == "MoELayer"]
-    return [NativeMoETimingBinding(l, layer_id=i, mode=mode, logger=logger) for i, l in enumerate(layers)]
+    return [NativeMoETimingBinding(layer, layer_id=i, mode=mode, logger=logger) for i, layer in enumerate(layers)]

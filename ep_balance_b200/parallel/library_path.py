@@ -38,7 +38,7 @@ def _env_truthy(name: str, default: str = "0") -> bool:
     return os.environ.get(name, default).strip().lower() not in ("0", "", "false", "no")
 
 
-# ====================================================================== plan-derived tables (§9.4)
+# ====================================================================== tables derived from the plan (reference: eplb_manager.py:482-536)
 def split_sizes(plan: Plan, my_rank: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """``(sent_per_dst[R], recv_per_src[R], recv_per_expert[E])`` for this rank, on the plan's device."""
     q = plan.q.to(torch.int64)

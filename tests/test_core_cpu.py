@@ -111,14 +111,7 @@ def test_trace_round_trip_and_analysis(tmp_path):
 
 
 def _debug_window(monkeypatch):
-    monkeypatch.setattr(profiling, "_PROFILE_ENABLED", False)
-    monkeypatch.setattr(profiling, "_DEBUG_ENABLED", True)
-    monkeypatch.setattr(profiling, "_ENABLED", True)
-    monkeypatch.setattr(profiling, "_STATS", OrderedDict())
-    monkeypatch.setattr(profiling, "_WINDOW_STATS", OrderedDict())
-    monkeypatch.setattr(profiling, "_PENDING", [])
-    monkeypatch.setattr(profiling, "_calls", 0)
-    monkeypatch.setattr(profiling, "_debug_logger", None)
+    monkeypatch.setattr(profiling, "_P", profiling.Profiler(debug=True))
     profiling.begin_debug_window()
 
 
@@ -134,11 +127,27 @@ def test_debug_timing_line_format(monkeypatch):
     assert len(lines) == 1 and lines[0].startswith("[EPLB-debug] layer=3 mb=7 ")
     assert "solver=" in lines[0] and "dispatch=" in lines[0] and "ms(x2)" in lines[0]
     assert "/8.00MiB/" in lines[0] and "GB/s" in lines[0]
-    assert not profiling._WINDOW_STATS
+    assert not profiling.current().window
     with profiling.record("apply/grad_move", time_it=True, device="cpu"):
         pass
     profiling.begin_debug_window()  # backward phases are reported at the next window
     assert any("direction=backward" in l and "expert_grad_reduce=" in l for l in lines)
+
+
+def test_profile_table_and_rank_reduction(monkeypatch):
+    monkeypatch.setattr(profiling, "_P", profiling.Profiler(profile=True, every=2, rank="3"))
+    lines = []
+    for _ in range(2):
+        with profiling.record("apply/expert_gemm", time_it=True, device="cpu", payload_bytes=1 << 20):
+            pass
+        profiling.maybe_summary(lines.append)
+    assert len(lines) == 1 and lines[0].startswith("[EPLB-profile r3] region")
+    assert "apply/expert_gemm" in lines[0] and "peak memory" in lines[0]
+    assert profiling.stats()["apply/expert_gemm"].count == 2 and profiling.last_ms("apply/expert_gemm") >= 0.0
+    mean_max = profiling.reduce_over_ranks()  # no process group: this rank alone
+    assert set(mean_max) == {"apply/expert_gemm"} and mean_max["apply/expert_gemm"][0] == mean_max["apply/expert_gemm"][1]
+    profiling.reset()
+    assert "no samples" in profiling.summary_str()
 
 
 def test_rebalancer_ring_and_backward():

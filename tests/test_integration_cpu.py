@@ -169,11 +169,7 @@ def test_routing_to_units_fixed_topk_equals_nonzero_path():
 
 
 def test_native_timing_wraps_and_restores(monkeypatch):
-    monkeypatch.setattr(profiling, "_DEBUG_ENABLED", True)
-    monkeypatch.setattr(profiling, "_ENABLED", True)
-    monkeypatch.setattr(profiling, "_STATS", OrderedDict())
-    monkeypatch.setattr(profiling, "_WINDOW_STATS", OrderedDict())
-    monkeypatch.setattr(profiling, "_PENDING", [])
+    monkeypatch.setattr(profiling, "_P", profiling.Profiler(debug=True))
     layer = MoELayer()
     model = nn.Sequential(layer)
     original = layer.forward
@@ -187,3 +183,10 @@ def test_native_timing_wraps_and_restores(monkeypatch):
         bind_native_moe_timing(model, mode="off")
     binding.remove()
     assert layer.forward.__func__ is original.__func__ and not hasattr(layer, "_eplb_native_timing")
+    assert "forward" not in vars(layer.router) and "dispatch" not in vars(layer)
+    # a layer without a required call: nothing stays installed
+    broken = MoELayer()
+    broken.combine = None
+    with pytest.raises(RuntimeError):
+        bind_native_moe_timing(nn.Sequential(broken), mode="off")
+    assert "forward" not in vars(broken.router) and not hasattr(broken, "_eplb_native_timing")
