@@ -159,7 +159,9 @@ def timed_loop(step_fn, steps: int, world: int, finish=None):
     return float(ms) / steps
 
 
-def emit(args, world, impl, ms_dev, ms_e2e, launches, clocks, h2d, d2h, extra_cfg):
+def emit(args, world, impl, ms_dev, ms_e2e, launches, clocks, h2d, d2h, quality, notes):
+    """One JSON line.  ``config`` has the same keys and values in both arms; what is specific to an arm goes to
+    ``quality`` (plan quality of the last step: rank load max/mean, replicas, plan digest) and ``notes``."""
     tokens_total = args.tokens * world
     line = {
         "metric": "moe_layer_train_tokens_per_s", "value": tokens_total / (ms_dev * 1e-3), "unit": "tokens/s",
@@ -170,8 +172,9 @@ def emit(args, world, impl, ms_dev, ms_e2e, launches, clocks, h2d, d2h, extra_cf
                    "global_batch": tokens_total, "seq_len": args.tokens, "parallelism": f"ep{world}",
                    "domains": DOMAINS.get(world, 1), "replica_slots_per_rank": CFG["extra_slots"] if world > 1 else 0,
                    "step": "forward + backward + fused AdamW, plan solved every step",
-                   "l2": "per-step working set (activations + expert weights) is several hundred MB, far above the 126 MB L2",
-                   **extra_cfg},
+                   "l2": "per-step working set (activations + expert weights) is several hundred MB, far above the 126 MB L2"},
+        "quality": quality,
+        "notes": notes,
         "clocks": clocks,
         "e2e": {"value": tokens_total / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -330,14 +333,16 @@ def run_ours(args):
                     print(f"[phase] {name:<20} mean {mean:8.3f} ms   max over ranks {mx:8.3f} ms", file=sys.stderr)
     plan = layer.last_plan()
     loads = layer.rank_loads().float()
-    extra = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(plan.x.sum()) - CFG["num_experts"],
-             "gemm_ctas": args.gemm_ctas,
+    quality = {"rank_load_max_over_mean": float(loads.max() / loads.mean()),
+               "replicas": int(plan.x.sum()) - CFG["num_experts"], "plan_digest": plan.digest()[:16]}
+    notes = {"gemm_ctas": args.gemm_ctas, "fused_transport": bool(layer.rt_config["fused_comm"]),
              "e2e_step": e2e_mode,
              "e2e_loop": "input H2D prefetched on a side stream (ring of 3 staging buffers); loss D2H copied "
                          "asynchronously and read by the host two steps later, the outstanding ones before the closing event",
-             "kernels": "tcgen05 grouped GEMM (6 modes), device solver, P2P dispatch/combine, peer-load weight pull + grad return, fused AdamW"}
+             "kernels": "tcgen05 grouped GEMM with transport warps (dispatch + replica pull inside GEMM1, gradient dispatch "
+                        "inside Dgrad2), per-tile arrival counters, device solver, peer-load grad return, fused AdamW"}
     if rank == 0:
-        emit(args, world, "ours", ms_dev, ms_e2e, launches, clocks, batches[0].numel() * 2, 4, extra)
+        emit(args, world, "ours", ms_dev, ms_e2e, launches, clocks, batches[0].numel() * 2, 4, quality, notes)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -432,6 +437,7 @@ def run_reference(args):
         weights_local[e] = (w1, w2)
         params += [w1, w2]
     weight_shapes = [torch.Size((2 * Fd, H)), torch.Size((H, Fd))]
+    last = {"plan": None}
     bias = router_bias_for_imbalance(E, K, CFG["router_std"] * H ** 0.5, CFG["imbalance_target"]).to(dev)
     opt = torch.optim.AdamW(params, lr=1e-5, fused=True)
     batched = make_batched_gated_mlp(True, F.silu)
@@ -450,6 +456,7 @@ def run_reference(args):
         unit_expert = top_idx.reshape(-1).contiguous()
         local_row = torch.bincount(unit_expert, minlength=E).to(torch.int64)
         plan = reb.rebalance(local_row, 0, state["mb"], group=None).plan
+        last["plan"] = plan
         state["mb"] += 1
         out = sync_free_moe_forward(
             tokens=x, unit_token_idx=tok_idx, unit_expert=unit_expert, unit_prob=prob.reshape(-1).to(x.dtype),
@@ -488,9 +495,16 @@ def run_reference(args):
     ms_e2e = timed_loop(step_e2e, args.steps, world)
     clocks = sampler.stop() if rank == 0 else {}
     if rank == 0:
-        emit(args, world, "reference", ms_dev, ms_e2e, 0, clocks, batches[0].numel() * 2, 4,
+        from ep_balance_b200.core.plan import Plan  # digest of the reference's plan in this repo's plan format
+
+        rp = last["plan"]
+        loads = rp.q.sum((0, 1)).float()
+        quality = {"rank_load_max_over_mean": float(loads.max() / loads.mean()), "replicas": int(rp.x.sum()) - E,
+                   "plan_digest": Plan(rp.x.clone(), rp.q.to(torch.int64), rp.theta).digest()[:16]}
+        emit(args, world, "reference", ms_dev, ms_e2e, 0, clocks, batches[0].numel() * 2, 4, quality,
              {"path": "eplb.EPLBRebalancer.rebalance + eplb.integration.sync_free_moe_forward (AllToAllAdapter, "
-                      "dist.broadcast replicas, torch._grouped_mm), unmodified from baseline/_ref"})
+                      "dist.broadcast replicas, torch._grouped_mm), unmodified from baseline/_ref; stock knobs",
+              "knobs": {k: os.environ[k] for k in ("EPLB_CHUNKS", "EPLB_OVERLAP", "EPLB_MANUAL_BWD") if k in os.environ}})
     dist.barrier()
     dist.destroy_process_group()
 

@@ -154,14 +154,12 @@ def bind_fused_moe_layer(moe_layer, fused_layer) -> None:
             fused_layer.w2[i].copy_(w2.to(fused_layer.w2.dtype))
 
     def forward(self, hidden_states, *args, **kwargs):
-        from ..models.moe_layer import _FusedMoEFunction
-
         shape = hidden_states.shape
         tokens = hidden_states.reshape(-1, shape[-1]).contiguous()
         probs, routing_map = self.router(hidden_states)
         k = int(self.config.moe_router_topk)
         _, ue, up = _routing_to_units(probs, routing_map, tokens.shape[0], fused_layer.cfg.num_experts, topk=k)
-        out = _FusedMoEFunction.apply(tokens, ue.view(-1, k).contiguous(), up.float().view(-1, k).contiguous(), fused_layer)
+        out = fused_layer.apply_routed(tokens, ue.view(-1, k), up.view(-1, k))
         out = out.reshape(shape)
         if getattr(self, "use_shared_expert", False):
             out = out + self.shared_experts_compute(hidden_states)

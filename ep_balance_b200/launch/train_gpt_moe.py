@@ -136,6 +136,9 @@ def main(argv=None):
         gen.set_state(shard["data_rng"])
 
     def save(step: int) -> None:
+        # a step that ran with a non-zero status skipped its expert update; never write such a state down silently
+        monitor.drain()
+        model.check_status()
         save_checkpoint(a.save, step, rank=rank, world=world,
                         replicated={"model": model.replicated_state(), "dense_opt": dense_opt.state_dict(),
                                     "skew_g": skew.g.clone(), "skew_rng": skew.gen.get_state(), "args": vars(a)},
@@ -160,7 +163,7 @@ def main(argv=None):
         if not (want_log or trace is not None) or rank != 0:
             return
         for li, b in enumerate(model.blocks):
-            omega = b.moe.heap.tensor("omega", rank).to(torch.int64)
+            omega = b.moe.omega().to(torch.int64)
             if trace is not None:
                 trace.add(li, mb, omega.cpu())
             if not want_log:
@@ -179,6 +182,9 @@ def main(argv=None):
         print(f"[ep_balance_b200] mode={mode} world={world} domains={cfg.num_domains} extra_slots={extra} "
               f"micro_batches={M} resume_step={start_step}", flush=True)
 
+    from ..utils.status import StatusMonitor
+
+    monitor = StatusMonitor(model.status.words)
     guard = None
     if a.heartbeat_file:
         from ..parallel.health import Heartbeat, StepGuard
@@ -208,6 +214,8 @@ def main(argv=None):
         return 0
     gbs = a.micro_batch * world * M
     flops = _flops_per_step(a, a.micro_batch * a.seq_len * M)
+    if world > 1:
+        dist.barrier()  # start together: device-side waits on the other ranks are bounded
     for step in range(start_step + 1, a.steps + 1):
         if guard is not None:
             guard.before_step(step)
@@ -229,10 +237,12 @@ def main(argv=None):
         model.allreduce_dense_grads()
         gn = torch.nn.utils.clip_grad_norm_(model.dense_parameters(), 1.0)
         dense_opt.step()
-        expert_opt.step()
+        expert_opt.step()      # skipped on the device while any layer's status word is set
         dense_opt.zero_grad(set_to_none=True)
+        monitor.poll()         # asynchronous copy of the status words; raises for a step seen damaged (one or two steps late)
         if step % a.log_every == 0:
             torch.cuda.synchronize()
+            monitor.drain()
             ms = (time.perf_counter() - t0) * 1e3
             lv = total.clone()
             if world > 1:
@@ -253,6 +263,7 @@ def main(argv=None):
         save(a.steps)
     if trace is not None:
         trace.flush()
+    monitor.drain()
     model.check_status()
     if world > 1:
         dist.barrier()

@@ -19,6 +19,7 @@ import torch.nn.functional as F
 
 from ..core.config import EPLBConfig
 from ..parallel.symm import SymmetricHeap
+from ..utils.status import StatusBoard
 from .moe_layer import FusedMoE, MoEConfig, heap_layout
 
 
@@ -92,12 +93,14 @@ class DSv3Stack(nn.Module):
                          max_tokens=cfg.max_tokens, extra_slots=cfg.extra_slots,
                          capacity_factor=cfg.capacity_factor, num_domains=domains,
                          fp8_inference=cfg.fp8_inference)
-        self.heaps: List[SymmetricHeap] = []
+        # one symmetric allocation for the stack: per-layer state + one set of per-step scratch buffers
+        self.heap = SymmetricHeap(heap_layout(mcfg, world, layers=cfg.layers), device, group=group)
+        self.status = StatusBoard(cfg.layers, device)
+        self._scratch: dict = {}
         blocks = []
         for layer in range(cfg.layers):
-            heap = SymmetricHeap(heap_layout(mcfg, world), device, group=group)
-            self.heaps.append(heap)
-            blk = DSv3Block(cfg, FusedMoE(mcfg, heap, rank, world, solver_cfg=solver_cfg, seed=layer))
+            blk = DSv3Block(cfg, FusedMoE(mcfg, self.heap, rank, world, solver_cfg=solver_cfg, seed=layer,
+                                          layer_index=layer, scratch=self._scratch, status=self.status.row(layer)))
             blk.norm.to(device=device, dtype=torch.bfloat16)
             blk.shared.to(device=device, dtype=torch.bfloat16)
             blocks.append(blk)
@@ -122,8 +125,7 @@ class DSv3Stack(nn.Module):
         return x
 
     def check_status(self) -> None:
-        for b in self.blocks:
-            b.moe.check_status()
+        self.status.check_now()
 
     def quantize_weights(self) -> None:
         """Refresh the fp8 copies of every layer's own experts (``DSv3Config.fp8_inference``); collective:

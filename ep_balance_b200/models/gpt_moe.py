@@ -19,6 +19,7 @@ import torch.nn.functional as F
 
 from ..core.config import EPLBConfig
 from ..parallel.symm import SymmetricHeap
+from ..utils.status import StatusBoard
 from .moe_layer import FusedMoE, MoEConfig, heap_layout
 
 
@@ -102,12 +103,15 @@ class GPTMoE(nn.Module):
                          max_tokens=cfg.tokens_per_rank, extra_slots=cfg.extra_slots,
                          capacity_factor=cfg.capacity_factor, num_domains=cfg.num_domains,
                          grad_accum_dtype=cfg.grad_accum_dtype)
-        self.heaps: List[SymmetricHeap] = []
+        # one symmetric allocation (and one handle exchange) for the whole model: per-layer state plus a single
+        # set of per-step scratch buffers shared by all layers; one status board for every layer's status word
+        self.heap = SymmetricHeap(heap_layout(mcfg, world, layers=cfg.layers), device, group=group)
+        self.status = StatusBoard(cfg.layers, device)
+        self._scratch: dict = {}
         blocks = []
         for layer in range(cfg.layers):
-            heap = SymmetricHeap(heap_layout(mcfg, world), device, group=group)
-            self.heaps.append(heap)
-            blocks.append(Block(cfg, FusedMoE(mcfg, heap, rank, world, solver_cfg=solver_cfg, seed=layer)))
+            blocks.append(Block(cfg, FusedMoE(mcfg, self.heap, rank, world, solver_cfg=solver_cfg, seed=layer,
+                                              layer_index=layer, scratch=self._scratch, status=self.status.row(layer))))
         self.embed = nn.Embedding(cfg.vocab, cfg.hidden)
         self.blocks = nn.ModuleList(blocks)
         self.norm = RMSNorm(cfg.hidden)
@@ -170,8 +174,8 @@ class GPTMoE(nn.Module):
         return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
 
     def check_status(self) -> None:
-        for b in self.blocks:
-            b.moe.check_status()
+        """Synchronous read of every layer's status word; raises :class:`MoEStatusError` if one is set."""
+        self.status.check_now()
 
     def zero_expert_grad_accum(self) -> None:
         for b in self.blocks:

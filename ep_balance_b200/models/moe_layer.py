@@ -43,8 +43,7 @@ from ..ops.extension import load
 from ..parallel.symm import HeapLayout, SymmetricHeap
 from ..utils import profiling
 
-STATUS_NAMES = {0: "ok", 1: "barrier timeout", 2: "signal timeout", 3: "pipeline timeout", 4: "row overflow",
-                5: "bad argument"}
+from ..utils.status import STATUS_NAMES  # noqa: E402,F401  (re-exported)
 
 
 @dataclass
@@ -80,36 +79,71 @@ class MoEConfig:
     wait_ms: int = 1500
 
 
-def heap_layout(cfg: MoEConfig, world: int) -> HeapLayout:
-    """Symmetric regions of one layer (identical on every rank)."""
+# Regions that only live inside one layer's forward or backward pass: a model keeps ONE copy of them for
+# all its layers (``heap_layout(..., layers=n)``).  Reuse across layers is safe without extra barriers: a
+# peer writes layer L+1's rows into this rank's scratch only after its solver has seen this rank's
+# publish for L+1 (forward), or after this rank's gradient rows for that layer reached it (backward), and
+# both follow, in this rank's stream, the kernels that read the previous layer's contents.
+SHARED_SYMM = ("ybuf", "dybuf", "dxbuf", "dprob", "xq", "sfx")
+SHARED_LOCAL = ("dact", "actq", "sfact")
+
+
+def region_name(name: str, layer: Optional[int]) -> str:
+    """Heap region of ``name`` for layer ``layer`` of a model heap (None: a single-layer heap, plain names)."""
+    if layer is None:
+        return name
+    return f"S.{name}" if name in SHARED_SYMM else f"L{layer}.{name}"
+
+
+def heap_layout(cfg: MoEConfig, world: int, layers: Optional[int] = None) -> HeapLayout:
+    """Symmetric regions (identical on every rank) of one layer, or -- with ``layers`` -- of a whole model:
+    per-layer state under ``L<i>.`` and one set of per-step scratch buffers under ``S.``; one allocation and
+    one handle exchange per model."""
     E, H, F = cfg.num_experts, cfg.hidden, cfg.ffn
     home_cap = -(-E // world)
     w_slots = home_cap + (cfg.extra_slots if world > 1 else 0)
     U = cfg.max_tokens * cfg.top_k
     cap = row_capacity(cfg, world)
     lay = HeapLayout()
-    lay.add("omega", (world, E), torch.int32)
-    lay.add("signals", (16,), torch.int32)
-    # arrival counters per GEMM M-tile of the receive buffers (forward, backward) + replica pull counters
-    lay.add("arrive", (2 * (cap // (128 * cfg.gemm_ctas)) + 2 * max(w_slots - home_cap, 0) + 4,), torch.int32)
-    lay.add("xbuf", (cap, H), torch.bfloat16)
-    lay.add("meta", (cap, 2), torch.int32)
-    lay.add("rowp", (cap,), torch.float32)     # gate weight of every received row (stored by its sender)
-    lay.add("dprob", (U,), torch.float32)      # gate-weight gradients of this rank's units (stored by their hosts)
-    lay.add("ybuf", (U, H), torch.bfloat16)
-    lay.add("dybuf", (cap, H), torch.bfloat16)
-    lay.add("dxbuf", (U, H), torch.bfloat16)
-    lay.add("w1", (w_slots, 2 * F, H), torch.bfloat16)
-    lay.add("w2", (w_slots, H, F), torch.bfloat16)
-    lay.add("gw1", (w_slots, 2 * F, H), torch.bfloat16)
-    lay.add("gw2", (w_slots, H, F), torch.bfloat16)
+    per_layer = [
+        ("omega", (world, E), torch.int32),
+        ("signals", (16,), torch.int32),
+        # arrival counters per GEMM M-tile of the receive buffers (forward, backward) + replica pull counters
+        ("arrive", (2 * (cap // (128 * cfg.gemm_ctas)) + 2 * max(w_slots - home_cap, 0) + 4,), torch.int32),
+        ("xbuf", (cap, H), torch.bfloat16),
+        ("meta", (cap, 2), torch.int32),
+        ("rowp", (cap,), torch.float32),      # gate weight of every received row (stored by its sender)
+        ("w1", (w_slots, 2 * F, H), torch.bfloat16),
+        ("w2", (w_slots, H, F), torch.bfloat16),
+        ("gw1", (w_slots, 2 * F, H), torch.bfloat16),
+        ("gw2", (w_slots, H, F), torch.bfloat16),
+    ]
+    scratch = [
+        ("dprob", (U,), torch.float32),       # gate-weight gradients of this rank's units (stored by their hosts)
+        ("ybuf", (U, H), torch.bfloat16),
+        ("dybuf", (cap, H), torch.bfloat16),
+        ("dxbuf", (U, H), torch.bfloat16),
+    ]
     if cfg.fp8_inference:
-        lay.add("w1q", (w_slots, 2 * F, H), torch.uint8)
-        lay.add("w2q", (w_slots, H, F), torch.uint8)
-        lay.add("sfb1", (w_slots, _sf_bytes(2 * F, H)), torch.uint8)
-        lay.add("sfb2", (w_slots, _sf_bytes(H, F)), torch.uint8)
-        lay.add("xq", (cap, H), torch.uint8)                      # received rows, quantised by the sender
-        lay.add("sfx", (cap // 128 * _sf_bytes(128, H),), torch.uint8)
+        per_layer += [
+            ("w1q", (w_slots, 2 * F, H), torch.uint8),
+            ("w2q", (w_slots, H, F), torch.uint8),
+            ("sfb1", (w_slots, _sf_bytes(2 * F, H)), torch.uint8),
+            ("sfb2", (w_slots, _sf_bytes(H, F)), torch.uint8),
+        ]
+        scratch += [
+            ("xq", (cap, H), torch.uint8),                      # received rows, quantised by the sender
+            ("sfx", (cap // 128 * _sf_bytes(128, H),), torch.uint8),
+        ]
+    if layers is None:
+        for name, shape, dtype in per_layer + scratch:
+            lay.add(name, shape, dtype)
+        return lay
+    for i in range(int(layers)):
+        for name, shape, dtype in per_layer:
+            lay.add(region_name(name, i), shape, dtype)
+    for name, shape, dtype in scratch:
+        lay.add(region_name(name, 0), shape, dtype)
     return lay
 
 
@@ -197,9 +231,17 @@ class FusedMoE(nn.Module):
     """
 
     def __init__(self, cfg: MoEConfig, heap: SymmetricHeap, rank: int, world: int, *,
-                 solver_cfg: Optional[EPLBConfig] = None, multi_rank_sync: bool = True, seed: int = 0) -> None:
+                 solver_cfg: Optional[EPLBConfig] = None, multi_rank_sync: bool = True, seed: int = 0,
+                 layer_index: Optional[int] = None, scratch: Optional[Dict[str, torch.Tensor]] = None,
+                 status: Optional[torch.Tensor] = None) -> None:
+        """``layer_index``: this layer's position in a model heap built with ``heap_layout(cfg, world, layers=n)``
+        (None: ``heap`` holds this layer alone).  ``scratch``: a dict shared by the layers of a model in which the
+        per-step local buffers are created once.  ``status``: an int32 ``[4]`` view to use as this layer's status
+        word (a row of a :class:`~ep_balance_b200.utils.status.StatusBoard`)."""
         super().__init__()
         self.cfg, self.heap, self.rank, self.world = cfg, heap, int(rank), int(world)
+        self.layer_index = layer_index
+        sym = lambda name: region_name(name, layer_index)  # noqa: E731
         self.solver_cfg = solver_cfg or EPLBConfig()
         dev = heap.device
         self.device = dev
@@ -218,7 +260,7 @@ class FusedMoE(nn.Module):
         # ---- parameters: router + the owned expert slots (views of symmetric memory)
         g = torch.Generator(device="cpu").manual_seed(1234 + seed)
         self.router = nn.Parameter((torch.randn(E, H, generator=g) * 0.02).to(dev, cfg.router_dtype))
-        w1_all, w2_all = heap.tensor("w1", rank), heap.tensor("w2", rank)
+        w1_all, w2_all = heap.tensor(sym("w1"), rank), heap.tensor(sym("w2"), rank)
         ge = torch.Generator(device=dev)
         for i in range(self.home_cap):
             e = rank * self.home_cap + i
@@ -227,8 +269,8 @@ class FusedMoE(nn.Module):
             w2_all[i].copy_((torch.randn(H, F, generator=ge, device=dev) * 0.02).to(torch.bfloat16))
         self.w1 = nn.Parameter(w1_all[: self.home_cap])
         self.w2 = nn.Parameter(w2_all[: self.home_cap])
-        self._gw1 = heap.tensor("gw1", rank)[: self.home_cap]
-        self._gw2 = heap.tensor("gw2", rank)[: self.home_cap]
+        self._gw1 = heap.tensor(sym("gw1"), rank)[: self.home_cap]
+        self._gw2 = heap.tensor(sym("gw2"), rank)[: self.home_cap]
         self.router_bias: Optional[torch.Tensor] = None  # additive logit skew (synthetic workloads)
         self.route_fn = None  # optional ``logits [N, E] -> (top_idx int64 [N, K], prob fp32 [N, K])``
         # Inference (no autograd) selects experts with one fused kernel.  ``None``: the default top-k + softmax
@@ -248,7 +290,7 @@ class FusedMoE(nn.Module):
             "slot_used": torch.zeros(R, **i32), "stuck": torch.zeros(R, dtype=torch.uint8, device=dev),
             "theta": torch.zeros(1, dtype=torch.int64, device=dev),
             "control": torch.zeros(3, dtype=torch.int64, device=dev), "sync": torch.zeros(2, **i32),
-            "status": torch.zeros(4, **i32), "epochs": torch.zeros(8, **i32),
+            "status": status if status is not None else torch.zeros(4, **i32), "epochs": torch.zeros(8, **i32),
             "slot_of": torch.full((E, R), -1, **i32), "row_base": torch.full((E, R), -1, **i32),
             "group_expert": torch.full((self.w_slots,), -1, **i32), "group_wslot": torch.zeros(self.w_slots, **i32),
             "group_off": torch.zeros(self.w_slots + 1, **i32), "group_rows": torch.zeros(self.w_slots, **i32),
@@ -261,7 +303,18 @@ class FusedMoE(nn.Module):
             "hbuf": torch.zeros((self.row_capacity, 2 * F), dtype=torch.bfloat16, device=dev),
             "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
         }
-        self.loc["dact"] = torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev)
+        if status is not None and (status.shape != (4,) or status.dtype != torch.int32 or status.device != torch.device(dev)
+                                   or not status.is_contiguous()):
+            raise ValueError("status must be a contiguous int32 [4] tensor on the layer's device")
+
+        def local_scratch(name, shape, dtype):
+            pool = scratch if scratch is not None else {}
+            t = pool.get(name)
+            if t is None or t.shape != tuple(shape) or t.dtype != dtype:
+                t = pool[name] = torch.zeros(shape, dtype=dtype, device=dev)
+            return t
+
+        self.loc["dact"] = local_scratch("dact", (self.row_capacity, F), torch.bfloat16)
         ptrs = {k: v.data_ptr() for k, v in self.loc.items()}
         self._acc_gw1 = self._acc_gw2 = None
         if cfg.grad_accum_dtype is not None:
@@ -282,14 +335,14 @@ class FusedMoE(nn.Module):
             symm_names += ["w1q", "w2q", "sfb1", "sfb2", "xq", "sfx"]
             table_names += [(n, n + "_ptrs") for n in ("w1q", "w2q", "sfb1", "sfb2", "xq", "sfx")]
             cap = self.row_capacity
-            u8 = dict(dtype=torch.uint8, device=dev)
-            self._fp8_local = {"actq": torch.zeros((cap, F), **u8), "sfact": torch.zeros(cap // 128 * _sf_bytes(128, F), **u8)}
+            self._fp8_local = {"actq": local_scratch("actq", (cap, F), torch.uint8),
+                               "sfact": local_scratch("sfact", (cap // 128 * _sf_bytes(128, F),), torch.uint8)}
             ptrs.update({k: v.data_ptr() for k, v in self._fp8_local.items()})
         for name in symm_names:
-            ptrs[name] = heap.address(name, rank)
+            ptrs[name] = heap.address(sym(name), rank)
         self._tables: List[torch.Tensor] = []
         for name, key in table_names:
-            t = heap.peer_ptrs(name)
+            t = heap.peer_ptrs(sym(name))
             self._tables.append(t)
             ptrs[key] = t.data_ptr()
         sc = self.solver_cfg
@@ -304,6 +357,7 @@ class FusedMoE(nn.Module):
                       gemm_ctas=cfg.gemm_ctas, accum_fp32=int(cfg.grad_accum_dtype == torch.float32),
                       fused_comm=int(os.environ.get("EPLB_FUSED_COMM", int(cfg.fused_comm))),
                       wait_ms=int(os.environ.get("EPLB_WAIT_MS", cfg.wait_ms)))
+        self.rt_config = rt_cfg
         self.rt = load().MoeRuntime(rt_cfg, ptrs)
         self.bind_grads()
 
@@ -365,6 +419,11 @@ class FusedMoE(nn.Module):
             prob = torch.softmax(top_val.float(), dim=-1) if self.cfg.normalize_topk else torch.sigmoid(top_val.float())
         return top_idx.contiguous(), prob.contiguous()
 
+    def apply_routed(self, tokens: torch.Tensor, top_idx: torch.Tensor, prob: torch.Tensor) -> torch.Tensor:
+        """Expert computation for an externally made routing decision (``top_idx`` int64 ``[N, K]``, ``prob``
+        fp32 ``[N, K]``): what a framework binding calls after running its own router."""
+        return _FusedMoEFunction.apply(tokens.contiguous(), top_idx.contiguous(), prob.float().contiguous(), self)
+
     def forward(self, tokens: torch.Tensor) -> torch.Tensor:
         if tokens.dtype != torch.bfloat16 or tokens.dim() != 2 or tokens.shape[1] != self.cfg.hidden:
             raise ValueError("tokens must be bf16 [num_tokens, hidden]")
@@ -379,11 +438,17 @@ class FusedMoE(nn.Module):
             return out
         return _FusedMoEFunction.apply(tokens, top_idx, prob, self)
 
+    def omega(self) -> torch.Tensor:
+        """This rank's gathered load matrix ``[R, E]`` (int32 view of symmetric memory)."""
+        return self.heap.tensor(region_name("omega", self.layer_index), self.rank)
+
     # ---- introspection (these read device memory: debugging / tests only) ---
     def check_status(self) -> None:
-        st = self.loc["status"].tolist()
-        if st[0] != 0:
-            raise RuntimeError(f"MoE runtime status: {STATUS_NAMES.get(st[0], st[0])} (site {st[1]}, detail {st[2]})")
+        """Synchronous read of this layer's status word; raises :class:`MoEStatusError` when it is set."""
+        from ..utils.status import raise_if_set
+
+        rows = [[0, 0, 0, 0]] * (self.layer_index or 0) + [self.loc["status"].tolist()]
+        raise_if_set(rows)
 
     def last_plan(self):
         from ..core.plan import Plan

@@ -146,6 +146,41 @@ def test_bound_layer_matches_per_token_truth(shared):
     assert layer._eplb["mb"] == 1
 
 
+class _FakeFusedLayer:
+    """Stands in for FusedMoE on CPU: same attributes the binding touches, expert math by the plain oracle."""
+
+    def __init__(self):
+        self.cfg = SimpleNamespace(num_experts=E)
+        self.w1 = torch.zeros(E, 2 * F, H)
+        self.w2 = torch.zeros(E, H, F)
+        self.calls = []
+
+    def apply_routed(self, tokens, top_idx, prob):
+        from ep_balance_b200.models.reference_moe import moe_reference
+
+        self.calls.append((tuple(top_idx.shape), tuple(prob.shape), top_idx.dtype))
+        return moe_reference(tokens, top_idx, prob, self.w1, self.w2)
+
+
+@pytest.mark.parametrize("shared", [False, True])
+def test_fused_binding_rehomes_weights_and_matches_truth(shared):
+    from ep_balance_b200.integration.megatron_moe import bind_fused_moe_layer
+
+    torch.manual_seed(2)
+    layer = MoELayer(shared=shared)
+    x = torch.randn(2, 3, H)
+    want = _truth(layer, x) + (layer.shared_experts_compute(x) if shared else 0)
+    fused = _FakeFusedLayer()
+    bind_fused_moe_layer(layer, fused)
+    # the local experts were copied into the fused layer's owned slots, in order
+    for i, ex in enumerate(layer.experts.local_experts):
+        assert torch.equal(fused.w1[i], ex.linear_fc1.weight) and torch.equal(fused.w2[i], ex.linear_fc2.weight)
+    got, bias = layer(x)
+    assert bias is None and got.shape == x.shape and torch.allclose(got, want, atol=1e-5, rtol=1e-4)
+    # one call with the router's decision as fixed-width [tokens, top-k] tensors (no data-dependent shapes)
+    assert fused.calls == [((6, K), (6, K), torch.int64)]
+
+
 def test_bind_rejects_unsupported_configurations(monkeypatch):
     layer = MoELayer(shared=True)
     layer.shared_expert_overlap = True
