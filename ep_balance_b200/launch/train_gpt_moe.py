@@ -14,6 +14,7 @@ scripts/pretrain_eplb_moe.py:100-176):
 ``EPLB_N_SLOT``          TOTAL expert slots per rank (default: owned experts + 2)
 ``GPUS_PER_NODE``        ranks per logical topology domain
 ``ROUTER_SKEW``          scale of the drifting router-logit bias
+``ROUTER_BALANCING``     none (default) | aux_loss: auxiliary load-balancing loss on every router (``ROUTER_AUX_COEFF``)
 ``EPLB_TRACE_OUT/MAX/EVERY``  routing trace (format v3) written by rank 0
 ``EPLB_LOG=1``           print the ``[EPLB]`` line in apply mode too (one host read per layer)
 
@@ -107,9 +108,16 @@ def main(argv=None):
     gpn = int(os.environ.get("GPUS_PER_NODE", str(world)) or world)
     domains = world // gpn if gpn > 0 and world % gpn == 0 else 1
     M = max(1, a.num_micro_batches)
+    # ROUTER_BALANCING=none (default) leaves the routing skew intact for the balancer; aux_loss adds the usual
+    # auxiliary loss (coefficient ROUTER_AUX_COEFF, default 1e-2), which flattens the skew at its source
+    balancing = os.environ.get("ROUTER_BALANCING", "none").strip().lower() or "none"
+    if balancing not in ("none", "aux_loss"):
+        raise SystemExit("ROUTER_BALANCING must be none or aux_loss")
+    aux_coeff = float(os.environ.get("ROUTER_AUX_COEFF", "1e-2")) if balancing == "aux_loss" else 0.0
     cfg = GPTMoEConfig(vocab=a.vocab, layers=a.layers, hidden=a.hidden, heads=a.heads, ffn=a.ffn, experts=a.experts,
                        top_k=a.top_k, seq_len=a.seq_len, micro_batch=a.micro_batch, extra_slots=extra,
-                       num_domains=max(domains, 1), grad_accum_dtype=torch.float32 if M > 1 else None)
+                       num_domains=max(domains, 1), grad_accum_dtype=torch.float32 if M > 1 else None,
+                       aux_loss_coeff=aux_coeff)
     torch.manual_seed(a.seed)
     model = GPTMoE(cfg, dev, rank=rank, world=world)
     model.sync_dense_parameters()

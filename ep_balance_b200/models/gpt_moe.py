@@ -39,6 +39,7 @@ class GPTMoEConfig:
     num_domains: int = 1
     rope_base: float = 10000.0
     grad_accum_dtype: Optional[torch.dtype] = None  # set for steps made of several micro-batches
+    aux_loss_coeff: float = 0.0  # > 0: router load-balancing auxiliary loss (ROUTER_BALANCING=aux_loss)
 
     @property
     def tokens_per_rank(self) -> int:
@@ -102,7 +103,7 @@ class GPTMoE(nn.Module):
         mcfg = MoEConfig(hidden=cfg.hidden, ffn=cfg.ffn, num_experts=cfg.experts, top_k=cfg.top_k,
                          max_tokens=cfg.tokens_per_rank, extra_slots=cfg.extra_slots,
                          capacity_factor=cfg.capacity_factor, num_domains=cfg.num_domains,
-                         grad_accum_dtype=cfg.grad_accum_dtype)
+                         grad_accum_dtype=cfg.grad_accum_dtype, aux_loss_coeff=cfg.aux_loss_coeff)
         # one symmetric allocation (and one handle exchange) for the whole model: per-layer state plus a single
         # set of per-step scratch buffers shared by all layers; one status board for every layer's status word
         self.heap = SymmetricHeap(heap_layout(mcfg, world, layers=cfg.layers), device, group=group)
@@ -171,7 +172,11 @@ class GPTMoE(nn.Module):
         logits = self.head(self.norm(x))
         if targets is None:
             return logits
-        return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
+        loss = F.cross_entropy(logits.float().view(-1, logits.shape[-1]), targets.reshape(-1))
+        for b in self.blocks:  # router balancing pressure, when switched on
+            if b.moe.aux_loss is not None:
+                loss = loss + b.moe.aux_loss
+        return loss
 
     def check_status(self) -> None:
         """Synchronous read of every layer's status word; raises :class:`MoEStatusError` if one is set."""

@@ -70,6 +70,10 @@ class MoEConfig:
     # activation scales, 128 x 128 weight scales, power-of-two scale factors).  Call
     # ``FusedMoE.quantize_weights()`` after the weights change; replicas then pull the fp8 copies.
     fp8_inference: bool = False
+    # > 0: switch-style auxiliary load-balancing loss  coeff * E * sum_e f_e * P_e  (f_e: share of routed units,
+    # P_e: mean router probability) is left in ``FusedMoE.aux_loss`` by every forward that runs with autograd.
+    # 0 (default): no balancing pressure on the router, the routing skew reaches the dispatcher intact.
+    aux_loss_coeff: float = 0.0
     # True: the token transport of a pass (dispatch + replica weight pull in forward, gradient dispatch in
     # backward) runs on spare warps of the GEMM kernel that consumes the rows, so transfer and tensor-core
     # tiles overlap.  False: a stand-alone transport kernel runs first.  ``EPLB_FUSED_COMM=0`` overrides.
@@ -272,6 +276,7 @@ class FusedMoE(nn.Module):
         self._gw1 = heap.tensor(sym("gw1"), rank)[: self.home_cap]
         self._gw2 = heap.tensor(sym("gw2"), rank)[: self.home_cap]
         self.router_bias: Optional[torch.Tensor] = None  # additive logit skew (synthetic workloads)
+        self.aux_loss: Optional[torch.Tensor] = None     # auxiliary balancing loss of the last forward (aux_loss_coeff > 0)
         self.route_fn = None  # optional ``logits [N, E] -> (top_idx int64 [N, K], prob fp32 [N, K])``
         # Inference (no autograd) selects experts with one fused kernel.  ``None``: the default top-k + softmax
         # (or sigmoid) router; a model with its own ``route_fn`` sets ``dict(mode=2, n_groups=, topk_groups=, scale=)``
@@ -417,6 +422,13 @@ class FusedMoE(nn.Module):
                 return top_idx.contiguous(), prob.float().contiguous()
             top_val, top_idx = torch.topk(logits, self.cfg.top_k, dim=-1)
             prob = torch.softmax(top_val.float(), dim=-1) if self.cfg.normalize_topk else torch.sigmoid(top_val.float())
+            self.aux_loss = None
+            if self.cfg.aux_loss_coeff > 0 and torch.is_grad_enabled():
+                E = self.cfg.num_experts
+                share = torch.zeros(E, dtype=torch.float32, device=logits.device).scatter_add_(
+                    0, top_idx.reshape(-1), torch.ones(top_idx.numel(), dtype=torch.float32, device=logits.device))
+                share = share / max(top_idx.numel(), 1)
+                self.aux_loss = self.cfg.aux_loss_coeff * E * (share * torch.softmax(logits.float(), dim=-1).mean(0)).sum()
         return top_idx.contiguous(), prob.contiguous()
 
     def apply_routed(self, tokens: torch.Tensor, top_idx: torch.Tensor, prob: torch.Tensor) -> torch.Tensor:
