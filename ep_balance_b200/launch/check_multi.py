@@ -73,10 +73,23 @@ def main() -> int:
         out = torch.empty_like(tokens)
         dtok = torch.empty_like(tokens)
         dprob = torch.empty_like(prob)
+        layer.rt.trace_launches(step == a.steps - 1)
         layer.rt.forward(tokens.data_ptr(), idx.data_ptr(), prob.data_ptr(), out.data_ptr(), a.tokens)
         layer.rt.backward(dout.data_ptr(), dtok.data_ptr(), dprob.data_ptr(), a.tokens)
         torch.cuda.synchronize()
         layer.check_status()
+        if step == a.steps - 1 and world > 1:
+            # launch order of the multi-rank step: the gradient return (barrier + owner-side reduce, on the side
+            # stream) is issued after the last weight-gradient GEMM and before Dgrad1, so that it runs beside it
+            log = layer.rt.launch_log()
+            side = [i for i, n in enumerate(log) if n.startswith("side:")]
+            gemms = [i for i, n in enumerate(log) if n.startswith("grouped_gemm")]
+            order_ok = (log[:3] == ["count_publish", "solver", "route_assign"] and len(side) == 3
+                        and log[side[0]] == "side:symm_barrier" and side == list(range(side[0], side[0] + 3))
+                        and gemms[-2] < side[0] < gemms[-1] and log[-1] == "unit_reduce(bwd)")
+            if not order_ok:
+                ok = False
+                print(f"[rank {rank}] unexpected launch order: {log}", flush=True)
         dist.barrier()
 
         w1s = [torch.empty_like(layer.w1.data) for _ in range(world)]

@@ -121,8 +121,9 @@ def main(argv=None):
     torch.manual_seed(a.seed)
     model = GPTMoE(cfg, dev, rank=rank, world=world)
     model.sync_dense_parameters()
-    dense_opt = torch.optim.AdamW(model.dense_parameters(), lr=a.lr, fused=True)
-    expert_opt = FusedAdamW(list(model.expert_parameters()), lr=a.lr)
+    # both optimizers skip their update on the device while any layer's status word is set
+    dense_opt = FusedAdamW(model.dense_parameters(), lr=a.lr, guard=model.status.words)
+    expert_opt = FusedAdamW(list(model.expert_parameters()), lr=a.lr, guard=model.status.words)
     skew = DriftingRouterSkew(a.layers, a.experts, rho=0.9, scale=float(os.environ.get("ROUTER_SKEW", "1.0")),
                               seed=a.seed, device=dev)
     gen = torch.Generator(device="cpu").manual_seed(1000 + rank)

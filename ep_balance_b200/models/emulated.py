@@ -14,6 +14,7 @@ import torch
 
 from ..core.config import EPLBConfig
 from ..parallel.symm import SymmetricHeap
+from ..utils.status import StatusBoard
 from .moe_layer import FusedMoE, MoEConfig, heap_layout
 
 
@@ -23,8 +24,10 @@ class EmulatedCluster:
         self.cfg, self.world = cfg, world
         self.heap = SymmetricHeap(heap_layout(cfg, world), torch.device(device), backend="local",
                                   num_local_ranks=world)
+        self.status = StatusBoard(world, torch.device(device))  # row r: status word of logical rank r
         self.layers: List[FusedMoE] = [
-            FusedMoE(cfg, self.heap, r, world, solver_cfg=solver_cfg, multi_rank_sync=False, seed=seed)
+            FusedMoE(cfg, self.heap, r, world, solver_cfg=solver_cfg, multi_rank_sync=False, seed=seed,
+                     status=self.status.row(r))
             for r in range(world)
         ]
         for l in self.layers[1:]:  # one router for the whole group

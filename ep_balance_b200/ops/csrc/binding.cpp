@@ -178,7 +178,7 @@ void grouped_gemm(int64_t mode, torch::Tensor a, torch::Tensor b, torch::Tensor 
 // In-place AdamW step on one tensor (param, grad and both moments share dtype and shape).
 void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, torch::Tensor exp_avg_sq, double lr,
                 double beta1, double beta2, double eps, double weight_decay, int64_t step,
-                c10::optional<torch::Tensor> step_tensor) {
+                c10::optional<torch::Tensor> step_tensor, c10::optional<torch::Tensor> status_guard) {
   const c10::cuda::CUDAGuard guard(param.device());
   TORCH_CHECK(param.is_contiguous() && grad.is_contiguous() && exp_avg.is_contiguous() && exp_avg_sq.is_contiguous(),
               "adamw_step needs contiguous tensors");
@@ -207,6 +207,14 @@ void adamw_step(torch::Tensor param, torch::Tensor grad, torch::Tensor exp_avg, 
   a.step_ptr = nullptr;
   if (step_tensor.has_value() && step_tensor->defined())
     a.step_ptr = dptr<int64_t>(*step_tensor, "step_tensor", torch::kInt64);
+  a.guard = nullptr;
+  a.guard_rows = 0;
+  if (status_guard.has_value() && status_guard->defined()) {
+    TORCH_CHECK(status_guard->dim() == 2 && status_guard->size(1) == 4 && status_guard->device() == param.device(),
+                "guard must be an int32 [n, 4] tensor of status words on the parameter's device");
+    a.guard = dptr<int>(*status_guard, "guard", torch::kInt32);
+    a.guard_rows = (int)status_guard->size(0);
+  }
   cuda_check(epb::launch_adamw(a, current_stream()), "launch_adamw");
 }
 
@@ -409,7 +417,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("wait_probe", &wait_probe);
   m.def("adamw_step", &adamw_step, py::arg("param"), py::arg("grad"), py::arg("exp_avg"), py::arg("exp_avg_sq"),
         py::arg("lr"), py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("weight_decay"), py::arg("step"),
-        py::arg("step_tensor") = py::none());
+        py::arg("step_tensor") = py::none(), py::arg("guard") = py::none());
   m.def("get_batched", &get_batched);
   m.def("put_batched", &put_batched);
   m.def("signal_peers", &signal_peers);

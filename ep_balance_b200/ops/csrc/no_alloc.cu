@@ -49,6 +49,18 @@ unsigned char* scratch_for_current_device() {
 
 extern "C" int epb_noalloc_last_cuda_error(void) { return g_last_cuda_error; }
 
+extern "C" int epb_noalloc_status(int32_t* out4, cudaStream_t stream) {
+  if (out4 == nullptr) return EPB_NOALLOC_BAD_ARGUMENT;
+  unsigned char* base = scratch_for_current_device();
+  if (base == nullptr) return EPB_NOALLOC_CUDA_ERROR;
+  cudaError_t e = cudaMemcpyAsync(out4, base + kOffZeroed + 16, 4 * sizeof(int32_t), cudaMemcpyDeviceToDevice, stream);
+  if (e != cudaSuccess) {
+    g_last_cuda_error = (int)e;
+    return EPB_NOALLOC_CUDA_ERROR;
+  }
+  return EPB_NOALLOC_OK;
+}
+
 extern "C" int epb_solve_plan_noalloc(const int32_t* omega, const int32_t* dom, const int32_t* cost,
                                       const int32_t* main_rank, const int64_t* weight_bytes, int64_t s_tok, int R,
                                       int E, int D, int n_slot, int u_min, int iters, int allow_cross, int8_t* x,

@@ -17,7 +17,15 @@
 //     there.  The words that must start at zero are cleared on the caller's stream before every
 //     launch.  Two calls whose GPU work overlaps (different streams, no ordering) race on the
 //     array; order them.
-//   * The call enqueues work on `stream` and returns; it does not synchronise.
+//   * The call enqueues work on `stream` and returns; it does not synchronise.  EPB_NOALLOC_OK therefore
+//     only means "enqueued".  Whether the kernel ran to the end is in its status word, which lives in the
+//     scratch array: copy it out with epb_noalloc_status() on the same stream and read it once the stream
+//     has been synchronised.  A non-zero code (a bounded wait ran out, a rank's domain id was outside
+//     0..D-1) means x, q and theta are not a valid plan.
+//   * The repair loop runs `iters` rounds per domain; the optional stagnation probe of the tensor entry
+//     point (EPLBConfig.stage2_patience_all_scales) is not available here.
+//   * Host side: the functions keep a per-device address table and a last-error word without locking.
+//     Call them from one thread at a time (per process).
 //   * No cudaMalloc, cudaFree or allocating library routine is called.
 #pragma once
 
@@ -51,7 +59,12 @@ int epb_solve_plan_noalloc(const int32_t* omega, const int32_t* dom, const int32
                            const int64_t* weight_bytes, int64_t s_tok, int R, int E, int D, int n_slot, int u_min,
                            int iters, int allow_cross, int8_t* x, int32_t* q, int64_t* theta, cudaStream_t stream);
 
-// CUDA error code (cudaError_t as int) of the last failing CUDA call made by the function above.
+// Copy the status word {code, site, detail, 0} of the last solve enqueued on this device into `out4`
+// (device memory of the caller, 4 x int32), ordered after that solve on `stream`.  Codes as in the
+// library's status words: 0 ok, 1 barrier timeout, 5 bad argument.  Allocates nothing.
+int epb_noalloc_status(int32_t* out4, cudaStream_t stream);
+
+// CUDA error code (cudaError_t as int) of the last failing CUDA call made by the functions above.
 int epb_noalloc_last_cuda_error(void);
 
 #ifdef __cplusplus

@@ -25,7 +25,16 @@ __device__ __forceinline__ void resolve_step(AdamArgs& a) {
   }
 }
 
+// True while any status word of the guard is set (every thread reads the same few words; they are cached).
+__device__ __forceinline__ bool guard_tripped(const AdamArgs& a) {
+  if (a.guard == nullptr) return false;
+  for (int i = 0; i < a.guard_rows; ++i)
+    if (a.guard[4 * i] != 0) return true;
+  return false;
+}
+
 __global__ void __launch_bounds__(256) adamw_bf16_kernel(AdamArgs a) {
+  if (guard_tripped(a)) return;
   resolve_step(a);
   const size_t n_vec = a.numel / 8;
   uint4* p4 = reinterpret_cast<uint4*>(a.param);
@@ -85,6 +94,7 @@ __global__ void __launch_bounds__(256) adamw_bf16_kernel(AdamArgs a) {
 }
 
 __global__ void __launch_bounds__(256) adamw_f32_kernel(AdamArgs a) {
+  if (guard_tripped(a)) return;
   resolve_step(a);
   float* p = reinterpret_cast<float*>(a.param);
   const float* g = reinterpret_cast<const float*>(a.grad);
@@ -106,7 +116,10 @@ cudaError_t launch_adamw(const AdamArgs& a, cudaStream_t stream) {
   if (a.numel == 0) return cudaSuccess;
   const size_t work = a.is_bf16 ? (a.numel + 7) / 8 : a.numel;
   size_t blocks = (work + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+    sms = 132;
+  if (blocks > (size_t)sms * 16) blocks = (size_t)sms * 16;
   if (a.is_bf16) adamw_bf16_kernel<<<(unsigned)blocks, 256, 0, stream>>>(a);
   else adamw_f32_kernel<<<(unsigned)blocks, 256, 0, stream>>>(a);
   return cudaGetLastError();

@@ -16,6 +16,8 @@ struct AdamArgs {
   float bias_correction1, bias_correction2_sqrt;  // 1 - beta1^t, sqrt(1 - beta2^t)
   int is_bf16;
   int grad_f32;      // bf16 parameters with an fp32 (accumulated) gradient
+  const int* guard;         // optional device status words [guard_rows, 4]: while any row's first int is non-zero the
+  int guard_rows;           // kernel returns without touching parameter or moments (a damaged step is not applied)
   const int64_t* step_ptr;  // optional device step counter: when set, the bias corrections are computed from it in the
                             // kernel (the host-side values are ignored), which makes the launch CUDA-graph replayable
 };

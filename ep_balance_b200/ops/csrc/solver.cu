@@ -648,6 +648,21 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
     if (!sig_ok) return;  // every CTA fails the same bounded wait; nobody is left at a barrier
   }
 
+  // Every rank must belong to one of the D domains; a plan solved with an out-of-range id would leave that
+  // rank's load unset.  Every CTA evaluates the same input, so all of them return together.
+  {
+    __shared__ int bad_rank;
+    if (threadIdx.x == 0) bad_rank = -1;
+    __syncthreads();
+    for (int r = threadIdx.x; r < p.R; r += blockDim.x)
+      if (p.dom[r] < 0 || p.dom[r] >= p.D) bad_rank = r;
+    __syncthreads();
+    if (bad_rank >= 0) {
+      if (threadIdx.x == 0) set_status(p.status, kStatusBadArgument, 13, bad_rank);
+      return;
+    }
+  }
+
   bool ok = true;
   for (int d = blockIdx.x; d < p.D; d += gridDim.x) phase0_domain(p, s, d);
   ok = ok && grid_barrier(p, 11);

@@ -6,11 +6,16 @@ per layer, so the whole expert update is two launches.  Moments are kept in the 
 lives on the host and enters the kernel as two bias-correction scalars.  With ``capturable=True`` the step
 count lives on the device instead and the kernel derives the bias corrections itself, so ``step()`` can be
 captured in a CUDA graph and replayed.
+
+``guard`` (an int32 ``[n, 4]`` tensor of device status words, e.g. ``StatusBoard.words``) contains a damaged
+step: while any word is set the kernel leaves parameter and moments untouched, so a step in which rows
+were dropped or a peer's data did not arrive never reaches the weights; the host raises a step or two
+later (``ep_balance_b200.utils.status.StatusMonitor``).
 """
 
 from __future__ import annotations
 
-from typing import Iterable
+from typing import Iterable, Optional
 
 import torch
 
@@ -19,10 +24,11 @@ from ..ops.extension import load
 
 class FusedAdamW(torch.optim.Optimizer):
     def __init__(self, params: Iterable[torch.nn.Parameter], lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8,
-                 weight_decay: float = 1e-2, capturable: bool = False) -> None:
+                 weight_decay: float = 1e-2, capturable: bool = False, guard: Optional[torch.Tensor] = None) -> None:
         super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
         self._ext = load()
         self.capturable = bool(capturable)
+        self.guard = guard
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -44,8 +50,8 @@ class FusedAdamW(torch.optim.Optimizer):
                 st["step"] += 1
                 if self.capturable:
                     self._ext.adamw_step(p.data, grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
-                                         group["eps"], group["weight_decay"], 1, st["step"])
+                                         group["eps"], group["weight_decay"], 1, st["step"], self.guard)
                 else:
                     self._ext.adamw_step(p.data, grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], group["lr"], b1, b2,
-                                         group["eps"], group["weight_decay"], st["step"])
+                                         group["eps"], group["weight_decay"], st["step"], None, self.guard)
         return loss

@@ -206,3 +206,102 @@ def test_no_kernel_writes_past_a_symmetric_region():
     off = cl.heap.layout.guards["ybuf"]
     flat[off + 3] = 0                                        # host-side: simulate an overrun of `ybuf`
     assert cl.heap.damaged_guards(2) == ["ybuf"]
+
+
+def _one_layer(**kw):
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+
+    cfg = MoEConfig(hidden=256, ffn=256, num_experts=8, top_k=2, max_tokens=256, **kw)
+    return EmulatedCluster(cfg, world=1).layers[0]
+
+
+def test_warm_forward_backward_has_no_host_sync():
+    """The hot path never reads device data on the host (reference: tests/test_gin_weights.py:423-436,
+    tests/test_gpu_solver.py:149-171): a warmed step passes under the synchronisation detector."""
+    layer = _one_layer()
+    x = torch.randn(256, 256, device="cuda").bfloat16()
+    dout = torch.randn_like(x)
+    for _ in range(2):  # warm-up: lazy initialisation may synchronise
+        y = layer(x.clone().requires_grad_(True))
+        y.backward(dout)
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        tok = x.clone().requires_grad_(True)
+        y = layer(tok)
+        y.backward(dout)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    layer.check_status()
+    assert torch.isfinite(tok.grad.float()).all()
+
+
+@pytest.mark.parametrize("fused_comm", [True, False])
+def test_launch_order_of_a_step(fused_comm):
+    """The step is a fixed launch sequence (reference: the backward collective issue order pinned in
+    tests/test_sync_free.py:61-82, 152-157): transport inside (or right before) the GEMM that consumes it,
+    Dgrad2 before the weight-gradient GEMMs, Dgrad1 last so that the gradient return can run beside it."""
+    layer = _one_layer(fused_comm=fused_comm)
+    x = torch.randn(256, 256, device="cuda").bfloat16().requires_grad_(True)
+    layer.rt.trace_launches(True)
+    layer(x).backward(torch.randn(256, 256, device="cuda").bfloat16())
+    torch.cuda.synchronize()
+    log = layer.rt.launch_log()
+    layer.rt.trace_launches(False)
+    gemm1 = ["grouped_gemm+transport"] if fused_comm else ["dispatch", "grouped_gemm"]
+    dgrad2 = ["grouped_gemm+transport"] if fused_comm else ["dispatch_grads", "grouped_gemm"]
+    want = (["count_publish", "solver", "route_assign"] + gemm1 + ["grouped_gemm", "unit_reduce"]            # forward
+            + dgrad2 + ["swiglu_backward", "grouped_gemm", "grouped_gemm", "grouped_gemm", "unit_reduce(bwd)"])  # backward
+    assert log == want, log
+
+
+def test_capacity_overflow_is_detected_and_contained():
+    """Rows beyond the receive buffers are dropped by the kernels (never written out of bounds).  Such a step must
+    not reach the weights and must surface on the host: the optimizer kernel skips its update while a status
+    word is set, and the late monitor raises within two steps; afterwards the context is still usable."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+    from ep_balance_b200.utils.optim import FusedAdamW
+    from ep_balance_b200.utils.status import MoEStatusError, StatusMonitor
+
+    torch.manual_seed(3)
+    world, E, K, N, H = 4, 8, 2, 512, 256
+    # no replica slots and buffers for exactly the mean load: one hot expert overflows its owner
+    cfg = MoEConfig(hidden=H, ffn=256, num_experts=E, top_k=K, max_tokens=N, extra_slots=0, capacity_factor=1.0)
+    cl = EmulatedCluster(cfg, world=world)
+    bias = torch.zeros(E, device="cuda")
+    bias[0] = 8.0
+    for l in cl.layers:
+        l.router_bias = bias
+    params = [p for l in cl.layers for p in (l.w1, l.w2)]
+    opt = FusedAdamW(params, lr=1e-2, guard=cl.status.words)
+    before = [p.detach().clone() for p in params]
+    tokens = [torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)]
+    douts = [torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)]
+    monitor = StatusMonitor(cl.status.words)
+    raised_at = None
+    for step in range(3):
+        cl.step(tokens, douts)
+        opt.step()
+        try:
+            monitor.poll()
+        except MoEStatusError as err:
+            raised_at, seen = step, err
+            break
+    assert raised_at is not None and raised_at <= 2, "the overflow never reached the host"
+    assert seen.code == 4 and "row overflow" in str(seen)
+    torch.cuda.synchronize()
+    for p, b in zip(params, before):
+        assert torch.equal(p.detach(), b), "a damaged step changed the weights"
+    assert cl.heap.damaged_guards() == []            # nothing was written past a buffer
+    # the context survives: with the status cleared and a balanced router the same cluster trains again
+    cl.status.clear()
+    for l in cl.layers:
+        l.router_bias = None
+    cl.step(tokens, douts)
+    opt.step()
+    torch.cuda.synchronize()
+    cl.status.check_now()
+    assert any(not torch.equal(p.detach(), b) for p, b in zip(params, before))

@@ -91,3 +91,22 @@ def test_capturable_adamw_replays_from_a_graph_like_eager_steps():
     assert err < 2e-3, err
     assert float((graph_layer.w1.float() - eager_layer.w1.float()).abs().max()) > 0      # it did train
     assert all(l == l and l > 0 for l in losses)
+
+
+def test_guarded_adamw_skips_the_update_while_a_status_word_is_set():
+    from ep_balance_b200.utils.optim import FusedAdamW
+
+    guard = torch.zeros((3, 4), dtype=torch.int32, device="cuda")
+    p = torch.nn.Parameter(torch.randn(4099, device="cuda").bfloat16())
+    p.grad = torch.randn_like(p)
+    opt = FusedAdamW([p], lr=1e-2, guard=guard)
+    before = p.detach().clone()
+    guard[2, 0] = 4                       # some layer reported a row overflow
+    opt.step()
+    torch.cuda.synchronize()
+    assert torch.equal(p.detach(), before)
+    assert float(opt.state[p]["exp_avg"].float().abs().sum()) == 0.0   # moments untouched too
+    guard.zero_()
+    opt.step()
+    torch.cuda.synchronize()
+    assert not torch.equal(p.detach(), before)
