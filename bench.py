@@ -44,6 +44,9 @@ def parse():
     p.add_argument("--no-graph", action="store_true",
                    help="end-to-end loop: launch every step eagerly instead of replaying it from a CUDA graph")
     p.add_argument("--phases", action="store_true", help="also print a per-phase device-time table (stderr)")
+    p.add_argument("--check", action="store_true",
+                   help="before timing, run one forward+backward through the native path and compare outputs, token, "
+                        "gate and the owners' weight gradients with the plain PyTorch fp32 oracle (stderr; aborts on mismatch)")
     return p.parse_args()
 
 
@@ -273,6 +276,28 @@ def run_ours(args):
         while pending:
             read_loss(pending.pop(0))
 
+    if args.check:
+        from ep_balance_b200.launch.check_multi import oracle_errors
+
+        x = dev_batches[0]
+        g = torch.Generator(device="cpu").manual_seed(4242 + rank)
+        dout = torch.randn(x.shape, generator=g).to(dev, torch.bfloat16)
+        with torch.no_grad():
+            idx, prob = layer.route_tokens(x)
+        out, dtok, dprob = torch.empty_like(x), torch.empty_like(x), torch.empty_like(prob)
+        layer.rt.forward(x.data_ptr(), idx.data_ptr(), prob.data_ptr(), out.data_ptr(), x.shape[0])
+        layer.rt.backward(dout.data_ptr(), dtok.data_ptr(), dprob.data_ptr(), x.shape[0])
+        torch.cuda.synchronize()
+        layer.check_status()
+        errs = oracle_errors(layer, x, idx, prob, dout, out, dtok, dprob, rank, world)
+        digests = [layer.last_plan().digest()]
+        if world > 1:
+            digests = [None] * world
+            dist.all_gather_object(digests, layer.last_plan().digest())
+        line = f"[check rank {rank}/{world}] plan_identical={len(set(digests)) == 1} " + " ".join(f"{k}={v:.2e}" for k, v in errs.items())
+        print(line, file=sys.stderr, flush=True)
+        if max(errs.values()) > 3e-2 or len(set(digests)) != 1:
+            raise SystemExit("bench --check: the native step disagrees with the fp32 oracle: " + line)
     for ev in consumed:
         ev.record()
     sampler = ClockSampler(local)

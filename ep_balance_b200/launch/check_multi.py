@@ -26,6 +26,37 @@ def rel(a, b):
     return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12))
 
 
+def oracle_errors(layer, tokens, idx, prob, dout, out, dtok, dprob, rank: int, world: int) -> dict:
+    """Relative L2 errors of one native forward+backward against the plain PyTorch fp32 oracle: this rank's
+    outputs, token gradients and gate gradients, and the owners' weight gradients (the oracle's are summed
+    over all ranks, replicas included).  Collective: every rank calls it."""
+    from ..models.reference_moe import moe_reference
+
+    if world > 1:
+        w1s = [torch.empty_like(layer.w1.data) for _ in range(world)]
+        w2s = [torch.empty_like(layer.w2.data) for _ in range(world)]
+        dist.all_gather(w1s, layer.w1.data.contiguous())
+        dist.all_gather(w2s, layer.w2.data.contiguous())
+    else:
+        w1s, w2s = [layer.w1.data], [layer.w2.data]
+    w1 = torch.cat(w1s).float().requires_grad_(True)
+    w2 = torch.cat(w2s).float().requires_grad_(True)
+    x = tokens.float().requires_grad_(True)
+    p = prob.clone().requires_grad_(True)
+    o = moe_reference(x, idx, p, w1, w2)
+    o.backward(dout.float())
+    gw1, gw2 = w1.grad.clone(), w2.grad.clone()
+    if world > 1:
+        dist.all_reduce(gw1)
+        dist.all_reduce(gw2)
+    hc = layer.home_cap
+    return {
+        "out": rel(out, o.detach()), "dtokens": rel(dtok, x.grad), "dprob": rel(dprob, p.grad),
+        "dw1": rel(layer.w1.grad, gw1[rank * hc:(rank + 1) * hc]),
+        "dw2": rel(layer.w2.grad, gw2[rank * hc:(rank + 1) * hc]),
+    }
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=3)
@@ -45,7 +76,6 @@ def main() -> int:
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
 
     from ..models.moe_layer import FusedMoE, MoEConfig, heap_layout
-    from ..models.reference_moe import moe_reference
     from ..parallel.symm import SymmetricHeap
 
     domains = 2 if world % 2 == 0 and world >= 4 else 1
@@ -92,25 +122,7 @@ def main() -> int:
                 print(f"[rank {rank}] unexpected launch order: {log}", flush=True)
         dist.barrier()
 
-        w1s = [torch.empty_like(layer.w1.data) for _ in range(world)]
-        w2s = [torch.empty_like(layer.w2.data) for _ in range(world)]
-        dist.all_gather(w1s, layer.w1.data.contiguous())
-        dist.all_gather(w2s, layer.w2.data.contiguous())
-        w1 = torch.cat(w1s).float().requires_grad_(True)
-        w2 = torch.cat(w2s).float().requires_grad_(True)
-        x = tokens.float().requires_grad_(True)
-        p = prob.clone().requires_grad_(True)
-        o = moe_reference(x, idx, p, w1, w2)
-        o.backward(dout.float())
-        gw1, gw2 = w1.grad.clone(), w2.grad.clone()
-        dist.all_reduce(gw1)
-        dist.all_reduce(gw2)
-        hc = layer.home_cap
-        errs = {
-            "out": rel(out, o.detach()), "dtokens": rel(dtok, x.grad), "dprob": rel(dprob, p.grad),
-            "dw1": rel(layer.w1.grad, gw1[rank * hc:(rank + 1) * hc]),
-            "dw2": rel(layer.w2.grad, gw2[rank * hc:(rank + 1) * hc]),
-        }
+        errs = oracle_errors(layer, tokens, idx, prob, dout, out, dtok, dprob, rank, world)
         digests = [None] * world
         dist.all_gather_object(digests, layer.last_plan().digest())
         same_plan = len(set(digests)) == 1

@@ -106,6 +106,7 @@ void solve_plan(torch::Tensor omega, torch::Tensor dom, torch::Tensor cost, torc
   p.stuck = dptr<unsigned char>(stuck, "stuck", torch::kUInt8);
   p.theta = dptr<int64_t>(theta, "theta", torch::kInt64);
   p.control = dptr<int64_t>(control, "control", torch::kInt64);
+  p.trace = control.numel() >= 16 ? p.control + 8 : nullptr;  // a control tensor of 16 words also receives phase timestamps
   p.sync = reinterpret_cast<unsigned*>(dptr<int32_t>(sync, "sync", torch::kInt32));
   p.status = dptr<int>(status, "status", torch::kInt32);
   epb::RankTables t{};

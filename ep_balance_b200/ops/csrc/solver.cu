@@ -7,8 +7,11 @@
 //   phase 1  per (src, e): even split over active hosts in ascending rank id
 //   phase 2  per domain: bounded greedy repair (busiest rank -> best (expert, target))
 //   phase 3  routing tables for the calling rank (slot layout, destination row bases)
-// The reference spends a sort + ~10 torch kernels + 3 launches and R*E blocks on this; here
-// phases are separated by a bounded grid barrier inside one launch, one CTA per domain.
+// The reference spends a sort + ~10 torch kernels + 3 launches and R*E blocks on this; here phases are
+// separated by a bounded grid barrier inside one launch, one CTA per domain.  On the common path (<= 64
+// ranks, the domain's quota columns fit in shared memory) a CTA routes exactly its own domain's columns
+// straight into the shared-memory state the repair loop works on, so phases 1 and 2 need no barrier and no
+// cache fill between them; walks that cannot change anything (no free slot left, nothing movable) stop early.
 #include "solver.h"
 
 #include <cooperative_groups.h>
@@ -86,12 +89,19 @@ struct Smem {
   int* q_c;         // [R * E * n] cached q[s, e, domain rank] (or unused)
 };
 
+__host__ __device__ inline int pow2_at_least(int n) {
+  int p = 1;
+  while (p < n) p <<= 1;
+  return p;
+}
+
 __device__ Smem carve(unsigned char* base, int R, int E) {
   Smem s;
+  const int P = pow2_at_least(E) < 32 ? 32 : pow2_at_least(E);  // the candidate sort works on a power-of-two array
   s.prio = reinterpret_cast<long long*>(base);
-  base += sizeof(long long) * E;
+  base += sizeof(long long) * P;
   s.order = reinterpret_cast<int*>(base);
-  base += sizeof(int) * E;
+  base += sizeof(int) * P;
   s.dom_ranks = reinterpret_cast<int*>(base);
   base += sizeof(int) * R;
   s.local_idx = reinterpret_cast<int*>(base);
@@ -110,19 +120,23 @@ __device__ Smem carve(unsigned char* base, int R, int E) {
   return s;
 }
 
+// Ranks of domain d in ascending id (s.dom_ranks) and every rank's index in that list or -1 (s.local_idx).
+// One warp compacts 32 ranks per step with a ballot; the loads of a step are one coalesced request.
 __device__ int collect_domain(const SolverParams& p, Smem& s, int d) {
   __shared__ int n_sh;
   __syncthreads();
-  for (int r = threadIdx.x; r < p.R; r += blockDim.x) s.local_idx[r] = -1;
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < kWarp) {
+    const int lane = threadIdx.x;
     int n = 0;
-    for (int r = 0; r < p.R; ++r)
-      if (p.dom[r] == d) {
-        s.local_idx[r] = n;
-        s.dom_ranks[n++] = r;
-      }
-    n_sh = n;
+    for (int base = 0; base < p.R; base += kWarp) {
+      const int r = base + lane;
+      const bool in = r < p.R && p.dom[r] == d;
+      const unsigned m = __ballot_sync(kFull, in);
+      if (r < p.R) s.local_idx[r] = in ? n + __popc(m & ((1u << lane) - 1u)) : -1;
+      if (in) s.dom_ranks[n + __popc(m & ((1u << lane) - 1u))] = r;
+      n += __popc(m);
+    }
+    if (lane == 0) n_sh = n;
   }
   __syncthreads();
   return n_sh;
@@ -153,30 +167,87 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
   // gate and benefit
   for (int e = tid; e < E; e += nt) {
     long long T = 0;
-    for (int i = 0; i < n; ++i) T += p.omega[(size_t)s.dom_ranks[i] * E + e];
+    const int owner = __ldg(p.main_rank + e);
+    const long long wb = __ldg(p.weight_bytes + e);
+    for (int i = 0; i < n; ++i) T += __ldg(p.omega + (size_t)s.dom_ranks[i] * E + e);
     long long rhs = 2 * T * p.s_tok;
-    bool valid = p.allow_cross && p.dom[p.main_rank[e]] != d && T > 0 && p.weight_bytes[e] < rhs;
-    s.prio[e] = valid ? rhs - p.weight_bytes[e] : -1;
+    bool valid = p.allow_cross && __ldg(p.dom + owner) != d && T > 0 && wb < rhs;
+    s.prio[e] = valid ? rhs - wb : -1;
     if (valid) atomicAdd(&n_valid, 1);
   }
   __syncthreads();
   const int nv = n_valid;
   if (nv > 0) {
-    // stable descending order by counting how many entries precede each valid one
-    for (int e = tid; e < E; e += nt) {
-      long long pe = s.prio[e];
-      if (pe < 0) continue;
-      int pos = 0;
-      for (int o = 0; o < E; ++o) {
-        long long po = s.prio[o];
-        pos += (po > pe) || (po == pe && o < e);
+    // Descending benefit, ties by ascending expert id (what a stable descending sort of the row gives).  The
+    // (benefit, id) pairs are distinct, so any comparison sort yields this one order: a bitonic sort,
+    // O(E log^2 E / threads) instead of counting all pairs.  Invalid entries (-1) and the padding (-2) sink
+    // to the end.
+    const int P = max(pow2_at_least(E), kWarp);
+    if (P <= nt) {
+      // one element per thread, kept in registers: exchanges at distance < 32 are warp shuffles, only the
+      // longer ones go through shared memory (10 of the 45 steps at 512 experts)
+      long long mp = tid < E ? s.prio[tid] : -2;
+      int me = tid;
+      __syncthreads();
+      for (int k = 2; k <= P; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+          long long op;
+          int oe;
+          if (j >= kWarp) {
+            if (tid < P) {
+              s.prio[tid] = mp;
+              s.order[tid] = me;
+            }
+            __syncthreads();
+            op = tid < P ? s.prio[tid ^ j] : -2;
+            oe = tid < P ? s.order[tid ^ j] : tid;
+            __syncthreads();
+          } else {
+            op = __shfl_xor_sync(kFull, mp, j);
+            oe = __shfl_xor_sync(kFull, me, j);
+          }
+          const bool mine_first = mp > op || (mp == op && me < oe);  // does my element precede the partner's?
+          const bool keep_first = ((tid & j) == 0) == ((tid & k) == 0);
+          if (mine_first != keep_first) {
+            mp = op;
+            me = oe;
+          }
+        }
       }
-      s.order[pos] = e;
+      if (tid < P) s.order[tid] = me;
+      __syncthreads();
+    } else {
+      for (int i = tid; i < P; i += nt) {
+        s.order[i] = i;
+        if (i >= E) s.prio[i] = -2;
+      }
+      __syncthreads();
+      for (int k = 2; k <= P; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+          for (int t = tid; t < P / 2; t += nt) {
+            const int lo = ((t & ~(j - 1)) << 1) | (t & (j - 1)), hi = lo | j;
+            const long long pl = s.prio[lo], ph = s.prio[hi];
+            const int el = s.order[lo], eh = s.order[hi];
+            const bool lo_first = pl > ph || (pl == ph && el < eh);   // does `lo` precede `hi` in the wanted order?
+            const bool ascending_block = (lo & k) == 0;               // blocks alternate direction
+            if (lo_first != ascending_block) {
+              s.prio[lo] = ph;
+              s.prio[hi] = pl;
+              s.order[lo] = eh;
+              s.order[hi] = el;
+            }
+          }
+          __syncthreads();
+        }
+      }
     }
-    __syncthreads();
     if (tid < kWarp) {
       const int lane = tid;
-      for (int c = 0; c < nv; ++c) {
+      // free slots left in the domain: once they are used up no later candidate can be admitted, so the walk stops
+      int free_left = 0;
+      for (int i = lane; i < n; i += kWarp) free_left += max(p.n_slot - s.slot[i], 0);
+      for (int off = kWarp / 2; off > 0; off >>= 1) free_left += __shfl_xor_sync(kFull, free_left, off);
+      for (int c = 0; c < nv && free_left > 0; ++c) {
         const int e = s.order[c];
         bool present = false;
         long long key = LLONG_MAX;  // (slots used, domain-local index) of the best free rank
@@ -187,12 +258,15 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
           if (used < p.n_slot) key = min(key, ((long long)used << 32) | (unsigned)i);
         }
         const unsigned any = __ballot_sync(kFull, present);
-        for (int off = kWarp / 2; off > 0; off >>= 1) key = min(key, __shfl_down_sync(kFull, key, off));
-        if (lane == 0 && any == 0 && key != LLONG_MAX) {
-          int i = (int)(key & 0xffffffffll);
-          if (xc) xc[e * n + i] = 1;
-          else p.x[(size_t)e * R + s.dom_ranks[i]] = 1;
-          s.slot[i] += 1;
+        for (int off = kWarp / 2; off > 0; off >>= 1) key = min(key, __shfl_xor_sync(kFull, key, off));
+        if (any == 0 && key != LLONG_MAX) {  // the same decision on every lane
+          if (lane == 0) {
+            int i = (int)(key & 0xffffffffll);
+            if (xc) xc[e * n + i] = 1;
+            else p.x[(size_t)e * R + s.dom_ranks[i]] = 1;
+            s.slot[i] += 1;
+          }
+          --free_left;
         }
         __syncwarp(kFull);
       }
@@ -264,6 +338,70 @@ __device__ void phase1_routing_masks(const SolverParams& p, Smem& s) {
   }
 }
 
+// One CTA computes exactly the quota columns of ITS domain's ranks (all sources, all experts), straight
+// into the shared-memory caches that the repair loop works on, and stores them to global memory on the
+// way.  The repair loop then needs neither a grid barrier after routing nor a cache fill.
+// Requires R <= 64 and the quota cache (s.q_c, s.erl_c) of this domain to fit.
+__device__ void phase1_domain(const SolverParams& p, Smem& s, int d) {
+  __shared__ unsigned long long dom_mask[64];
+  const int R = p.R, E = p.E, u_min = p.u_min;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int n = collect_domain(p, s, d);
+  if (n == 0) return;
+  unsigned long long* host = reinterpret_cast<unsigned long long*>(s.prio);  // [E]
+  for (int e = tid; e < E; e += nt) {
+    unsigned long long m = 0;
+    for (int dst = 0; dst < R; ++dst) m |= (unsigned long long)(p.x[(size_t)e * R + dst] != 0) << dst;
+    host[e] = m;
+  }
+  for (int r = tid; r < R; r += nt) {
+    unsigned long long m = 0;
+    const int dr = p.dom[r];
+    for (int o = 0; o < R; ++o) m |= (unsigned long long)(p.dom[o] == dr) << o;
+    dom_mask[r] = m;
+  }
+  __syncthreads();
+  // the loads of the next pair are issued before the stores of the current one (the compiler cannot reorder them
+  // itself: q and omega might alias for all it knows)
+  int need_next = tid < R * E ? __ldg(p.omega + tid) : 0;
+  for (int pair = tid; pair < R * E; pair += nt) {
+    const int src = pair / E, e = pair - src * E;
+    const int need = need_next;
+    if (pair + nt < R * E) need_next = __ldg(p.omega + pair + nt);
+    const unsigned long long loc = host[e] & dom_mask[src];
+    const unsigned long long act = loc ? loc : host[e];
+    // the even split of even_share(), with its divisions done once per pair instead of once per destination
+    const int count = __popcll(act);
+    int takers = count;
+    if (u_min > 1 && need >= u_min) takers = min(count, need / u_min);
+    else if (need < u_min) takers = 1;
+    const bool any = need > 0 && count > 0;
+    const int base = any ? need / takers : 0, extra = any ? need - base * takers : 0;
+    int* qrow = p.q + (size_t)pair * R;
+    int* crow = s.q_c + (size_t)pair * n;
+    for (int i = 0; i < n; ++i) {
+      const int dst = s.dom_ranks[i];
+      int v = 0;
+      if (any && ((act >> dst) & 1ull)) {
+        const int pos = __popcll(act & ((1ull << dst) - 1ull));
+        if (pos < takers) v = base + (pos < extra ? 1 : 0);
+      }
+      qrow[dst] = v;
+      crow[i] = v;
+    }
+  }
+  __syncthreads();
+  for (int cell = tid; cell < E * n; cell += nt) {
+    const int e = cell / n, i = cell - e * n;
+    int acc = 0;
+    for (int src = 0; src < R; ++src) acc += s.q_c[((size_t)src * E + e) * n + i];
+    s.erl_c[cell] = acc;
+    p.erl[(size_t)e * R + s.dom_ranks[i]] = acc;
+    s.x_c[cell] = (signed char)((host[e] >> s.dom_ranks[i]) & 1ull);
+  }
+  __syncthreads();
+}
+
 __device__ void phase1_routing(const SolverParams& p) {
   const int R = p.R, E = p.E, u_min = p.u_min;
   const int lane = threadIdx.x & 31;
@@ -318,7 +456,9 @@ struct ProbeState {
   int patience;
 };
 
-__device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, ProbeState probe, bool fresh) {
+// prefilled: phase1_domain of this CTA has just left this domain's q / erl / x columns in the caches.
+__device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, ProbeState probe, bool fresh,
+                              bool prefilled = false) {
   __shared__ int busy_idx, busy_rank, busy_load, finished, sel_idx, apply_move;
   __shared__ int best_theta, stagnant;
   __shared__ Cand best_sh;
@@ -333,7 +473,7 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
     for (int i = warp_; i < n; i += nwarps_) {
       const int r = s.dom_ranks[i];
       int acc = 0;
-      for (int e = lane_; e < E; e += kWarp) acc += p.erl[(size_t)e * R + r];
+      for (int e = lane_; e < E; e += kWarp) acc += prefilled ? s.erl_c[e * n + i] : p.erl[(size_t)e * R + r];
       for (int off = kWarp / 2; off > 0; off >>= 1) acc += __shfl_down_sync(kFull, acc, off);
       if (lane_ == 0) {
         s.load[i] = acc;
@@ -354,13 +494,13 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
   // beyond the quota move itself.  Global copies are kept up to date for the later phases.
   const bool cached = p.cache_stage2 != 0;
   const bool qcached = p.cache_q != 0 && u_min == 1;  // the quota columns of this domain's ranks too
-  if (qcached) {
+  if (qcached && !prefilled) {
     for (int idx = tid; idx < R * E * n; idx += nt) {
       const int se = idx / n, i = idx - se * n;
       s.q_c[idx] = p.q[(size_t)se * R + s.dom_ranks[i]];
     }
   }
-  if (cached) {
+  if (cached && !prefilled) {
     for (int idx = tid; idx < E * n; idx += nt) {
       const int e = idx / n, i = idx - e * n;
       const int r = s.dom_ranks[i];
@@ -369,6 +509,41 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
     }
   }
   __syncthreads();
+
+  // A move needs a target that already hosts the expert or has a free slot.  When no rank of the domain has a
+  // free slot and no expert has two hosts inside the domain, no iteration can ever move anything: the loop
+  // would only mark the loaded ranks stuck one by one.  Write that outcome down directly.
+  if (cached && !probe.on) {
+    __shared__ int movable;
+    if (tid == 0) {
+      movable = 0;
+      for (int i = 0; i < n; ++i)
+        if (s.slot[i] < p.n_slot) movable = 1;
+    }
+    __syncthreads();
+    if (!movable) {
+      for (int e = tid; e < E; e += nt) {
+        int hosts = 0;
+        for (int i = 0; i < n; ++i) hosts += s.x_c[e * n + i] != 0;
+        if (hosts > 1) movable = 1;  // benign race: every writer stores 1
+      }
+    }
+    __syncthreads();
+    if (tid == 0 && !movable) {
+      int loaded = 0;
+      for (int i = 0; i < n; ++i) loaded += s.load[i] > 0;
+      if (loaded > iters) movable = 1;  // the loop would stop early: let it run
+    }
+    __syncthreads();
+    if (!movable) {
+      if (tid == 0) {
+        // the loop marks the ranks busiest first and stops at the first rank with no load, which stays unmarked
+        for (int i = 0; i < n; ++i) s.stuck[i] = s.load[i] > 0 ? 1 : 0;
+      }
+      __syncthreads();
+      iters = 0;
+    }
+  }
 
   for (int it = 0; it < iters; ++it) {
     if (tid == 0) {
@@ -556,6 +731,13 @@ __device__ int global_theta(const SolverParams& p) {
   for (int r = 0; r < p.R; ++r) th = max(th, p.rank_load[r]);
   return th;
 }
+// The same maximum, by the first warp of the CTA (all 32 lanes call it); valid on every lane.
+__device__ int global_theta_warp(const SolverParams& p) {
+  int th = -1;
+  for (int r = threadIdx.x & 31; r < p.R; r += kWarp) th = max(th, p.rank_load[r]);
+  for (int off = kWarp / 2; off > 0; off >>= 1) th = max(th, __shfl_xor_sync(kFull, th, off));
+  return th;
+}
 
 // ------------------------------------------------------------------ phase 3
 __device__ void build_tables(const SolverParams& p, const RankTables& t, int me) {
@@ -633,9 +815,14 @@ __device__ void build_tables(const SolverParams& p, const RankTables& t, int me)
 }
 
 // ------------------------------------------------------------------ kernels
+__device__ __forceinline__ void trace_mark(const SolverParams& p, int slot) {
+  if (p.trace != nullptr && blockIdx.x == 0 && threadIdx.x == 0) p.trace[slot] = (int64_t)globaltimer_ns();
+}
+
 __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables tables) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   Smem s = carve(smem_raw, p.R, p.E);
+  trace_mark(p, 0);
 
   // Wait (bounded) until every rank's row of omega has landed in the gather buffer.
   if (p.omega_signal != nullptr) {
@@ -664,16 +851,29 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
   }
 
   bool ok = true;
+  trace_mark(p, 1);
   for (int d = blockIdx.x; d < p.D; d += gridDim.x) phase0_domain(p, s, d);
+  trace_mark(p, 2);
   ok = ok && grid_barrier(p, 11);
-  if (ok) {
+  trace_mark(p, 3);
+  // Fast path (every domain has its own CTA, <= 64 ranks, quota cache fits, plain quota floor): each CTA routes
+  // exactly its own domain's columns into its caches and goes on repairing them, with no grid barrier between.
+  const bool own_columns = p.cache_q && p.u_min == 1 && p.R <= 64 && (int)gridDim.x >= p.D && !p.probe;
+  if (ok && !own_columns) {
     if (p.R <= 64) phase1_routing_masks(p, s);
     else phase1_routing(p);
   }
-  ok = ok && grid_barrier(p, 12);
+  if (!own_columns) ok = ok && grid_barrier(p, 12);
 
   if (ok) {
-    if (!p.probe) {
+    if (own_columns) {
+      if ((int)blockIdx.x < p.D) {
+        phase1_domain(p, s, blockIdx.x);
+        trace_mark(p, 4);
+        stage2_domain(p, s, blockIdx.x, p.iters, ProbeState{false, 0}, true, true);
+        trace_mark(p, 5);
+      }
+    } else if (!p.probe) {
       for (int d = blockIdx.x; d < p.D; d += gridDim.x) stage2_domain(p, s, d, p.iters, ProbeState{false, 0}, true);
     } else {
       // Stagnation probe: 1 repair round, then `patience` rounds, then the remainder unless the
@@ -708,23 +908,33 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
       }
     }
   }
-  ok = ok && grid_barrier(p, 16);
-
-  if (ok && blockIdx.x == 0) {
-    if (threadIdx.x == 0) p.theta[0] = global_theta(p);
-    if (tables.me >= 0) build_tables(p, tables, tables.me);
-  }
-
-  // Last CTA out rewinds the barrier counters so the workspace can be reused by any grid size.
+  // No barrier before the tail: every CTA publishes its results and counts itself out; the LAST one to leave sees
+  // all domains' results, so it computes theta, builds the routing tables and rewinds the barrier counters.
+  __shared__ int last_out;
   __syncthreads();
-  if (threadIdx.x == 0 && gridDim.x > 1) {
-    unsigned left_before = atomicAdd(p.sync + 1, 1u);
-    if (left_before == gridDim.x - 1) {
-      p.sync[0] = 0;
-      p.sync[1] = 0;
+  if (threadIdx.x == 0) {
+    last_out = 1;
+    if (gridDim.x > 1) {
+      __threadfence();
+      last_out = atomicAdd(p.sync + 1, 1u) == gridDim.x - 1 ? 1 : 0;
       __threadfence();
     }
   }
+  __syncthreads();
+  if (!last_out) return;
+  if (ok && (gridDim.x == 1 || *reinterpret_cast<volatile int*>(p.status) == 0)) {
+    if (threadIdx.x < kWarp) {
+      const int th = global_theta_warp(p);
+      if (threadIdx.x == 0) p.theta[0] = th;
+    }
+    if (tables.me >= 0) build_tables(p, tables, tables.me);
+  }
+  if (threadIdx.x == 0 && gridDim.x > 1) {
+    p.sync[0] = 0;
+    p.sync[1] = 0;
+    __threadfence();
+  }
+  if (p.trace != nullptr && threadIdx.x == 0) p.trace[6] = (int64_t)globaltimer_ns();
 }
 
 __global__ void __launch_bounds__(1024) tables_kernel(SolverParams p, RankTables tables) {
@@ -732,7 +942,8 @@ __global__ void __launch_bounds__(1024) tables_kernel(SolverParams p, RankTables
 }
 
 size_t solver_base_smem(int R, int E) {
-  return sizeof(long long) * E + sizeof(int) * E + sizeof(int) * 5 * R + sizeof(Cand) * 32 + 64;
+  const size_t P = (size_t)(pow2_at_least(E) < 32 ? 32 : pow2_at_least(E));
+  return sizeof(long long) * P + sizeof(int) * P + sizeof(int) * 5 * R + sizeof(Cand) * 32 + 64;
 }
 size_t solver_cache_smem(int R, int E) { return (((size_t)E * R * 5 + 15) / 16) * 16; }  // erl (int) + x (byte) per (e, rank)
 size_t solver_qcache_smem(int R, int E) { return (size_t)R * E * R * 4; }

@@ -26,6 +26,7 @@ struct SolverParams {
   unsigned char* stuck;   // [R]
   int64_t* theta;         // [1]
   int64_t* control;       // [3] probe-mode control words (may be null)
+  int64_t* trace;         // optional [8]: CTA 0 stores the global timer (ns) at its phase boundaries (profiling aid)
   // workspace
   unsigned* sync;         // [2] grid-barrier arrival / departure counters, zero when idle
   int* status;            // [4] error status (see common.cuh), zero when healthy
