@@ -345,9 +345,12 @@ def run_ours(args):
                 torch.cuda.synchronize()
                 dist.barrier()  # start the step together: otherwise `solve` also counts the host skew between ranks
                 torch.cuda.synchronize()
+                layer.fused_trace_reset()
                 step_device(i)
                 for name, ms in layer.rt.phase_times():
                     acc.setdefault(name, []).append(ms)
+                for name, us in layer.fused_trace().items():   # EPLB_TRACE_FUSED=1: inside the fused kernels
+                    acc.setdefault("  " + name, []).append(us * 1e-3)
             layer.rt.enable_timing(False)
             table = torch.tensor([[sum(v) / len(v)] for v in acc.values()], device=dev)
             worst = table.clone()
@@ -382,21 +385,24 @@ def phase_table(layer, x):
     idx, prob = layer.route_tokens(x)
     out = torch.empty_like(x)
     dprob = torch.empty_like(prob)
+    def psr():  # every transport draws its blocks from a ticket that publish clears: re-run it before each one
+        rt.publish(idx.data_ptr(), n * K)
+        rt.solve()
+        rt.route(idx.data_ptr(), n * K)
+
     phases = [
         ("publish", lambda: rt.publish(idx.data_ptr(), n * K)), ("solve", rt.solve),
         ("route", lambda: rt.route(idx.data_ptr(), n * K)),
-        ("dispatch", lambda: rt.dispatch_tokens(x.data_ptr(), prob.data_ptr(), n * K)), ("pull_weights", rt.pull_weights),
+        ("publish+solve+route (psr)", psr),
+        ("psr + dispatch", lambda: (psr(), rt.dispatch_tokens(x.data_ptr(), prob.data_ptr(), n * K))),
         ("gemm1", rt.gemm1), ("gemm2", rt.gemm2),
         ("reduce_out", lambda: rt.reduce_out(out.data_ptr(), n)),
-        ("dispatch_grads", lambda: rt.dispatch_grads(out.data_ptr(), n * K)),
+        ("psr + dispatch_grads", lambda: (psr(), rt.dispatch_grads(out.data_ptr(), n * K))),
         ("dgrad2 + swiglu pass", rt.dgrad2), ("wgrad2", rt.wgrad2), ("wgrad1", rt.wgrad1), ("dgrad1", rt.dgrad1),
         ("reduce_dtokens", lambda: rt.reduce_dtokens(out.data_ptr(), dprob.data_ptr(), n)),
-        # the one-kernel forms the step itself uses (each needs fresh arrival counters: publish clears them)
-        ("publish+solve+route", lambda: (rt.publish(idx.data_ptr(), n * K), rt.solve(), rt.route(idx.data_ptr(), n * K))),
-        ("psr+dispatch+gemm1 fused", lambda: (rt.publish(idx.data_ptr(), n * K), rt.solve(), rt.route(idx.data_ptr(), n * K),
-                                              rt.gemm1_fused(x.data_ptr(), prob.data_ptr(), n * K))),
-        ("psr+dispatch_grads+dgrad2 fused", lambda: (rt.publish(idx.data_ptr(), n * K), rt.solve(), rt.route(idx.data_ptr(), n * K),
-                                                     rt.dgrad2_fused(out.data_ptr(), n * K))),
+        # the one-kernel forms the step itself uses
+        ("psr + dispatch+gemm1 fused", lambda: (psr(), rt.gemm1_fused(x.data_ptr(), prob.data_ptr(), n * K))),
+        ("psr + dispatch_grads+dgrad2 fused", lambda: (psr(), rt.dgrad2_fused(out.data_ptr(), n * K))),
     ]
     if layer.world > 1:
         return  # phases that wait on peers cannot be timed one rank at a time

@@ -320,6 +320,9 @@ class FusedMoE(nn.Module):
             return t
 
         self.loc["dact"] = local_scratch("dact", (self.row_capacity, F), torch.bfloat16)
+        if os.environ.get("EPLB_TRACE_FUSED", "0") not in ("", "0"):
+            # profiling aid: the fused transport+GEMM kernels leave four timestamps each (see fused_trace())
+            self.loc["gemm_trace"] = torch.zeros(24, dtype=torch.int64, device=dev)
         ptrs = {k: v.data_ptr() for k, v in self.loc.items()}
         self._acc_gw1 = self._acc_gw2 = None
         if cfg.grad_accum_dtype is not None:
@@ -449,6 +452,33 @@ class FusedMoE(nn.Module):
             self._keep = (tokens, top_idx, prob)  # alive until the enqueued kernels have read them
             return out
         return _FusedMoEFunction.apply(tokens, top_idx, prob, self)
+
+    def fused_trace_reset(self) -> None:
+        if "gemm_trace" in self.loc:
+            one = [-1, 0, 0, -1, 0, 0, 0, 0, 0, 0, 0, 0]
+            self.loc["gemm_trace"].copy_(torch.tensor(one + one, dtype=torch.int64), non_blocking=True)
+
+    def fused_trace(self) -> Dict[str, float]:
+        """With ``EPLB_TRACE_FUSED=1``: microseconds, from the first transport warp's start, until the last transport
+        warp finished / the last MMA was issued / the first tile had its operands, for the forward (dispatch +
+        GEMM1) and the backward (gradient dispatch + Dgrad2) kernel of the last step.  Call ``fused_trace_reset()``
+        before the step; reads device memory."""
+        if "gemm_trace" not in self.loc:
+            return {}
+        t = self.loc["gemm_trace"].tolist()
+        out = {}
+        warps = 2 * self.rt_config["num_sms"]  # transport warps of a fused launch
+        for name, o in (("fwd", 0), ("bwd", 12)):
+            if t[o + 1] > 0:
+                out[f"{name}_transport_us"] = (t[o + 1] - t[o]) / 1e3
+                out[f"{name}_mma_end_us"] = (t[o + 2] - t[o]) / 1e3
+                out[f"{name}_first_tile_us"] = (t[o + 3] - t[o]) / 1e3
+                # per transport warp: time waiting for loads / for ring slots / in drains, and segments moved
+                out[f"{name}_warp_load_wait_us"] = t[o + 8] / warps / 1e3
+                out[f"{name}_warp_slot_wait_us"] = t[o + 9] / warps / 1e3
+                out[f"{name}_warp_drain_us"] = t[o + 10] / warps / 1e3
+                out[f"{name}_warp_segments"] = t[o + 11] / warps * 1e3
+        return out
 
     def omega(self) -> torch.Tensor:
         """This rank's gathered load matrix ``[R, E]`` (int32 view of symmetric memory)."""

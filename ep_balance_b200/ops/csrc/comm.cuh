@@ -21,17 +21,18 @@
 
 namespace epb {
 
-constexpr int kCommSlots = 4;          // ring slots per warp
 constexpr int kCommSlotBytes = 4096;   // one segment
-constexpr int kCommWarpBytes = kCommSlots * kCommSlotBytes;   // ring bytes per warp
-constexpr int kCommCtrlBytes = 192;    // per warp: kCommSlots mbarriers + kCommSlots slot records
+constexpr int kCommCtrlBytes = 192;    // per warp: up to 8 mbarriers + 8 slot records
+// Shared memory of one transport warp with a ring of kSlots segments (kSlots / 2 loads in flight).
+template <int kSlots>
+constexpr int comm_warp_bytes() { return kSlots * kCommSlotBytes + kCommCtrlBytes; }
 
 struct CommSlot {
   void* dst;       // where the segment goes
   int bytes;
   int pad;
 };
-static_assert(kCommSlots * 8 + kCommSlots * sizeof(CommSlot) <= kCommCtrlBytes, "per-warp control block too small");
+static_assert(8 * 8 + 8 * sizeof(CommSlot) <= kCommCtrlBytes, "per-warp control block too small");
 
 __device__ __forceinline__ void red_release_gpu_add(unsigned* p, unsigned v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -66,9 +67,17 @@ __device__ __forceinline__ void comm_bulk_store(void* gdst, const void* smem_src
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
-// The per-warp copy pipeline.  `smem` is the warp's private region: kCommWarpBytes of ring (16-byte
+// The per-warp copy pipeline.  `smem` is the warp's private region: kSlots segments of ring (16-byte
 // aligned) followed by kCommCtrlBytes of control data.  All 32 lanes call every member together.
+template <int kCommSlots>
 struct CommPipe {
+  static_assert(kCommSlots >= 4 && kCommSlots <= 8 && kCommSlots % 2 == 0, "ring of 4, 6 or 8 slots");
+  static constexpr int kCommWarpBytes = kCommSlots * kCommSlotBytes;
+  // Half of the ring holds loads in flight; the other half holds segments whose stores may still be reading
+  // them.  The copy engine of an SM serves requests in order, behind the GEMM's own tile loads, so a store
+  // starts reading its segment a while after it was issued: the issuing lane must not wait for the newest ones.
+  static constexpr int kLoads = kCommSlots / 2;
+  static constexpr int kStoresPending = kCommSlots - kLoads - 1;
   static constexpr int kSeg = kCommSlotBytes;  // bytes of one segment
   uint8_t* ring;
   uint64_t* bars;
@@ -77,8 +86,13 @@ struct CommPipe {
   int lane;
   bool failed;
   int* status;
+  // optional profiling (null: off): ns spent by lane 0 waiting for loads, for stores' reads, and draining
+  unsigned long long* prof;
+  unsigned long long t_load, t_read, t_drain, n_seg;
 
-  __device__ __forceinline__ void init(uint8_t* smem, int* status_word) {
+  __device__ __forceinline__ void init(uint8_t* smem, int* status_word, unsigned long long* prof_out = nullptr) {
+    prof = prof_out;
+    t_load = t_read = t_drain = n_seg = 0ull;
     ring = smem;
     bars = reinterpret_cast<uint64_t*>(smem + kCommWarpBytes);
     slots = reinterpret_cast<CommSlot*>(bars + kCommSlots);
@@ -98,6 +112,7 @@ struct CommPipe {
   __device__ __forceinline__ void pop() {
     const int s = (int)(popped % kCommSlots);
     const uint32_t parity = (popped / kCommSlots) & 1u;
+    const unsigned long long p0 = prof ? globaltimer_ns() : 0ull;
     if (!failed) {
       unsigned long long t0 = 0;
       for (unsigned spin = 0; !comm_bar_try(&bars[s], parity); ++spin) {
@@ -113,24 +128,37 @@ struct CommPipe {
       failed = __any_sync(0xffffffffu, failed);
       if (failed && lane == 0) set_status(status, kStatusPipeTimeout, 8, (int)blockIdx.x);
     }
+    if (prof) t_load += globaltimer_ns() - p0;
     const CommSlot rec = slots[s];
     uint8_t* seg = ring + (size_t)s * kCommSlotBytes;
     __syncwarp();
-    if (lane == 0 && !failed) comm_bulk_store(rec.dst, seg, (uint32_t)rec.bytes);
+    if (lane == 0 && !failed) {
+      const unsigned long long p3 = prof ? globaltimer_ns() : 0ull;
+      comm_bulk_store(rec.dst, seg, (uint32_t)rec.bytes);
+      if (prof) t_read += globaltimer_ns() - p3;
+    }
     ++popped;
   }
 
   // Start moving `bytes` (<= kSeg, multiple of 16) from `src` to `dst`.
   __device__ __forceinline__ void push(const void* src, void* dst, int bytes) {
-    if (pushed - popped >= (unsigned)(kCommSlots - 1)) pop();
+    if (pushed - popped >= (unsigned)kLoads) pop();
     const int s = (int)(pushed % kCommSlots);
     if (lane == 0 && !failed) {
-      // every store but the most recent one has finished reading its slot; slot s was stored two pops ago
-      asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      // slot s was stored at least kCommSlots - kLoads pops ago: all but the kStoresPending newest stores must have
+      // finished reading their segments
+      const unsigned long long p1 = prof ? globaltimer_ns() : 0ull;
+      asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoresPending) : "memory");
+      if (prof) {
+        t_read += globaltimer_ns() - p1;
+        ++n_seg;
+      }
       slots[s] = CommSlot{dst, bytes, 0};
       uint8_t* seg = ring + (size_t)s * kCommSlotBytes;
+      const unsigned long long p4 = prof ? globaltimer_ns() : 0ull;
       comm_bar_expect(&bars[s], (uint32_t)bytes);
       comm_bulk_load(seg, src, (uint32_t)bytes, &bars[s]);
+      if (prof) t_read += globaltimer_ns() - p4;
     }
     __syncwarp();
     ++pushed;
@@ -138,21 +166,33 @@ struct CommPipe {
 
   // Finish everything in flight; on return the stores are complete and fenced for a following release.
   __device__ __forceinline__ void drain() {
+    const unsigned long long p2 = prof ? globaltimer_ns() : 0ull;
     while (popped != pushed) pop();
     if (lane == 0) {
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async;" ::: "memory");
     }
     __syncwarp();
+    if (prof) t_drain += globaltimer_ns() - p2;
+  }
+  // add this warp's counters to prof[0..3] = {load waits, read waits, drains (incl. their load waits), segments}
+  __device__ __forceinline__ void report() {
+    if (prof != nullptr && lane == 0) {
+      atomicAdd(prof, t_load);
+      atomicAdd(prof + 1, t_read);
+      atomicAdd(prof + 2, t_drain);
+      atomicAdd(prof + 3, n_seg);
+    }
   }
 };
 
 // The warp sends rows [row0, row0 + nrow) (nrow <= 32) of peer buffer `dbuf`; lane i holds the unit of
 // row row0 + i in `my_u`.  Forward also stores {source rank, unit} and the unit's gate weight beside the row.
-__device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe& pipe, int my_u, int nrow, int row0,
+template <int kSlots>
+__device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe<kSlots>& pipe, int my_u, int nrow, int row0,
                                                uint8_t* dbuf, int2* dmeta, float* drowp, int lane) {
   constexpr unsigned kAll = 0xffffffffu;
-  constexpr int kSeg = CommPipe::kSeg;
+  constexpr int kSeg = CommPipe<kSlots>::kSeg;
   const int row_bytes = a.H * 2;
   if (lane < nrow) {
     if (dmeta != nullptr) dmeta[row0 + lane] = make_int2(a.me, my_u);
@@ -166,17 +206,13 @@ __device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe& pipe
   }
 }
 
-// Warp `worker` of `n_workers` takes items worker, worker + n_workers, ... of each item list.
-// Called by whole warps (all 32 lanes active); `smem` = the warp's kCommWarpBytes + kCommCtrlBytes.
-__device__ inline void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* smem, int* status) {
+// Replica weights (peer loads): the worker's share of the 32 KB chunks of every replica slot.
+template <int kSlots>
+__device__ inline void comm_pull(const CommArgs& a, CommPipe<kSlots>& pipe, int worker, int n_workers) {
   constexpr unsigned kAll = 0xffffffffu;
   const int lane = threadIdx.x & 31;
-  CommPipe pipe;
-  pipe.init(smem, status);
-
-  // ---------------------------------------------------------------- replica weights (peer loads)
-  if (a.do_pull && a.w_slots > a.home_cap) {
-    constexpr int kSeg = CommPipe::kSeg;
+  {
+    constexpr int kSeg = CommPipe<kSlots>::kSeg;
     const int rs = a.w_slots - a.home_cap;
     const int c1 = (int)pull_chunks(a.w1_elems), c2 = (int)pull_chunks(a.w2_elems);
     const int n_items = rs * (c1 + c2);
@@ -208,15 +244,24 @@ __device__ inline void comm_run(const CommArgs& a, int worker, int n_workers, ui
       if (lane == 0) red_release_gpu_add(a.pull_cnt + (size_t)j * rs + s, 1u);
     }
   }
+}
 
-  // ---------------------------------------------------------------- token rows (peer stores)
-  if (a.do_dispatch) {
+// Token rows (peer stores): the warp draws blocks from the shared ticket counter, at most max_items of them.
+template <int kSlots>
+__device__ inline void comm_dispatch(const CommArgs& a, CommPipe<kSlots>& pipe, int max_items) {
+  constexpr unsigned kAll = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  {
     int max_tiles = 0;
     for (int h = lane; h < a.R; h += 32) max_tiles = max(max_tiles, a.tiles_of[h]);
     for (int off = 16; off > 0; off >>= 1) max_tiles = max(max_tiles, __shfl_xor_sync(kAll, max_tiles, off));
     const int bpt = a.tile_rows / a.block_rows;
     const int n_items = max_tiles * bpt * a.R;
-    for (int it = worker; it < n_items; it += n_workers) {
+    for (int done = 0; done < max_items; ++done) {
+      unsigned drawn = 0;
+      if (lane == 0) drawn = atomicAdd(a.ticket, 1u);
+      const int it = (int)__shfl_sync(kAll, drawn, 0);
+      if (it >= n_items) break;
       const int b = it / a.R, k = it - b * a.R;
       int dst = a.me + k;
       if (dst >= a.R) dst -= a.R;
@@ -248,16 +293,20 @@ __device__ inline void comm_run(const CommArgs& a, int worker, int n_workers, ui
           }
         }
       }
-      // the block's copies are complete; every lane's plain stores are fenced; one lane publishes the block
+      // the block's copies are complete; the release orders them, and the lanes' plain stores (ordered before it
+      // by the warp barrier), before the counter update that publishes the block
       pipe.drain();
-      __threadfence_system();
+      if (dmeta != nullptr || drowp != nullptr) __threadfence_system();  // every lane fences its own plain stores
       __syncwarp();
       if (lane == 0) red_release_sys_add(a.arrive_ptrs[dst] + a.arrive_off + r0 / a.tile_rows, 1u);
     }
   }
+}
 
-  // ---------------------------------------------------------------- this rank's padding rows
-  if (a.do_pad) {
+// This rank's padding rows.
+__device__ inline void comm_pad(const CommArgs& a, int worker, int n_workers) {
+  const int lane = threadIdx.x & 31;
+  {
     const int vec_per_row = a.H / 8;
     const int sub = a.tile_rows / 32;  // a group's padding is shorter than one tile
     const int n_items = a.n_groups_cap * sub;
@@ -272,7 +321,25 @@ __device__ inline void comm_run(const CommArgs& a, int worker, int n_workers, ui
       if (a.local_meta != nullptr && lo + lane < hi) a.local_meta[lo + lane] = make_int2(-1, -1);
     }
   }
-  pipe.drain();
 }
+
+// Warp `worker` of `n_workers` takes chunks worker, worker + n_workers, ... of the replica weights and of the
+// padding rows; blocks of token rows are drawn from the ticket counter.
+// Called by whole warps (all 32 lanes active); `smem` = the warp's comm_warp_bytes<kSlots>().
+// Order: the worker's first block of token rows (so that the consumer's first tiles complete early), then its
+// share of the replica weights, then the remaining blocks, then its share of the padding rows.
+template <int kSlots>
+__device__ inline void comm_run(const CommArgs& a, int worker, int n_workers, uint8_t* smem, int* status,
+                                unsigned long long* prof = nullptr) {
+  CommPipe<kSlots> pipe;
+  pipe.init(smem, status, prof);
+  if (a.do_dispatch) comm_dispatch(a, pipe, 1);
+  if (a.do_pull && a.w_slots > a.home_cap) comm_pull(a, pipe, worker, n_workers);
+  if (a.do_dispatch) comm_dispatch(a, pipe, 0x7fffffff);
+  if (a.do_pad) comm_pad(a, worker, n_workers);
+  pipe.drain();
+  pipe.report();
+}
+
 
 }  // namespace epb

@@ -31,10 +31,11 @@ constexpr int TMEM_COLS = 512;
 // two SMs) computes a 256 x 256 tile with tcgen05.mma.cta_group::2; each CTA stages its own 128
 // rows of A and its own 128 columns of B, so per-SM operand traffic drops from 48 KB to 32 KB per
 // k-block and the shared-memory ring deepens from 4 to 6 stages.
-// The fused-transport variants (kComm != 0) give one ring stage to the transport warps' copy rings.
+// The fused-transport variants (kComm != 0) give 64 KB of the operand ring to the transport warps' copy rings.
 template <int kCtas, int kComm = 0>
 struct Geometry {
-  static constexpr int STAGES = (kCtas == 2 ? 6 : 4) - (kComm ? 1 : 0);
+  static constexpr int STAGES = (kCtas == 2 ? 6 : 4) - (kComm ? (kCtas == 2 ? 2 : 1) : 0);
+  static constexpr int COMM_SLOTS = kCtas == 2 ? 8 : 6;  // ring slots of a transport warp: 4 (3) loads of 4 KB in flight
   static constexpr int B_BYTES = BN * BK * 2 / kCtas;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_M = BM * kCtas;
@@ -519,6 +520,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!mbar_wait(&acc_empty[buf], acc_phase[buf] ^ 1u, abort_v, args.status, 2)) break;
         acc_phase[buf] ^= 1u;
         tc_fence_after();
+        if (args.trace != nullptr && local == 0) {
+          // first operands of this CTA's first tile have landed?  (start of useful tensor work)
+          if (mbar_wait(&full_bar[stage], phase, abort_v, args.status, 3)) atomicMin(args.trace + 3, globaltimer_ns());
+        }
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         // columns the MMA must produce for this tile (multiple of 16, at most 256); a CTA pair
         // always produces all 256 because each CTA holds a fixed half of them
@@ -562,6 +567,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (failed) break;
+        if (args.trace != nullptr) atomicMax(args.trace + 2, globaltimer_ns());
         // accumulator ready for the epilogue warps (of both CTAs)
         if (kCtas == 2) {
           const uint32_t ab = smem_u32(&acc_full[buf]);
@@ -576,9 +582,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (kComm != 0 && warp >= NUM_THREADS / 32) {
     // ------------------------------------------------------------ transport (warps 10, 11)
     uint8_t* comm_smem_base = reinterpret_cast<uint8_t*>(stage_tiles) + 8 * kStageWarpBytes +
-                              (warp - NUM_THREADS / 32) * (kCommWarpBytes + kCommCtrlBytes);
-    comm_run(args.comm, (int)blockIdx.x * COMM_WARPS + (warp - NUM_THREADS / 32), (int)gridDim.x * COMM_WARPS,
-                         comm_smem_base, args.status);
+                              (warp - NUM_THREADS / 32) * comm_warp_bytes<G::COMM_SLOTS>();
+    if (args.trace != nullptr && lane == 0) atomicMin(args.trace, globaltimer_ns());
+    comm_run<G::COMM_SLOTS>(args.comm, (int)blockIdx.x * COMM_WARPS + (warp - NUM_THREADS / 32), (int)gridDim.x * COMM_WARPS,
+             comm_smem_base, args.status, args.trace != nullptr ? args.trace + 8 : nullptr);
+    if (args.trace != nullptr && lane == 0) atomicMax(args.trace + 1, globaltimer_ns());
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..9)
     // Each warp owns 32 accumulator rows.  Columns are processed 32 at a time: the TMEM load of
@@ -772,7 +780,7 @@ template <int kCtas, int kComm>
 constexpr size_t smem_bytes() {
   return Geometry<kCtas, kComm>::STAGES * Geometry<kCtas, kComm>::STAGE_BYTES + 1024 /*align*/ +
          kCtrlBytes /*barriers, flags, tile prefix*/ + 8 * kStageWarpBytes /*staging*/ +
-         (kComm ? COMM_WARPS * (kCommWarpBytes + kCommCtrlBytes) : 0) /*transport rings*/;
+         (kComm ? COMM_WARPS * comm_warp_bytes<Geometry<kCtas, kComm>::COMM_SLOTS>() : 0) /*transport rings*/;
 }
 static_assert(smem_bytes<2, 1>() <= 232448 && smem_bytes<1, 1>() <= 232448 && smem_bytes<2, 0>() <= 232448, "shared memory budget");
 

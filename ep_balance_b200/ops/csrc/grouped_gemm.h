@@ -66,6 +66,12 @@ struct GemmArgs {
   // replica weights, with kDgrad1 (used as the plain Dgrad2) they send output gradients; the producer
   // of the same kernel -- on every rank -- gates its tiles on the arrival counters those warps advance.
   CommArgs comm;
+  // ---- optional profiling aid: unsigned long long [12] in device memory, set to {~0, 0, 0, ~0, -, -, -, -, 0, 0, 0, 0}
+  // before the launch.  The kernel leaves {earliest start of a transport warp, latest end of a transport warp,
+  // latest end of an MMA issuer, earliest moment an MMA issuer had the operands of its first tile} as
+  // global-timer values (ns) and, in words 8..11, sums over all transport warps of {ns waiting for loads,
+  // ns waiting for stores to release ring slots, ns draining at block ends, segments moved}.
+  unsigned long long* trace;
 };
 
 // Host-side tensor-map helpers (driver entry point fetched at run time; no -lcuda needed).

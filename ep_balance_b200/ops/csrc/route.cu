@@ -150,14 +150,15 @@ __global__ void __launch_bounds__(kRouteChunk) route_assign_kernel(RouteArgs a) 
 
 // ------------------------------------------------------------------ stand-alone transport
 constexpr int kCommKernelWarps = 8;
-constexpr int kCommKernelSmem = kCommKernelWarps * (kCommWarpBytes + kCommCtrlBytes) + 128;
+constexpr int kCommKernelSlots = 4;   // 8 warps x 2 loads of 4 KB in flight per SM
+constexpr int kCommKernelSmem = kCommKernelWarps * comm_warp_bytes<kCommKernelSlots>() + 128;
 
 __global__ void __launch_bounds__(kCommKernelWarps * 32) comm_kernel(const __grid_constant__ CommArgs a, int* status) {
   extern __shared__ uint8_t comm_smem_raw[];
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(comm_smem_raw) + 127) & ~(uintptr_t)127);
   const int warp = threadIdx.x >> 5;
-  comm_run(a, (int)blockIdx.x * kCommKernelWarps + warp, (int)gridDim.x * kCommKernelWarps,
-                 base + warp * (kCommWarpBytes + kCommCtrlBytes), status);
+  comm_run<kCommKernelSlots>(a, (int)blockIdx.x * kCommKernelWarps + warp, (int)gridDim.x * kCommKernelWarps,
+                             base + warp * comm_warp_bytes<kCommKernelSlots>(), status);
 }
 
 // ------------------------------------------------------------------ unit reduce
@@ -410,7 +411,7 @@ cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_
     if (e != cudaSuccess) return e;
     device_setup_done(configured, dev);
   }
-  // one CTA per SM: 8 warps x 3 segments of 4 KB in flight
+  // one CTA per SM
   comm_kernel<<<num_sms, kCommKernelWarps * 32, kCommKernelSmem, stream>>>(a, status);
   return cudaGetLastError();
 }

@@ -89,6 +89,8 @@ struct CommArgs {
   float* const* rowp_ptrs;       // R peers: float [row_capacity] (gate weight of the row's unit) or null
   unsigned* const* arrive_ptrs;  // R peers: base of the counter region
   int arrive_off;                // first word of the arrival counters [row_capacity / tile_rows] in that region
+  unsigned* ticket;              // local word, zero before the launch: the transport warps draw their blocks from it
+                                 // in ascending order, so a warp that got light blocks simply takes more of them
   // ---- padding rows of this rank (zero-filled; their meta entries, if given, become {-1, -1})
   void* local_buf;
   int2* local_meta;

@@ -182,7 +182,7 @@ void MoeRuntime::publish(const int64_t* topk_idx, int num_units, cudaStream_t st
   // arrival counters (forward, backward) and replica pull counters of this rank start every step at zero;
   // peers add to them only after their solver has seen this rank's signal
   a.clear = ptr<unsigned>("arrive");
-  a.clear_words = 2 * n_tiles_ + 2 * (cfg_.w_slots - cfg_.home_cap);
+  a.clear_words = 2 * n_tiles_ + 2 * (cfg_.w_slots - cfg_.home_cap) + 2;  // + the two ticket words of the transports
   check(launch_count_publish(a, stream), "count_publish");
 }
 
@@ -253,6 +253,7 @@ CommArgs MoeRuntime::comm_forward(const void* tokens, const float* topk_prob, bo
   a.local_buf = ptr<void>("xbuf");
   a.local_meta = ptr<int2>("meta");
   a.arrive_off = 0;
+  a.ticket = ptr<unsigned>("arrive") + 2 * n_tiles_ + 2 * (cfg_.w_slots - cfg_.home_cap);  // cleared by count_publish
   return a;
 }
 CommArgs MoeRuntime::comm_backward(const void* dout) const {
@@ -261,6 +262,7 @@ CommArgs MoeRuntime::comm_backward(const void* dout) const {
   a.buf_ptrs = ptr<void* const>("dybuf_ptrs");
   a.local_buf = ptr<void>("dybuf");
   a.arrive_off = n_tiles_;
+  a.ticket = ptr<unsigned>("arrive") + 2 * n_tiles_ + 2 * (cfg_.w_slots - cfg_.home_cap) + 1;
   return a;
 }
 
@@ -320,7 +322,11 @@ void MoeRuntime::gemm(int mode, const CUtensorMap& a, const CUtensorMap& b, int 
     g.done_R = cfg_.R;
   }
   g.row_scale = extra.row_scale;
-  if (extra.comm != nullptr) g.comm = *extra.comm;
+  if (extra.comm != nullptr) {
+    g.comm = *extra.comm;
+    g.trace = ptr<unsigned long long>("gemm_trace", false);  // optional: phase timestamps of the fused kernels
+    if (g.trace != nullptr) g.trace += mode == kFwd1 ? 0 : 12;
+  }
   check(launch_grouped_gemm(a, b, g, cfg_.num_sms, stream), extra.comm ? "grouped_gemm+transport" : "grouped_gemm");
 }
 

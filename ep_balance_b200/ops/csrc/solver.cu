@@ -754,44 +754,52 @@ __device__ void build_tables(const SolverParams& p, const RankTables& t, int me)
       }
     }
   }
+  // With home slots (home_index given) a rank's row blocks are ordered: the experts it owns first, then its
+  // replicas, each by ascending id.  The consuming GEMM walks its tiles in row order and the senders deliver in
+  // row order, so the owned groups are computed while the replica weights are still on their way.  Without home
+  // slots the order is plain ascending id (the reference's physical slot order).
+  const int passes = t.home_index != nullptr ? 2 : 1;
   for (int h = warp; h < R; h += nwarps) {
     int groups = 0, replicas = 0, rows = 0;  // running counts / padded row offset on rank h
-    for (int base = 0; base < E; base += kWarp) {
-      const int e = base + lane;
-      const bool hosted = e < E && p.x[(size_t)e * R + h] != 0;
-      const bool is_main = hosted && p.main_rank[e] == h;
-      const int size = hosted ? p.erl[(size_t)e * R + h] : 0;
-      const int padded = round_up(size, t.row_align);
-      const unsigned m = __ballot_sync(kFull, hosted);
-      const unsigned mr = __ballot_sync(kFull, hosted && !is_main);
-      const int my_group = groups + __popc(m & lt);
-      const int my_rep = replicas + __popc(mr & lt);
-      int incl = padded;
-      for (int off = 1; off < kWarp; off <<= 1) {
-        int o = __shfl_up_sync(kFull, incl, off);
-        if (lane >= off) incl += o;
-      }
-      const int my_off = rows + incl - padded;
-      int wslot = my_group;
-      if (t.home_index != nullptr) wslot = is_main ? t.home_index[e < E ? e : 0] : t.home_cap + my_rep;
-      if (e < E) {
-        if (t.slot_of) t.slot_of[(size_t)e * R + h] = hosted ? wslot : -1;
-        if (t.row_base && me >= 0) {
-          int before = 0;
-          if (hosted)
-            for (int s2 = 0; s2 < me; ++s2) before += p.q[((size_t)s2 * E + e) * R + h];
-          t.row_base[(size_t)e * R + h] = hosted ? my_off + before : -1;
+    for (int pass = 0; pass < passes; ++pass) {
+      for (int base = 0; base < E; base += kWarp) {
+        const int e = base + lane;
+        const bool hosted = e < E && p.x[(size_t)e * R + h] != 0;
+        const bool is_main = hosted && p.main_rank[e] == h;
+        const bool sel = hosted && (passes == 1 || is_main == (pass == 0));   // handled in this pass
+        const int size = sel ? p.erl[(size_t)e * R + h] : 0;
+        const int padded = round_up(size, t.row_align);
+        const unsigned m = __ballot_sync(kFull, sel);
+        const unsigned mr = __ballot_sync(kFull, sel && !is_main);
+        const int my_group = groups + __popc(m & lt);
+        const int my_rep = replicas + __popc(mr & lt);
+        int incl = padded;
+        for (int off = 1; off < kWarp; off <<= 1) {
+          int o = __shfl_up_sync(kFull, incl, off);
+          if (lane >= off) incl += o;
         }
-        if (hosted && h == me && my_group < t.n_slot) {
-          t.group_expert[my_group] = e;
-          t.group_wslot[my_group] = wslot;
-          t.group_off[my_group] = my_off;
-          t.group_rows[my_group] = size;
+        const int my_off = rows + incl - padded;
+        int wslot = my_group;
+        if (t.home_index != nullptr) wslot = is_main ? t.home_index[e < E ? e : 0] : t.home_cap + my_rep;
+        if (e < E && (sel || (!hosted && pass == 0))) {
+          if (t.slot_of) t.slot_of[(size_t)e * R + h] = hosted ? wslot : -1;
+          if (t.row_base && me >= 0) {
+            int before = 0;
+            if (hosted)
+              for (int s2 = 0; s2 < me; ++s2) before += p.q[((size_t)s2 * E + e) * R + h];
+            t.row_base[(size_t)e * R + h] = hosted ? my_off + before : -1;
+          }
+          if (hosted && h == me && my_group < t.n_slot) {
+            t.group_expert[my_group] = e;
+            t.group_wslot[my_group] = wslot;
+            t.group_off[my_group] = my_off;
+            t.group_rows[my_group] = size;
+          }
         }
+        groups += __popc(m);
+        replicas += __popc(mr);
+        rows += __shfl_sync(kFull, incl, kWarp - 1);
       }
-      groups += __popc(m);
-      replicas += __popc(mr);
-      rows += __shfl_sync(kFull, incl, kWarp - 1);
     }
     if (t.tiles_of != nullptr && lane == 0) {
       const int used = t.row_capacity > 0 && rows > t.row_capacity ? t.row_capacity : rows;

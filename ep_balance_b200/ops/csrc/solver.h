@@ -38,12 +38,13 @@ struct SolverParams {
 
 // Routing tables of one rank `me`, derived from the final (x, q).
 //
-// Two orderings exist on a rank.  *Groups* are the row blocks of the receive buffers: hosted
-// experts in ascending id, each block starting on a multiple of `row_align`.  *Weight slots*
-// say where an expert's weights live: an owner keeps expert e in home slot home_index[e]
-// (< home_cap) for ever, replicas land in slots home_cap, home_cap+1, ... in ascending expert id.
-// With home_index == nullptr weight slots equal group indices (ascending id, the reference's
-// physical slot order, eplb/integration/physical.py:23-27).
+// Two orderings exist on a rank.  *Groups* are the row blocks of the receive buffers, each block starting on
+// a multiple of `row_align`: with home slots, the experts the rank owns come first and its replicas after
+// them, each by ascending id (owned groups can be computed while replica weights are still arriving); without
+// home slots, all hosted experts by ascending id.  *Weight slots* say where an expert's weights live: an owner
+// keeps expert e in home slot home_index[e] (< home_cap) for ever, replicas land in slots home_cap,
+// home_cap+1, ... in ascending expert id.  With home_index == nullptr weight slots equal group indices
+// (ascending id, the reference's physical slot order, eplb/integration/physical.py:23-27).
 struct RankTables {
   int me;                 // -1: build nothing
   int n_slot;             // capacity of the per-group arrays
