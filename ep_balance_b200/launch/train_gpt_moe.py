@@ -72,6 +72,9 @@ def main(argv=None):
     p.add_argument("--save", default="", help="checkpoint directory to write")
     p.add_argument("--load", default="", help="checkpoint directory to resume from (newest complete step)")
     p.add_argument("--save-interval", type=int, default=0, help="save every N steps (0: only at the end when --save is set)")
+    p.add_argument("--capacity-factor", type=float, default=2.0,
+                   help="receive-buffer rows per rank as a multiple of its own routed units; a rank that receives more "
+                        "sets the overflow status, the step is not applied and the run stops")
     p.add_argument("--heartbeat-file", default="",
                    help="path of a shared file store: ranks publish a heartbeat per step, refuse to launch a step "
                         "when a peer is stale or reported a failure, and publish their own device status errors")
@@ -116,6 +119,7 @@ def main(argv=None):
     aux_coeff = float(os.environ.get("ROUTER_AUX_COEFF", "1e-2")) if balancing == "aux_loss" else 0.0
     cfg = GPTMoEConfig(vocab=a.vocab, layers=a.layers, hidden=a.hidden, heads=a.heads, ffn=a.ffn, experts=a.experts,
                        top_k=a.top_k, seq_len=a.seq_len, micro_batch=a.micro_batch, extra_slots=extra,
+                       capacity_factor=a.capacity_factor,
                        num_domains=max(domains, 1), grad_accum_dtype=torch.float32 if M > 1 else None,
                        aux_loss_coeff=aux_coeff)
     torch.manual_seed(a.seed)
