@@ -4,7 +4,8 @@ Reference: eplb/integration/__init__.py:3-50.
 """
 
 from ..parallel.comm import a2a_raw, all_to_all_single, broadcast_from_main
-from ..parallel.grouped_mlp import (grouped_expert_mlp, make_batched_gated_mlp, make_grouped_gated_mlp)
+from ..parallel.grouped_mlp import (check_row_budget, grouped_expert_mlp, make_batched_gated_mlp, make_grouped_gated_mlp,
+                                    row_budget_status)
 from ..parallel.hooks import Dispatcher, NullWeightMaterializer, RebalanceResult, WeightMaterializer
 from ..parallel.library_path import (AllToAllAdapter, BroadcastReplicaTransport, CommAdapter, ReplicaTransport,
                                      sync_free_moe_forward)

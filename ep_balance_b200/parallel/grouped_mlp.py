@@ -96,18 +96,59 @@ def slot_sort(recv_slot: torch.Tensor, valid: Optional[torch.Tensor], n_slot: in
 
 
 def compact_rows(x: torch.Tensor, order: torch.Tensor, total_rows: torch.Tensor, max_rows: Optional[int]) -> torch.Tensor:
-    """Rows in slot-major order, truncated to a host-static budget guarded by an async check."""
+    """Rows in slot-major order, truncated to a host-static budget.
+
+    When more rows arrive than the budget holds, the extra rows are dropped (they come back as zeros from
+    :func:`scatter_rows`) and the overflow is recorded in this device's row-budget status word -- code 4
+    (row overflow), site 20, detail = the number of rows that arrived.  Nothing traps and nothing
+    synchronises: the host learns of it from :func:`check_row_budget` or from a
+    :class:`~ep_balance_b200.utils.status.StatusMonitor` on :func:`row_budget_status`, and an optimizer
+    guarded by that word skips the damaged step.  The reference guards the same budget with a device-side
+    assert (eplb/integration/grouped_mlp.py:180-205), which ends the CUDA context.
+    """
     if max_rows is None:
         return x.index_select(0, order)
-    _assert_async(total_rows <= int(max_rows), "received rows exceed EPLB_MAX_RECV_ROWS")
+    _record_overflow(total_rows, int(max_rows))
     return x.index_select(0, order[: int(max_rows)])
 
 
-def _assert_async(cond: torch.Tensor, msg: str) -> None:
-    if cond.is_cuda:
-        torch._assert_async(cond, msg)
-    elif not bool(cond):
-        raise RuntimeError(msg)
+_ROW_BUDGET_SITE = 20
+_row_budget_words: dict = {}
+
+
+def row_budget_status(device) -> torch.Tensor:
+    """The ``[1, 4]`` int32 status word of the portable path's row budget on ``device`` (created on first use)."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    words = _row_budget_words.get(device)
+    if words is None:
+        words = _row_budget_words[device] = torch.zeros((1, 4), dtype=torch.int32, device=device)
+    return words
+
+
+def _record_overflow(total_rows: torch.Tensor, max_rows: int) -> None:
+    words = row_budget_status(total_rows.device)
+    total = total_rows.reshape(()).to(torch.int64)
+    over = (total > max_rows) & (words[0, 0] == 0)          # the first overflow stays on record
+    hit = torch.stack([torch.full_like(total, 4), torch.full_like(total, _ROW_BUDGET_SITE),
+                       total.clamp(max=2 ** 31 - 1), torch.full_like(total, max_rows)]).to(torch.int32)
+    words[0].copy_(torch.where(over, hit, words[0]))
+
+
+def check_row_budget(device=None, clear: bool = True) -> None:
+    """Synchronous read of the row-budget status; raises :class:`MoEStatusError` if a step overflowed."""
+    from ..utils.status import MoEStatusError
+    for dev, words in list(_row_budget_words.items()):
+        if device is not None and torch.device(device) != dev:
+            continue
+        code, site, detail, budget = (int(v) for v in words[0].tolist())
+        if code:
+            if clear:
+                words.zero_()
+            err = MoEStatusError(0, code, site, detail)
+            err.args = (f"{err.args[0]}: {detail} rows arrived, EPLB_MAX_RECV_ROWS holds {budget}",)
+            raise err
 
 
 def scatter_rows(y: torch.Tensor, order: torch.Tensor, num_rows: int) -> torch.Tensor:

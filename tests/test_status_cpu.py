@@ -41,3 +41,40 @@ def test_monitor_rejects_wrong_shapes():
     with pytest.raises(ValueError):
         StatusMonitor(torch.zeros(4, dtype=torch.int32))
     raise_if_set([[0, 0, 0, 0], [0, 9, 9, 9]])      # only the code column decides
+
+
+def test_row_budget_overflow_is_a_status_not_a_trap():
+    """Rows beyond EPLB_MAX_RECV_ROWS are dropped, recorded, and raised by the host-side check."""
+    from ep_balance_b200.parallel.grouped_mlp import (check_row_budget, grouped_expert_mlp, make_batched_gated_mlp,
+                                                       make_grouped_gated_mlp, row_budget_status)
+    torch.manual_seed(0)
+    S, H, F, T = 2, 8, 16, 10
+    w = (torch.randn(S, F, H), torch.randn(S, H, F))
+    x = torch.randn(T, H)
+    slot = torch.tensor([0, 1, 0, 1, 0, 1, 0, 1, 0, 0])
+    sizes = torch.bincount(slot, minlength=S)
+    act = torch.nn.functional.gelu
+    kw = dict(w_stacked=w, batched_mlp_fn=make_batched_gated_mlp(False, act), grouped_mlp_fn=make_grouped_gated_mlp(False, act))
+    check_row_budget()                       # clean to start with
+    full = grouped_expert_mlp(x, slot, sizes, max_recv_rows=T, **kw)
+    check_row_budget()                       # the budget held: nothing recorded
+    assert int(row_budget_status("cpu")[0, 0]) == 0
+    cut = grouped_expert_mlp(x, slot, sizes, max_recv_rows=T - 3, **kw)
+    words = row_budget_status("cpu")[0].tolist()
+    assert words == [4, 20, T, T - 3]
+    # the rows that fitted are unchanged, the dropped ones come back as zeros
+    order = torch.argsort(slot, stable=True)
+    kept, dropped = order[: T - 3], order[T - 3:]
+    assert torch.allclose(cut[kept], full[kept], atol=1e-5)
+    assert torch.count_nonzero(cut[dropped]) == 0
+    with pytest.raises(MoEStatusError) as err:
+        check_row_budget()
+    assert err.value.code == 4 and err.value.detail == T and "EPLB_MAX_RECV_ROWS" in str(err.value)
+    check_row_budget()                       # reading it cleared it
+    # the same word feeds the late monitor
+    grouped_expert_mlp(x, slot, sizes, max_recv_rows=T - 1, **kw)
+    mon = StatusMonitor(row_budget_status("cpu"))
+    mon.poll()
+    with pytest.raises(MoEStatusError):
+        mon.drain()
+    row_budget_status("cpu").zero_()
