@@ -70,6 +70,7 @@ def main() -> int:
     from .. import EPLBConfig, Loads, ProblemSpec, Topology, solve
     from ..parallel.grouped_mlp import make_batched_gated_mlp, make_grouped_gated_mlp
     from ..parallel.library_path import sync_free_moe_forward
+    from ..parallel.overlap import close_channels
     from ..parallel.symm_weights import clear_replicators
 
     E, H, F, T = a.experts, a.hidden, a.ffn, a.tokens
@@ -85,26 +86,32 @@ def main() -> int:
     mine = [e for e in range(E) if int(spec.main_rank[e]) == rank]
 
     ok = replicas > 0
+    # every weight channel x every way of holding the replicas; on GPUs the token all-to-alls run on a comm
+    # stream and the weight traffic on a stream (and, for broadcasts, a communicator) of its own
+    modes = {"held": dict(), "held, 2 chunks": dict(num_chunks=2), "leased, 2 chunks": dict(overlap=True, num_chunks=2),
+             "recomputed": dict(rematerialize=True)}
     for channel in ("broadcast", "symm"):
         os.environ["EPLB_WEIGHT_COMM"] = channel
-        weights_local = {e: (w1[e].to(dev).requires_grad_(True), w2[e].to(dev).requires_grad_(True)) for e in mine}
-        tok = tokens[rank].to(dev).requires_grad_(True)
-        pr = unit_prob[rank].to(dev).requires_grad_(True)
-        out = sync_free_moe_forward(tokens=tok, unit_token_idx=torch.arange(T, device=dev),
-                                    unit_expert=unit_expert[rank].to(dev), unit_prob=pr, plan=plan, spec=spec,
-                                    weights_local=weights_local, weight_shapes=[(2 * F, H), (H, F)],
-                                    batched_mlp_fn=make_batched_gated_mlp(True, Fn.silu),
-                                    grouped_mlp_fn=None, gated=True, act=Fn.silu, transpose_w=True)
-        out.sum().backward()
-        torch.cuda.synchronize()
-        tol = dict(atol=2e-4, rtol=2e-3)
-        good = torch.allclose(out.detach(), t_out[rank], **tol) and torch.allclose(tok.grad, t_tok[rank], **tol) \
-            and torch.allclose(pr.grad, t_pr[rank], **tol)
-        for e in mine:
-            good = good and torch.allclose(weights_local[e][0].grad, t_w1[e], **tol) \
-                and torch.allclose(weights_local[e][1].grad, t_w2[e], **tol)
-        print(f"[rank {rank}] weight channel {channel}: {'PASS' if good else 'FAIL'} replicas={replicas}", flush=True)
-        ok = ok and good
+        for mode, kw in modes.items():
+            weights_local = {e: (w1[e].to(dev).requires_grad_(True), w2[e].to(dev).requires_grad_(True)) for e in mine}
+            tok = tokens[rank].to(dev).requires_grad_(True)
+            pr = unit_prob[rank].to(dev).requires_grad_(True)
+            out = sync_free_moe_forward(tokens=tok, unit_token_idx=torch.arange(T, device=dev),
+                                        unit_expert=unit_expert[rank].to(dev), unit_prob=pr, plan=plan, spec=spec,
+                                        weights_local=weights_local, weight_shapes=[(2 * F, H), (H, F)],
+                                        batched_mlp_fn=make_batched_gated_mlp(True, Fn.silu),
+                                        grouped_mlp_fn=None, gated=True, act=Fn.silu, transpose_w=True, **kw)
+            out.sum().backward()
+            torch.cuda.synchronize()
+            tol = dict(atol=2e-4, rtol=2e-3)
+            good = torch.allclose(out.detach(), t_out[rank], **tol) and torch.allclose(tok.grad, t_tok[rank], **tol) \
+                and torch.allclose(pr.grad, t_pr[rank], **tol)
+            for e in mine:
+                good = good and torch.allclose(weights_local[e][0].grad, t_w1[e], **tol) \
+                    and torch.allclose(weights_local[e][1].grad, t_w2[e], **tol)
+            print(f"[rank {rank}] weight channel {channel}, replicas {mode}: {'PASS' if good else 'FAIL'} "
+                  f"replicas={replicas}", flush=True)
+            ok = ok and good
 
     if a.bandwidth_mb > 0 and world > 1:
         from ..parallel.onesided import SymmetricWorld
@@ -151,6 +158,7 @@ def main() -> int:
     torch.cuda.synchronize()
     dist.barrier()
     clear_replicators()
+    close_channels()
     dist.destroy_process_group()
     return 0 if int(flag) else 1
 

@@ -30,6 +30,8 @@ from ..core.problem import ProblemSpec
 from ..utils import profiling
 from .comm import a2a_raw, all_to_all_single, broadcast_from_main, global_rank
 from .grouped_mlp import grouped_expert_mlp
+from .overlap import (BackwardKick, LeasedExperts, WeightLease, forked, side_stream, side_streams_enabled,
+                      weight_channel)
 from .physical import assign_physical
 from .symm_weights import SymmReplicaTransport, replicator_for, symm_weights_enabled
 
@@ -144,13 +146,70 @@ class BroadcastReplicaTransport:
         ``rows`` (the received token rows of every chunk) are passed through unchanged.  Routing them
         through the same autograd node makes the gradient reductions of this node run strictly
         before the reverse token all-to-alls on every rank; without that dependency the autograd
-        engine may order the two kinds of collectives differently on different ranks.
+        engine may order the two kinds of collectives differently on different ranks (which matters
+        when both use one communicator).
         Returns ``stacks`` when ``rows`` is empty, else ``(rows_out, stacks)``.
         """
         out = _MaterializeStacks.apply(self, len(rows), *rows, *_owner_params(self))
         if not rows:
             return tuple(out)
         return tuple(out[: len(rows)]), tuple(out[len(rows):])
+
+    # ---- the two halves without autograd (used by the node above and by a WeightLease)
+    def acquire(self, owner_params: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
+        """Owned experts are copied into their slots; every replicated expert is broadcast from its owner
+        in a fixed order (expert id, then weight index) in which every rank takes part."""
+        params = list(owner_params) if owner_params is not None else _owner_params(self)
+        n_w = len(self.weight_shapes)
+        owned = sorted(self.weights_local)
+        slot_of_e, hosted = self.slot_of_e.tolist(), self.hosted.tolist()
+        stacks = [torch.zeros((self.n_slot,) + self.weight_shapes[j], dtype=self.dtype, device=self.device)
+                  for j in range(n_w)]
+        for i, e in enumerate(owned):
+            if hosted[e]:
+                for j in range(n_w):
+                    stacks[j][slot_of_e[e]] = params[i * n_w + j].detach().to(self.dtype)
+        with profiling.record("apply/weight_move", time_it=True, device=self.device):
+            for e, owner in zip(self.replicated, self.replicated_main):
+                root = global_rank(self.group, owner)
+                for j in range(n_w):
+                    if owner == self.my_rank:
+                        buf = params[owned.index(e) * n_w + j].detach().to(self.dtype).contiguous().clone()
+                    else:
+                        buf = torch.empty(self.weight_shapes[j], dtype=self.dtype, device=self.device)
+                    if dist.is_available() and dist.is_initialized():
+                        dist.broadcast(buf, src=root, group=self.group)
+                    if hosted[e] and owner != self.my_rank:
+                        stacks[j][slot_of_e[e]] = buf
+        return stacks
+
+    def give_back(self, grad_stacks: Sequence[Optional[torch.Tensor]]) -> List[torch.Tensor]:
+        """One gradient per owned expert and weight tensor (``sorted(weights_local)`` order): the owner's
+        own slot plus, for replicated experts, a ``dist.reduce`` over every rank in the same fixed order."""
+        n_w = len(self.weight_shapes)
+        owned = sorted(self.weights_local)
+        slot_of_e, hosted = self.slot_of_e.tolist(), self.hosted.tolist()
+        grads: Dict[Tuple[int, int], torch.Tensor] = {}
+        for e in owned:  # the owner's own instance
+            for j in range(n_w):
+                g = grad_stacks[j]
+                grads[(e, j)] = (g[slot_of_e[e]].clone(memory_format=torch.contiguous_format) if g is not None and hosted[e]
+                                 else torch.zeros(self.weight_shapes[j], dtype=self.dtype, device=self.device))
+        with profiling.record("apply/grad_move", time_it=True, device=self.device):
+            for e, owner in zip(self.replicated, self.replicated_main):
+                root = global_rank(self.group, owner)
+                for j in range(n_w):
+                    g = grad_stacks[j]
+                    if owner == self.my_rank:
+                        buf = grads[(e, j)]
+                    elif hosted[e] and g is not None:
+                        buf = g[slot_of_e[e]].clone(memory_format=torch.contiguous_format)
+                    else:
+                        buf = torch.zeros(self.weight_shapes[j], dtype=self.dtype, device=self.device)
+                    reduce_to_root(buf, root, self.group)
+                    if owner == self.my_rank:
+                        grads[(e, j)] = buf
+        return [grads[(e, j)] for e in owned for j in range(n_w)]
 
 
 def reduce_to_root(buf: torch.Tensor, root: int, group) -> None:
@@ -177,88 +236,14 @@ class _MaterializeStacks(torch.autograd.Function):
     @staticmethod
     def forward(ctx, tr: "BroadcastReplicaTransport", n_rows: int, *tensors):
         rows, owner_params = tensors[:n_rows], tensors[n_rows:]
-        ctx.n_rows = n_rows
-        n_w = len(tr.weight_shapes)
-        owned = sorted(tr.weights_local)
-        slot_of_e, hosted = tr.slot_of_e.tolist(), tr.hosted.tolist()
-        stacks = [torch.zeros((tr.n_slot,) + tr.weight_shapes[j], dtype=tr.dtype, device=tr.device) for j in range(n_w)]
-        for i, e in enumerate(owned):
-            if hosted[e]:
-                for j in range(n_w):
-                    stacks[j][slot_of_e[e]] = owner_params[i * n_w + j].detach().to(tr.dtype)
-        with profiling.record("apply/weight_move", time_it=True, device=tr.device):
-            for e, owner in zip(tr.replicated, tr.replicated_main):
-                root = global_rank(tr.group, owner)
-                for j in range(n_w):
-                    if owner == tr.my_rank:
-                        buf = owner_params[owned.index(e) * n_w + j].detach().to(tr.dtype).contiguous().clone()
-                    else:
-                        buf = torch.empty(tr.weight_shapes[j], dtype=tr.dtype, device=tr.device)
-                    if dist.is_available() and dist.is_initialized():
-                        dist.broadcast(buf, src=root, group=tr.group)
-                    if hosted[e] and owner != tr.my_rank:
-                        stacks[j][slot_of_e[e]] = buf
-        ctx.tr, ctx.owned, ctx.n_w = tr, owned, n_w
-        ctx.meta = (slot_of_e, hosted)
+        ctx.n_rows, ctx.tr = n_rows, tr
+        stacks = tr.acquire(owner_params)
         return (*[r.view_as(r) for r in rows], *stacks)
 
     @staticmethod
     def backward(ctx, *grad_all):
         grad_rows, grad_stacks = grad_all[: ctx.n_rows], grad_all[ctx.n_rows:]
-        tr, owned, n_w = ctx.tr, ctx.owned, ctx.n_w
-        slot_of_e, hosted = ctx.meta
-        grads: Dict[Tuple[int, int], torch.Tensor] = {}
-        for e in owned:  # the owner's own instance
-            for j in range(n_w):
-                g = grad_stacks[j]
-                grads[(e, j)] = (g[slot_of_e[e]].clone(memory_format=torch.contiguous_format) if g is not None and hosted[e]
-                                 else torch.zeros(tr.weight_shapes[j], dtype=tr.dtype, device=tr.device))
-        with profiling.record("apply/grad_move", time_it=True, device=tr.device):
-            for e, owner in zip(tr.replicated, tr.replicated_main):
-                root = global_rank(tr.group, owner)
-                for j in range(n_w):
-                    g = grad_stacks[j]
-                    if owner == tr.my_rank:
-                        buf = grads[(e, j)]
-                    elif hosted[e] and g is not None:
-                        buf = g[slot_of_e[e]].clone(memory_format=torch.contiguous_format)
-                    else:
-                        buf = torch.zeros(tr.weight_shapes[j], dtype=tr.dtype, device=tr.device)
-                    reduce_to_root(buf, root, tr.group)
-                    if owner == tr.my_rank:
-                        grads[(e, j)] = buf
-        return (None, None, *grad_rows, *[grads[(e, j)] for e in owned for j in range(n_w)])
-
-
-class _ReacquireExperts(torch.autograd.Function):
-    """Expert compute that does not keep replica weights alive between forward and backward.
-
-    Forward runs without a graph; backward re-materialises the weight stacks through the transport
-    (a second broadcast) and replays the expert function under autograd to obtain input and weight
-    gradients, which then flow back to the owners through the transport's own backward.
-    """
-
-    @staticmethod
-    def forward(ctx, recv_tokens, transport, compute, *owner_params):
-        with torch.no_grad():
-            out = compute(recv_tokens, transport.materialize())
-        ctx.transport, ctx.compute = transport, compute
-        ctx.save_for_backward(recv_tokens)
-        ctx.n_params = len(owner_params)
-        return out
-
-    @staticmethod
-    def backward(ctx, grad_out):
-        (recv_tokens,) = ctx.saved_tensors
-        with torch.enable_grad():
-            with profiling.record("apply/weight_repull", time_it=True, device=grad_out.device):
-                stacks = ctx.transport.materialize()
-            x = recv_tokens.detach().requires_grad_(True)
-            out = ctx.compute(x, stacks)
-            params = _owner_params(ctx.transport)
-            with profiling.record("apply/grad_move", time_it=True, device=grad_out.device):
-                grads = torch.autograd.grad(out, [x] + params, grad_out, allow_unused=True)
-        return (grads[0], None, None, *grads[1:])
+        return (None, None, *grad_rows, *ctx.tr.give_back(grad_stacks))
 
 
 def _owner_params(transport) -> List[torch.Tensor]:
@@ -277,7 +262,8 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     """MoE output ``[Ntok, H]`` for this rank's tokens under ``plan`` (see module docstring).
 
     ``weights_local`` maps each expert owned by this rank to its parameter tuple.  ``rematerialize``
-    checkpoints replication + compute; ``overlap`` uses :class:`_ReacquireExperts`.  ``num_chunks``
+    checkpoints replication + compute; ``overlap`` holds no replica between forward and backward: one
+    :class:`~ep_balance_b200.parallel.overlap.WeightLease` per call, re-started by the first backward node.  ``num_chunks``
     (default: ``EPLB_CHUNKS``) splits the units into that many dispatch/compute/combine rounds that
     share one weight acquisition.  ``gated``/``act``/``transpose_w`` are accepted for signature
     compatibility; the expert math is whatever ``batched_mlp_fn``/``grouped_mlp_fn`` compute.
@@ -290,6 +276,11 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     device, dtype = tokens.device, tokens.dtype
     n_slot = int(spec.n_slot)
     chunks = int(num_chunks if num_chunks is not None else (os.environ.get("EPLB_CHUNKS", "1") or "1"))
+    # three lanes on CUDA: this stream computes, ``comm`` carries the token all-to-alls, ``weight`` (with a
+    # communicator of its own) carries the replica weights and their gradients
+    lanes = side_streams_enabled(device)
+    comm_lane = side_stream(device, "comm") if lanes else None
+    weight_lane = side_stream(device, "weight") if lanes else None
 
     _, _, recv_per_expert = split_sizes(plan, my_rank)
     slot_to_e, _, _ = slot_tables(plan.x, my_rank, n_slot)
@@ -307,7 +298,7 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     else:
         transport = BroadcastReplicaTransport(plan=plan, spec=spec, weights_local=weights_local,
                                               weight_shapes=weight_shapes, my_rank=my_rank, n_slot=n_slot,
-                                              dtype=dtype, device=device, group=group) \
+                                              dtype=dtype, device=device, group=weight_channel(group, device)) \
             if distributed or weights_local else None
 
     with profiling.record("apply/route", time_it=True, device=device):
@@ -318,21 +309,37 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     bounds = [U * k // n_chunks for k in range(n_chunks + 1)]
     R = int(plan.q.shape[0])
 
-    # ---- all dispatches first (their reverse legs then run last in backward, after the reductions)
-    sent_l, recv_l, perm_l, rows_l, slot_l = [], [], [], [], []
+    # ---- weights first: the acquisition is enqueued before any token traffic and joined before the first GEMM
+    lease = stacks = None
+    join_weights = lambda: None  # noqa: E731
+    if overlap:
+        lease = WeightLease(transport, n_chunks, device)
+        lease.start()
+    elif not rematerialize and lanes:
+        with forked(weight_lane) as join:
+            stacks = transport.materialize()
+        join_weights = join[0]
+
+    # ---- all dispatches next (their reverse legs then run last in backward, after the reductions)
+    sent_l, recv_l, perm_l, rows_l, slot_l, arrived = [], [], [], [], [], []
     for k in range(n_chunks):
         lo, hi = bounds[k], bounds[k + 1]
         c_dst, c_phys = dst_rank[lo:hi], phys_id[lo:hi]
         perm = torch.argsort(c_dst, stable=True)
         sent = torch.zeros(R, dtype=torch.int64, device=device).scatter_add_(0, c_dst, torch.ones_like(c_dst))
-        if distributed:
-            recv = torch.empty_like(sent)
-            dist.all_to_all_single(recv, sent, group=group)
-        else:
-            recv = sent
-        with profiling.record("apply/dispatch", time_it=True, device=device):
-            rows = adapter.dispatch_chunk(tokens[unit_token_idx[lo:hi]][perm], sent, recv, group, tag=k)
-            recv_phys = adapter.dispatch_ids(c_phys[perm].contiguous(), group, tag=k)
+        payload = tokens[unit_token_idx[lo:hi]][perm]
+        ids = c_phys[perm].contiguous()
+        with forked(comm_lane) as join:
+            if distributed:
+                recv = torch.empty_like(sent)
+                dist.all_to_all_single(recv, sent, group=group)
+            else:
+                recv = sent
+            with profiling.record("apply/dispatch", time_it=True, device=device):
+                rows = adapter.dispatch_chunk(payload, sent, recv, group, tag=k)
+                recv_phys = adapter.dispatch_ids(ids, group, tag=k)
+        _shared_between(comm_lane, device, payload, ids, sent, recv, rows, recv_phys)
+        arrived.append(join[0])
         sent_l.append(sent)
         recv_l.append(recv)
         perm_l.append(perm)
@@ -349,26 +356,55 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
 
         return compute
 
-    stacks = None
-    if not overlap and not rematerialize:
-        rows_l, stacks = transport.materialize(rows_l)
-        rows_l = list(rows_l)
+    if not lanes:
+        if not overlap and not rematerialize:
+            # one communicator, one stream: the rows pass through the weight node to pin the backward order
+            rows_l, stacks = transport.materialize(rows_l)
+            rows_l = list(rows_l)
+    else:
+        for k in range(n_chunks):
+            arrived[k]()            # (cheap: recv_phys above was already consumed on this stream)
+    if stacks is not None:
+        join_weights()
+        _shared_between(weight_lane, device, *stacks)
 
-    result = torch.zeros((tokens.shape[0], tokens.shape[1]), dtype=dtype, device=device)
+    # ---- per chunk: GEMMs here, the combine on the comm lane (so that it runs under the next chunk's GEMMs)
+    backs, combined = [], []
     for k in range(n_chunks):
-        lo, hi = bounds[k], bounds[k + 1]
         compute = compute_chunk(k)
         with profiling.record("apply/expert_compute", time_it=True, device=device):
             if overlap:
-                y = _ReacquireExperts.apply(rows_l[k], transport, compute, *_owner_params(transport))
+                y = LeasedExperts.apply(rows_l[k], lease, compute, *_owner_params(transport))
             elif rematerialize:
                 y = checkpoint(lambda x, c=compute: c(x, transport.materialize()), rows_l[k], use_reentrant=False,
                                preserve_rng_state=False)
             else:
                 y = compute(rows_l[k], stacks)
-        with profiling.record("apply/combine", time_it=True, device=device):
-            back = adapter.combine_chunk(y, sent_l[k], recv_l[k], group, tag=k)
+        with forked(comm_lane) as join:
+            with profiling.record("apply/combine", time_it=True, device=device):
+                back = adapter.combine_chunk(y, sent_l[k], recv_l[k], group, tag=k)
+        _shared_between(comm_lane, device, y, back)
         adapter.chunk_state(k)
-        per_unit = back[torch.argsort(perm_l[k])]
+        backs.append(back)
+        combined.append(join[0])
+
+    result = torch.zeros((tokens.shape[0], tokens.shape[1]), dtype=dtype, device=device)
+    for k in range(n_chunks):
+        lo, hi = bounds[k], bounds[k + 1]
+        combined[k]()
+        per_unit = backs[k][torch.argsort(perm_l[k])]
         result = result.index_add(0, unit_token_idx[lo:hi], unit_prob[lo:hi].unsqueeze(1).to(dtype) * per_unit)
+    if lease is not None:
+        result = BackwardKick.apply(result, lease)
     return result
+
+
+def _shared_between(lane, device, *tensors) -> None:
+    """Tensors that cross between this stream and ``lane``: tell the caching allocator about both users."""
+    if lane is None:
+        return
+    here = torch.cuda.current_stream(device)
+    for t in tensors:
+        if isinstance(t, torch.Tensor) and t.is_cuda:
+            t.record_stream(lane)
+            t.record_stream(here)

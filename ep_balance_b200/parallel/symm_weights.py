@@ -262,6 +262,13 @@ class SymmReplicaTransport:
         mine = [rows[j].index_select(0, self._owned_rows) for j in range(n_w)]
         return [mine[j][i] for i in range(len(self.owned)) for j in range(n_w)]
 
+    # ---- the two halves without autograd (what a WeightLease calls)
+    def acquire(self, owner_params: Optional[Sequence[torch.Tensor]] = None) -> List[torch.Tensor]:
+        return self.materialize_replicas(owner_params)
+
+    def give_back(self, grad_stacks: Sequence[Optional[torch.Tensor]]) -> List[torch.Tensor]:
+        return self.reduce_grads(grad_stacks)
+
     # ---- protocol used by the library path
     def materialize(self, rows: Sequence[torch.Tensor] = ()):
         params = [w for e in self.owned for w in self.weights_local[e]]

@@ -63,15 +63,29 @@ def _worker(rank, port, mode):
     weights_local = {e: (w1[e].clone().requires_grad_(True), w2[e].clone().requires_grad_(True)) for e in mine}
     tok = tokens[rank].clone().requires_grad_(True)
     pr = unit_prob[rank].clone().requires_grad_(True)
-    kw = dict(rematerialize=mode == "remat", overlap=mode == "overlap",
-              num_chunks=2 if mode == "chunks" else None,
+    leases = []
+    if mode == "overlap_chunks":       # count what the lease does: the chunks must share it
+        import ep_balance_b200.parallel.library_path as lp
+
+        class CountingLease(lp.WeightLease):
+            def __init__(self, *a, **k):
+                super().__init__(*a, **k)
+                leases.append(self)
+
+        lp.WeightLease = CountingLease
+    kw = dict(rematerialize=mode == "remat", overlap=mode in ("overlap", "overlap_chunks"),
+              num_chunks=2 if mode in ("chunks", "overlap_chunks") else None,
               grouped_mlp_fn=None if mode == "padded" else make_grouped_gated_mlp(True, Fn.silu))
     out = sync_free_moe_forward(tokens=tok, unit_token_idx=torch.arange(T), unit_expert=unit_expert[rank],
                                 unit_prob=pr, plan=plan, spec=spec, weights_local=weights_local,
                                 weight_shapes=[(2 * F, H), (H, F)],
                                 batched_mlp_fn=make_batched_gated_mlp(True, Fn.silu), gated=True, act=Fn.silu,
                                 transpose_w=True, **kw)
+    if leases:
+        assert (leases[0].acquisitions, leases[0]._stacks) == (1, None), "replicas must not outlive the forward"
     out.sum().backward()
+    if leases:   # one pull per pass for both chunks, one gradient return per layer call
+        assert (len(leases), leases[0].acquisitions, leases[0].returns) == (1, 2, 1)
     t_out, t_tok, t_pr, t_w1, t_w2 = _truth()
     tol = dict(atol=1e-4, rtol=1e-3)
     assert torch.allclose(out.detach(), t_out[rank], **tol), float((out.detach() - t_out[rank]).abs().max())
@@ -85,7 +99,7 @@ def _worker(rank, port, mode):
 
 
 @pytest.mark.parametrize("mode,port", [("plain", 6121), ("padded", 6122), ("remat", 6123), ("overlap", 6124),
-                                       ("chunks", 6125)])
+                                       ("chunks", 6125), ("overlap_chunks", 6126)])
 def test_library_path_matches_single_process_truth(mode, port):
     mp.spawn(_worker, args=(port, mode), nprocs=W, join=True)
 
