@@ -305,6 +305,7 @@ class FusedMoE(nn.Module):
             "exp_prefix": torch.zeros(E + 1, **i32), "sorted_units": torch.zeros(self.max_units, **i32),
             "done_ctr": torch.zeros(4, **i32),
             "unit_dst": torch.zeros(self.max_units, **i32), "unit_row": torch.zeros(self.max_units, **i32),
+            "unit_pos": torch.zeros(self.max_units, **i32),
             "hbuf": torch.zeros((self.row_capacity, 2 * F), dtype=torch.bfloat16, device=dev),
             "act": torch.zeros((self.row_capacity, F), dtype=torch.bfloat16, device=dev),
         }

@@ -187,15 +187,16 @@ struct CommPipe {
 };
 
 // The warp sends rows [row0, row0 + nrow) (nrow <= 32) of peer buffer `dbuf`; lane i holds the unit of
-// row row0 + i in `my_u`.  Forward also stores {source rank, unit} and the unit's gate weight beside the row.
+// row row0 + i in `my_u` and that unit's position in this rank's sorted order in `my_pos`.  Forward also stores
+// {source rank, position} (where the host returns the row) and the unit's gate weight beside the row.
 template <int kSlots>
-__device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe<kSlots>& pipe, int my_u, int nrow, int row0,
+__device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe<kSlots>& pipe, int my_u, int my_pos, int nrow, int row0,
                                                uint8_t* dbuf, int2* dmeta, float* drowp, int lane) {
   constexpr unsigned kAll = 0xffffffffu;
   constexpr int kSeg = CommPipe<kSlots>::kSeg;
   const int row_bytes = a.H * 2;
   if (lane < nrow) {
-    if (dmeta != nullptr) dmeta[row0 + lane] = make_int2(a.me, my_u);
+    if (dmeta != nullptr) dmeta[row0 + lane] = make_int2(a.me, my_pos);
     if (drowp != nullptr) drowp[row0 + lane] = a.unit_prob[my_u];
   }
   for (int i = 0; i < nrow; ++i) {
@@ -288,7 +289,7 @@ __device__ inline void comm_dispatch(const CommArgs& a, CommPipe<kSlots>& pipe, 
           for (int row0 = slo; row0 < shi; row0 += 32) {
             const int nrow = min(32, shi - row0);
             const int my_u = lane < nrow ? a.sorted_units[pos + lane] : 0;
-            comm_send_rows(a, pipe, my_u, nrow, row0, dbuf, dmeta, drowp, lane);
+            comm_send_rows(a, pipe, my_u, pos + lane, nrow, row0, dbuf, dmeta, drowp, lane);
             pos += nrow;
           }
         }

@@ -42,7 +42,7 @@ struct GemmArgs {
   void* out1;                  // kFwd1: act [T, N]
   const float* row_scale;      // kFwd1: optional [T] factor folded into act (the row's gate weight); null: 1
   void* const* out_ptrs;       // scatter modes: R peer buffers [units, N] (null -> local out0)
-  const int2* meta;            // scatter modes: {src rank, unit} per row
+  const int2* meta;            // scatter modes: {src rank, row in that rank's buffer} per row
   int* status;
   unsigned long long wait_ns;  // budget of the waits below (0: the library default)
   // ---- operand gating (each may be null).  The TMA producer polls before the first load of a tile:

@@ -803,7 +803,7 @@ __global__ void __launch_bounds__(256) dispatch_fp8_kernel(DispatchFp8Args a) {
     const int kb = v >> 4;
     if ((lane & 15) == 0) chunk_row[(size_t)(kb >> 2) * 512 + chunk_byte(row & 127, kb)] = (uint8_t)(e + 127);
   }
-  if (lane == 0 && a.meta_ptrs != nullptr) a.meta_ptrs[dst][row] = make_int2(a.me, u);
+  if (lane == 0 && a.meta_ptrs != nullptr) a.meta_ptrs[dst][row] = make_int2(a.me, a.unit_pos[u]);
 }
 
 // SwiGLU + quantisation in one pass: h [rows, 2F] (gate columns, then up columns) ->

@@ -82,9 +82,10 @@ struct DispatchFp8Args {
   int num_units, topk, H, R, me;
   const int32_t* unit_dst;      // [U]
   const int32_t* unit_row;      // [U]
+  const int32_t* unit_pos;      // [U] position of the unit in the source's expert-sorted order (where its row returns)
   uint8_t* const* xq_ptrs;      // R peers: e4m3 [row_capacity, H]
   uint8_t* const* sfx_ptrs;     // R peers: scale chunks [row_capacity / 128][kgroups][512]
-  int2* const* meta_ptrs;       // R peers: {src rank, unit} per row
+  int2* const* meta_ptrs;       // R peers: {src rank, position at the source} per row
   int row_capacity;
 };
 cudaError_t launch_dispatch_fp8(const DispatchFp8Args& a, cudaStream_t stream);

@@ -125,6 +125,7 @@ __global__ void __launch_bounds__(kRouteChunk) route_assign_kernel(RouteArgs a) 
     if (u < a.num_units) {
       a.unit_dst[u] = -1;
       a.unit_row[u] = -1;
+      if (a.unit_pos != nullptr) a.unit_pos[u] = -1;
     }
     return;
   }
@@ -137,7 +138,8 @@ __global__ void __launch_bounds__(kRouteChunk) route_assign_kernel(RouteArgs a) 
     ++dst;
     have = qrow[dst];
   }
-  if (j >= pre + have) {
+  const bool placed = j < pre + have;
+  if (!placed) {
     set_status(a.status, kStatusBadArgument, 40, e);
     a.unit_dst[u] = -1;
     a.unit_row[u] = -1;
@@ -146,6 +148,7 @@ __global__ void __launch_bounds__(kRouteChunk) route_assign_kernel(RouteArgs a) 
     a.unit_row[u] = a.row_base[(size_t)e * R + dst] + (j - pre);
   }
   if (a.sorted_units != nullptr) a.sorted_units[a.exp_prefix[e] + j] = u;
+  if (a.unit_pos != nullptr) a.unit_pos[u] = placed ? a.exp_prefix[e] + j : -1;
 }
 
 // ------------------------------------------------------------------ stand-alone transport
@@ -163,6 +166,7 @@ __global__ void __launch_bounds__(kCommKernelWarps * 32) comm_kernel(const __gri
 
 // ------------------------------------------------------------------ unit reduce
 __global__ void __launch_bounds__(256) unit_reduce_kernel(const uint4* __restrict__ unit_rows,
+                                                         const int32_t* __restrict__ unit_pos,
                                                          const float* __restrict__ unit_scale,
                                                          uint4* __restrict__ out, int num_tokens, int topk,
                                                          int vec_per_row, UnitReduceWait wait,
@@ -175,7 +179,10 @@ __global__ void __launch_bounds__(256) unit_reduce_kernel(const uint4* __restric
   }
   if (copy_dst != nullptr) {
     const size_t n = (size_t)num_tokens * topk;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) copy_dst[i] = copy_src[i];
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+      const int pos = unit_pos != nullptr ? unit_pos[i] : (int)i;
+      copy_dst[i] = pos >= 0 ? copy_src[pos] : 0.f;
+    }
   }
   // one warp per (token, 32-vector chunk of the row): small batches still fill the machine
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, wpb = blockDim.x >> 5;
@@ -189,7 +196,9 @@ __global__ void __launch_bounds__(256) unit_reduce_kernel(const uint4* __restric
 #pragma unroll 8
   for (int k = 0; k < topk; ++k) {
     const size_t u = (size_t)t * topk + k;
-    const uint4 val = unit_rows[u * vec_per_row + v];
+    const long long pos = unit_pos != nullptr ? (long long)unit_pos[u] : (long long)u;
+    if (pos < 0) continue;
+    const uint4 val = unit_rows[(size_t)pos * vec_per_row + v];
     const float s = unit_scale ? unit_scale[u] : 1.f;
     const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&val);
 #pragma unroll
@@ -416,8 +425,8 @@ cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_
   return cudaGetLastError();
 }
 
-cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, void* out, int num_tokens, int topk,
-                               int H, const UnitReduceWait* wait, const float* copy_src, float* copy_dst,
+cudaError_t launch_unit_reduce(const void* unit_rows, const int32_t* unit_pos, const float* unit_scale, void* out,
+                               int num_tokens, int topk, int H, const UnitReduceWait* wait, const float* copy_src, float* copy_dst,
                                cudaStream_t stream) {
   if (H % 8 != 0) return cudaErrorInvalidValue;
   const int wpb = 8;
@@ -426,7 +435,7 @@ cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, v
   UnitReduceWait w{};
   if (wait != nullptr) w = *wait;
   unit_reduce_kernel<<<(unsigned)((items + wpb - 1) / wpb), wpb * 32, 0, stream>>>(
-      reinterpret_cast<const uint4*>(unit_rows), unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8, w,
+      reinterpret_cast<const uint4*>(unit_rows), unit_pos, unit_scale, reinterpret_cast<uint4*>(out), num_tokens, topk, H / 8, w,
       copy_src, copy_src != nullptr ? copy_dst : nullptr);
   return cudaGetLastError();
 }

@@ -46,6 +46,7 @@ struct RouteArgs {
   int32_t* unit_dst;            // [U]
   int32_t* unit_row;            // [U]
   int32_t* sorted_units;        // [U] (may be null)
+  int32_t* unit_pos;            // [U] position of the unit in sorted_units, -1 if it goes nowhere (may be null)
   int* status;
 };
 cudaError_t launch_route_assign(const RouteArgs& a, cudaStream_t stream);
@@ -85,7 +86,7 @@ struct CommArgs {
   const int32_t* send_off;       // [E, R] units of expert e that go to ranks below dst
   const int32_t* tiles_of;       // [R] used M-tiles of every rank's receive buffer
   void* const* buf_ptrs;         // R peers: bf16 [row_capacity, H]
-  int2* const* meta_ptrs;        // R peers: int2 [row_capacity] ({src rank, unit}) or null
+  int2* const* meta_ptrs;        // R peers: int2 [row_capacity] ({src rank, position of the unit in sorted_units}) or null
   float* const* rowp_ptrs;       // R peers: float [row_capacity] (gate weight of the row's unit) or null
   unsigned* const* arrive_ptrs;  // R peers: base of the counter region
   int arrive_off;                // first word of the arrival counters [row_capacity / tile_rows] in that region
@@ -112,9 +113,12 @@ constexpr int kPullChunkBytes = 32768;
 __host__ __device__ inline unsigned pull_chunks(size_t elems) { return (unsigned)((elems * 2 + kPullChunkBytes - 1) / kPullChunkBytes); }
 cudaError_t launch_comm(const CommArgs& a, int num_sms, int* status, cudaStream_t stream);
 
-// out[t] = sum_k scale[t*topk+k] * rows[t*topk+k]   (scale may be null: plain sum)
-// `copy_src`/`copy_dst` (may be null): num_tokens * topk floats copied alongside (the gate-weight gradients
-// that the peers stored into this rank's symmetric buffer, handed to the caller's tensor).
+// out[t] = sum_k scale[u] * rows[pos(u)], u = t*topk+k   (scale may be null: plain sum)
+// `unit_pos` (may be null: pos(u) = u) maps a unit to its row: the hosts return a unit's row at the unit's position
+// in this rank's expert-sorted order, so that the rows one host returns for one expert are contiguous here and its
+// epilogue's peer stores walk this rank's buffer sequentially; a negative position contributes nothing.
+// `copy_src`/`copy_dst` (may be null): copy_dst[u] = copy_src[pos(u)] for num_tokens * topk floats (the gate-weight
+// gradients that the peers stored into this rank's symmetric buffer, handed to the caller's tensor).
 // With `wait_signal != nullptr` every CTA first waits (bounded) until *wait_signal >= *wait_epoch * R:
 // the peers' "all my rows are stored" signals of the producing GEMM (GemmArgs::done_*).
 struct UnitReduceWait {
@@ -124,9 +128,9 @@ struct UnitReduceWait {
   unsigned long long budget_ns;
   int* status;
 };
-cudaError_t launch_unit_reduce(const void* unit_rows, const float* unit_scale, void* out, int num_tokens,
-                               int topk, int H, const UnitReduceWait* wait, const float* copy_src, float* copy_dst,
-                               cudaStream_t stream);
+cudaError_t launch_unit_reduce(const void* unit_rows, const int32_t* unit_pos, const float* unit_scale, void* out,
+                               int num_tokens, int topk, int H, const UnitReduceWait* wait, const float* copy_src,
+                               float* copy_dst, cudaStream_t stream);
 
 // Cross-rank barrier on symmetric signal words: every rank adds 1 to word `slot` of every peer,
 // then waits (bounded) until its own word reaches (epoch+1)*R.  `epoch_word` lives in local
@@ -177,7 +181,7 @@ struct SwigluBwdArgs {
   int rows, F;
   const int32_t* row_limit;     // device: rows in use (may be null)
   const float* rowp;            // [rows] or null
-  const int2* meta;             // [rows] {src rank, unit}; rows with src < 0 are padding
+  const int2* meta;             // [rows] {src rank, position at the source}; rows with src < 0 are padding
   float* const* dprob_ptrs;     // R peers: float [U] or null
 };
 cudaError_t launch_swiglu_backward(const SwigluBwdArgs& a, cudaStream_t stream);

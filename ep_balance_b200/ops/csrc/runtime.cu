@@ -117,7 +117,7 @@ MoeRuntime::MoeRuntime(const LayerConfig& cfg, const std::map<std::string, uint6
   tables_.totals = ptr<int32_t>("totals");
   tables_.send_off = ptr<int32_t>("send_off");
   tables_.tiles_of = ptr<int32_t>("tiles_of");
-  for (const char* name : {"arrive", "arrive_ptrs", "chunk_hist", "hist_acc", "exp_prefix", "sorted_units", "done_ctr", "rowp",
+  for (const char* name : {"arrive", "arrive_ptrs", "chunk_hist", "hist_acc", "exp_prefix", "sorted_units", "unit_pos", "done_ctr", "rowp",
                            "rowp_ptrs", "dprob", "dprob_ptrs", "dact", "meta"})
     ptr<void>(name);
 
@@ -202,6 +202,7 @@ void MoeRuntime::route(const int64_t* topk_idx, int num_units, cudaStream_t stre
   a.unit_dst = ptr<int32_t>("unit_dst");
   a.unit_row = ptr<int32_t>("unit_row");
   a.sorted_units = ptr<int32_t>("sorted_units");
+  a.unit_pos = ptr<int32_t>("unit_pos");
   a.status = sp_.status;
   check(launch_route_assign(a, stream), "route_assign");
 }
@@ -364,7 +365,7 @@ UnitReduceWait MoeRuntime::reduce_wait(int slot) const {
 }
 void MoeRuntime::reduce_out(void* out, int num_tokens, cudaStream_t stream, bool wait_peers, const float* unit_scale) {
   const UnitReduceWait w = reduce_wait(2);
-  check(launch_unit_reduce(ptr<void>("ybuf"), unit_scale, out, num_tokens, cfg_.topk, cfg_.H,
+  check(launch_unit_reduce(ptr<void>("ybuf"), ptr<const int32_t>("unit_pos"), unit_scale, out, num_tokens, cfg_.topk, cfg_.H,
                            wait_peers && peers() ? &w : nullptr, nullptr, nullptr, stream),
         "unit_reduce");
 }
@@ -443,6 +444,7 @@ void MoeRuntime::dispatch_fp8(const void* tokens, int num_units, cudaStream_t st
   a.me = cfg_.me;
   a.unit_dst = ptr<const int32_t>("unit_dst");
   a.unit_row = ptr<const int32_t>("unit_row");
+  a.unit_pos = ptr<const int32_t>("unit_pos");
   a.xq_ptrs = ptr<uint8_t* const>("xq_ptrs");
   a.sfx_ptrs = ptr<uint8_t* const>("sfx_ptrs");
   a.meta_ptrs = ptr<int2* const>("meta_ptrs");
@@ -533,7 +535,7 @@ void MoeRuntime::dgrad1(cudaStream_t stream) {
 }
 void MoeRuntime::reduce_dtokens(void* dtokens, float* dprob, int num_tokens, cudaStream_t stream, bool wait_peers) {
   const UnitReduceWait w = reduce_wait(4);
-  check(launch_unit_reduce(ptr<void>("dxbuf"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H,
+  check(launch_unit_reduce(ptr<void>("dxbuf"), ptr<const int32_t>("unit_pos"), nullptr, dtokens, num_tokens, cfg_.topk, cfg_.H,
                            wait_peers && peers() ? &w : nullptr, ptr<const float>("dprob"), dprob, stream),
         "unit_reduce(bwd)");
 }

@@ -139,6 +139,7 @@ class BroadcastReplicaTransport:
         flat = torch.cat([rep, spec.main_rank.index_select(0, rep).to(torch.int64)]).tolist()
         self.replicated, self.replicated_main = flat[: len(flat) // 2], flat[len(flat) // 2:]
         _, self.slot_of_e, self.hosted = slot_tables(plan.x, my_rank, n_slot)
+        self._slot_of_e, self._hosted = self.slot_of_e.tolist(), self.hosted.tolist()
 
     def materialize(self, rows: Sequence[torch.Tensor] = ()):
         """Stacked ``[n_slot, *shape]`` weights, differentiable w.r.t. the owners' parameters.
@@ -162,7 +163,7 @@ class BroadcastReplicaTransport:
         params = list(owner_params) if owner_params is not None else _owner_params(self)
         n_w = len(self.weight_shapes)
         owned = sorted(self.weights_local)
-        slot_of_e, hosted = self.slot_of_e.tolist(), self.hosted.tolist()
+        slot_of_e, hosted = self._slot_of_e, self._hosted
         stacks = [torch.zeros((self.n_slot,) + self.weight_shapes[j], dtype=self.dtype, device=self.device)
                   for j in range(n_w)]
         for i, e in enumerate(owned):
@@ -188,7 +189,7 @@ class BroadcastReplicaTransport:
         own slot plus, for replicated experts, a ``dist.reduce`` over every rank in the same fixed order."""
         n_w = len(self.weight_shapes)
         owned = sorted(self.weights_local)
-        slot_of_e, hosted = self.slot_of_e.tolist(), self.hosted.tolist()
+        slot_of_e, hosted = self._slot_of_e, self._hosted
         grads: Dict[Tuple[int, int], torch.Tensor] = {}
         for e in owned:  # the owner's own instance
             for j in range(n_w):
@@ -338,13 +339,15 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
             with profiling.record("apply/dispatch", time_it=True, device=device):
                 rows = adapter.dispatch_chunk(payload, sent, recv, group, tag=k)
                 recv_phys = adapter.dispatch_ids(ids, group, tag=k)
-        _shared_between(comm_lane, device, payload, ids, sent, recv, rows, recv_phys)
+            # still on the comm lane: the received ids may be read only after their all-to-all
+            recv_slot = recv_phys - my_rank * n_slot
+        _shared_between(comm_lane, device, payload, ids, sent, recv, rows, recv_phys, recv_slot)
         arrived.append(join[0])
         sent_l.append(sent)
         recv_l.append(recv)
         perm_l.append(perm)
         rows_l.append(rows)
-        slot_l.append(recv_phys - my_rank * n_slot)
+        slot_l.append(recv_slot)
 
     def compute_chunk(k: int):
         sizes = torch.zeros(n_slot, dtype=torch.int64, device=device).scatter_add_(
@@ -363,7 +366,7 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
             rows_l = list(rows_l)
     else:
         for k in range(n_chunks):
-            arrived[k]()            # (cheap: recv_phys above was already consumed on this stream)
+            arrived[k]()            # nothing received on the comm lane was touched on this stream before this point
     if stacks is not None:
         join_weights()
         _shared_between(weight_lane, device, *stacks)
