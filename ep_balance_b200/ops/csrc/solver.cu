@@ -35,14 +35,20 @@ __device__ __forceinline__ bool better(const Cand& a, const Cand& b) {
   if (a.expert != b.expert) return a.expert < b.expert;
   return a.target < b.target;
 }
+// The best candidate of the warp under better(), on EVERY lane.  The order is lexicographic, so five warp-wide
+// integer reductions (one instruction each), each over the lanes still tied on the earlier fields, replace a
+// 5-step butterfly of 5-word shuffles: the repair loop's critical path is made of these.
 __device__ __forceinline__ Cand warp_best(Cand v) {
-  for (int off = kWarp / 2; off > 0; off >>= 1) {
-    Cand o{__shfl_down_sync(kFull, v.delta, off), __shfl_down_sync(kFull, v.load, off),
-           __shfl_down_sync(kFull, v.cost, off), __shfl_down_sync(kFull, v.expert, off),
-           __shfl_down_sync(kFull, v.target, off)};
-    if (better(o, v)) v = o;
-  }
-  return v;
+  const int d = __reduce_max_sync(kFull, v.delta);
+  bool in = v.delta == d;
+  const int l = __reduce_min_sync(kFull, in ? v.load : INT_MAX);
+  in = in && v.load == l;
+  const int c = __reduce_min_sync(kFull, in ? v.cost : INT_MAX);
+  in = in && v.cost == c;
+  const int e = __reduce_min_sync(kFull, in ? v.expert : INT_MAX);
+  in = in && v.expert == e;
+  const int t = __reduce_min_sync(kFull, in ? v.target : INT_MAX);
+  return Cand{d, l, c, e, t};
 }
 
 __device__ __forceinline__ int safe_move(int have, int there, int left, int u_min) {
@@ -87,6 +93,7 @@ struct Smem {
   int* erl_c;       // [E * n] cached erl[e, domain rank] of the domain being repaired (or null)
   signed char* x_c; // [E * n] cached x[e, domain rank]
   int* q_c;         // [R * E * n] cached q[s, e, domain rank] (or unused)
+  int* cost_c;      // [64] link costs between the domain's ranks (domains of at most 8 ranks)
 };
 
 __host__ __device__ inline int pow2_at_least(int n) {
@@ -114,6 +121,8 @@ __device__ Smem carve(unsigned char* base, int R, int E) {
   base += sizeof(int) * R;
   s.wcand = reinterpret_cast<Cand*>(base);
   base += sizeof(Cand) * 32;
+  s.cost_c = reinterpret_cast<int*>(base);
+  base += sizeof(int) * 64;
   s.erl_c = reinterpret_cast<int*>(base);
   s.x_c = reinterpret_cast<signed char*>(base + sizeof(int) * (size_t)E * R);
   s.q_c = reinterpret_cast<int*>(base + (((size_t)E * R * 5 + 15) / 16) * 16);
@@ -143,15 +152,19 @@ __device__ int collect_domain(const SolverParams& p, Smem& s, int d) {
 }
 
 // ------------------------------------------------------------------ phase 0
-__device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
+// Returns the number of ranks in domain d (s.dom_ranks / s.local_idx describe it on return).
+__device__ int phase0_domain(const SolverParams& p, Smem& s, int d) {
   __shared__ int n_valid;
   const int tid = threadIdx.x, nt = blockDim.x;
   const int R = p.R, E = p.E;
   const int n = collect_domain(p, s, d);
-  if (n == 0) return;
+  if (n == 0) return 0;
   // With the cache region available the domain's placement columns live in shared memory while
   // candidates are admitted (one global round trip per candidate otherwise) and are stored once.
   signed char* xc = p.cache_stage2 ? s.x_c : nullptr;
+  // link costs inside the domain, for the repair loop of a CTA that keeps this domain (their latency hides here)
+  if (n <= 8)
+    for (int idx = tid; idx < n * n; idx += nt) s.cost_c[idx] = __ldg(p.cost + (size_t)s.dom_ranks[idx / n] * R + s.dom_ranks[idx % n]);
   if (tid == 0) n_valid = 0;
   for (int i = tid; i < n; i += nt) s.slot[i] = 0;
   __syncthreads();
@@ -164,20 +177,43 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
     else p.x[(size_t)e * R + r] = own ? 1 : 0;
     if (own) atomicAdd(&s.slot[i], 1);
   }
-  // gate and benefit
-  for (int e = tid; e < E; e += nt) {
+  // gate and benefit (the owner's domain comes from the index collect_domain() left in shared memory, so the
+  // loop has no load that depends on another load); valid candidates are also listed compactly in s.order
+  // (with one domain, or with cross-domain replicas switched off, nothing can qualify: the loop is skipped)
+  for (int e = tid; e < E && p.allow_cross && p.D > 1; e += nt) {
     long long T = 0;
     const int owner = __ldg(p.main_rank + e);
     const long long wb = __ldg(p.weight_bytes + e);
     for (int i = 0; i < n; ++i) T += __ldg(p.omega + (size_t)s.dom_ranks[i] * E + e);
     long long rhs = 2 * T * p.s_tok;
-    bool valid = p.allow_cross && __ldg(p.dom + owner) != d && T > 0 && wb < rhs;
+    bool valid = p.allow_cross && s.local_idx[owner] < 0 && T > 0 && wb < rhs;
     s.prio[e] = valid ? rhs - wb : -1;
-    if (valid) atomicAdd(&n_valid, 1);
+    if (valid) {
+      const int at = atomicAdd(&n_valid, 1);
+      if (at < kWarp) s.order[at] = e;  // only used when at most 32 candidates exist
+    }
   }
   __syncthreads();
   const int nv = n_valid;
-  if (nv > 0) {
+  if (nv > 0 && nv <= kWarp) {
+    // Few candidates (the usual case: only experts whose traffic outweighs their weights qualify): one warp
+    // ranks them by counting, which gives the same order as sorting the whole row -- descending benefit, ties by
+    // ascending expert id; the pairs are distinct, so every rank is taken exactly once.
+    if (tid < kWarp) {
+      const int lane = tid;
+      const int me = lane < nv ? s.order[lane] : -1;
+      const long long mp = lane < nv ? s.prio[me] : -1;
+      int rank = 0;
+      for (int j = 0; j < nv; ++j) {
+        const int oe = __shfl_sync(kFull, me, j);
+        const long long op = __shfl_sync(kFull, mp, j);
+        if (op > mp || (op == mp && oe < me)) ++rank;
+      }
+      __syncwarp(kFull);
+      if (lane < nv) s.order[rank] = me;
+      __syncwarp(kFull);
+    }
+  } else if (nv > 0) {
     // Descending benefit, ties by ascending expert id (what a stable descending sort of the row gives).  The
     // (benefit, id) pairs are distinct, so any comparison sort yields this one order: a bitonic sort,
     // O(E log^2 E / threads) instead of counting all pairs.  Invalid entries (-1) and the padding (-2) sink
@@ -241,6 +277,8 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
         }
       }
     }
+  }
+  if (nv > 0) {
     if (tid < kWarp) {
       const int lane = tid;
       // free slots left in the domain: once they are used up no later candidate can be admitted, so the walk stops
@@ -279,6 +317,7 @@ __device__ void phase0_domain(const SolverParams& p, Smem& s, int d) {
       p.x[(size_t)e * R + s.dom_ranks[i]] = xc[idx];
     }
   for (int i = tid; i < n; i += nt) p.slot_used[s.dom_ranks[i]] = s.slot[i];
+  return n;
 }
 
 // ------------------------------------------------------------------ phase 1
@@ -339,20 +378,96 @@ __device__ void phase1_routing_masks(const SolverParams& p, Smem& s) {
 }
 
 // One CTA computes exactly the quota columns of ITS domain's ranks (all sources, all experts), straight
-// into the shared-memory caches that the repair loop works on, and stores them to global memory on the
-// way.  The repair loop then needs neither a grid barrier after routing nor a cache fill.
-// Requires R <= 64 and the quota cache (s.q_c, s.erl_c) of this domain to fit.
-__device__ void phase1_domain(const SolverParams& p, Smem& s, int d) {
-  __shared__ unsigned long long dom_mask[64];
-  const int R = p.R, E = p.E, u_min = p.u_min;
+// into the shared-memory caches that the repair loop works on, and stores the non-zero ones to global memory
+// (the grid cleared q before the barrier that precedes this phase).  The repair loop then needs neither a grid
+// barrier after routing nor a cache fill.  Requires R <= 64, u_min == 1 and the quota cache of this domain to fit.
+// MaskT: host sets as 32-bit words when R <= 32 (half the instructions of the 64-bit form; this phase runs on one
+// SM per domain and is bound by instruction issue, not by memory).
+template <typename MaskT>
+__device__ __forceinline__ int popc_mask(MaskT m) {
+  return sizeof(MaskT) == 8 ? __popcll((unsigned long long)m) : __popc((unsigned)m);
+}
+template <typename MaskT>
+__device__ __forceinline__ int lowest_bit(MaskT m) {
+  return sizeof(MaskT) == 8 ? __ffsll((long long)m) - 1 : __ffs((int)m) - 1;
+}
+// Thread (e, g): expert e, sources g, g + groups, ...  Only the hosts of e inside this domain get a quota, so the
+// loop walks the set bits of (active hosts & this domain) -- zero or one bit for most pairs -- instead of testing
+// every rank of the domain.  The caches were cleared beforehand; erl[e, rank] is accumulated on the way.
+template <typename MaskT>
+__device__ void phase1_domain_impl(const SolverParams& p, Smem& s, int n, const unsigned long long* dom_mask, MaskT mine) {
+  const int R = p.R, E = p.E;
   const int tid = threadIdx.x, nt = blockDim.x;
-  const int n = collect_domain(p, s, d);
+  const unsigned long long* host = reinterpret_cast<const unsigned long long*>(s.prio);  // [E]
+  const int groups = nt / E > 0 ? (nt / E < R ? nt / E : R) : 1;
+  for (int idx = tid; idx < E * groups; idx += nt) {
+    const int g = idx / E, e = idx - g * E;
+    const MaskT h = (MaskT)host[e];
+    for (int src0 = g; src0 < R; src0 += 8 * groups) {
+      int need_b[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {  // the loads of up to eight sources are in flight together
+        const int src = src0 + j * groups;
+        need_b[j] = src < R ? __ldg(p.omega + (size_t)src * E + e) : 0;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int src = src0 + j * groups;
+        if (src >= R) break;
+        const int need = need_b[j];
+        if (need <= 0) continue;
+        const MaskT loc = h & (MaskT)dom_mask[src];
+        const MaskT act = loc ? loc : h;
+        MaskT todo = act & mine;
+        if (!todo) continue;
+        const int count = popc_mask<MaskT>(act);
+        // even split over the active hosts (u_min == 1): need / count each, the first need % count get one more
+        const int base = count == 1 ? need : need / count;
+        const int extra = need - base * count;
+        const size_t pair = (size_t)src * E + e;
+        while (todo) {
+          const int dst = lowest_bit<MaskT>(todo);
+          todo &= todo - (MaskT)1;
+          const int pos = popc_mask<MaskT>(act & (((MaskT)1 << dst) - (MaskT)1));
+          const int v = base + (pos < extra ? 1 : 0);
+          if (v != 0) {
+            const int li = s.local_idx[dst];
+            p.q[pair * R + dst] = v;
+            s.q_c[pair * n + li] = v;
+            atomicAdd(&s.erl_c[e * n + li], v);
+          }
+        }
+      }
+    }
+  }
+}
+
+// n_known: the size of domain d when s.dom_ranks / s.local_idx still describe it (left by phase 0), else -1.
+__device__ void phase1_domain(const SolverParams& p, Smem& s, int d, int n_known) {
+  __shared__ unsigned long long dom_mask[64];
+  const int R = p.R, E = p.E;
+  const int tid = threadIdx.x, nt = blockDim.x;
+  const int n = n_known >= 0 ? n_known : collect_domain(p, s, d);
   if (n == 0) return;
   unsigned long long* host = reinterpret_cast<unsigned long long*>(s.prio);  // [E]
-  for (int e = tid; e < E; e += nt) {
-    unsigned long long m = 0;
-    for (int dst = 0; dst < R; ++dst) m |= (unsigned long long)(p.x[(size_t)e * R + dst] != 0) << dst;
-    host[e] = m;
+  if ((R & 7) == 0) {
+    // a row of x is R bytes, 8-byte aligned: eight hosts per load
+    for (int e = tid; e < E; e += nt) {
+      unsigned long long m = 0;
+      const unsigned long long* row = reinterpret_cast<const unsigned long long*>(p.x + (size_t)e * R);
+      for (int w = 0; w < R / 8; ++w) {
+        const unsigned long long v = row[w];
+#pragma unroll
+        for (int b = 0; b < 8; ++b) m |= (unsigned long long)(((v >> (8 * b)) & 0xffull) != 0) << (8 * w + b);
+      }
+      host[e] = m;
+    }
+  } else {
+    for (int e = tid; e < E; e += nt) {
+      unsigned long long m = 0;
+      for (int dst = 0; dst < R; ++dst) m |= (unsigned long long)(p.x[(size_t)e * R + dst] != 0) << dst;
+      host[e] = m;
+    }
   }
   for (int r = tid; r < R; r += nt) {
     unsigned long long m = 0;
@@ -360,43 +475,25 @@ __device__ void phase1_domain(const SolverParams& p, Smem& s, int d) {
     for (int o = 0; o < R; ++o) m |= (unsigned long long)(p.dom[o] == dr) << o;
     dom_mask[r] = m;
   }
-  __syncthreads();
-  // the loads of the next pair are issued before the stores of the current one (the compiler cannot reorder them
-  // itself: q and omega might alias for all it knows)
-  int need_next = tid < R * E ? __ldg(p.omega + tid) : 0;
-  for (int pair = tid; pair < R * E; pair += nt) {
-    const int src = pair / E, e = pair - src * E;
-    const int need = need_next;
-    if (pair + nt < R * E) need_next = __ldg(p.omega + pair + nt);
-    const unsigned long long loc = host[e] & dom_mask[src];
-    const unsigned long long act = loc ? loc : host[e];
-    // the even split of even_share(), with its divisions done once per pair instead of once per destination
-    const int count = __popcll(act);
-    int takers = count;
-    if (u_min > 1 && need >= u_min) takers = min(count, need / u_min);
-    else if (need < u_min) takers = 1;
-    const bool any = need > 0 && count > 0;
-    const int base = any ? need / takers : 0, extra = any ? need - base * takers : 0;
-    int* qrow = p.q + (size_t)pair * R;
-    int* crow = s.q_c + (size_t)pair * n;
-    for (int i = 0; i < n; ++i) {
-      const int dst = s.dom_ranks[i];
-      int v = 0;
-      if (any && ((act >> dst) & 1ull)) {
-        const int pos = __popcll(act & ((1ull << dst) - 1ull));
-        if (pos < takers) v = base + (pos < extra ? 1 : 0);
-      }
-      qrow[dst] = v;
-      crow[i] = v;
+  // clear the caches while those loads are in flight (q_c and erl_c are contiguous ints; x_c is written below)
+  {
+    const int q_ints = R * E * n, e_ints = E * n;
+    for (int i = tid; i < e_ints; i += nt) s.erl_c[i] = 0;
+    if ((reinterpret_cast<uintptr_t>(s.q_c) & 15) == 0 && (q_ints & 3) == 0) {
+      uint4* qv = reinterpret_cast<uint4*>(s.q_c);
+      for (int i = tid; i < q_ints / 4; i += nt) qv[i] = make_uint4(0, 0, 0, 0);
+    } else {
+      for (int i = tid; i < q_ints; i += nt) s.q_c[i] = 0;
     }
   }
   __syncthreads();
+  const unsigned long long mine = dom_mask[s.dom_ranks[0]];  // the ranks of this domain
+  if (R <= 32) phase1_domain_impl<unsigned>(p, s, n, dom_mask, (unsigned)mine);
+  else phase1_domain_impl<unsigned long long>(p, s, n, dom_mask, mine);
+  __syncthreads();
   for (int cell = tid; cell < E * n; cell += nt) {
     const int e = cell / n, i = cell - e * n;
-    int acc = 0;
-    for (int src = 0; src < R; ++src) acc += s.q_c[((size_t)src * E + e) * n + i];
-    s.erl_c[cell] = acc;
-    p.erl[(size_t)e * R + s.dom_ranks[i]] = acc;
+    p.erl[(size_t)e * R + s.dom_ranks[i]] = s.erl_c[cell];
     s.x_c[cell] = (signed char)((host[e] >> s.dom_ranks[i]) & 1ull);
   }
   __syncthreads();
@@ -458,14 +555,13 @@ struct ProbeState {
 
 // prefilled: phase1_domain of this CTA has just left this domain's q / erl / x columns in the caches.
 __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, ProbeState probe, bool fresh,
-                              bool prefilled = false) {
-  __shared__ int busy_idx, busy_rank, busy_load, finished, sel_idx, apply_move;
+                              bool prefilled = false, int n_known = -1) {
+  __shared__ int busy_idx, busy_rank, busy_load, finished;
   __shared__ int best_theta, stagnant;
-  __shared__ Cand best_sh;
   const int tid = threadIdx.x, nt = blockDim.x;
   const int lane = tid & 31, warp = tid >> 5, nwarps = nt >> 5;
   const int R = p.R, E = p.E, u_min = p.u_min;
-  const int n = collect_domain(p, s, d);
+  const int n = n_known >= 0 ? n_known : collect_domain(p, s, d);
   if (n == 0) return;
   if (fresh) {
     // first repair pass after routing: this domain's rank loads are column sums of erl
@@ -494,6 +590,11 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
   // beyond the quota move itself.  Global copies are kept up to date for the later phases.
   const bool cached = p.cache_stage2 != 0;
   const bool qcached = p.cache_q != 0 && u_min == 1;  // the quota columns of this domain's ranks too
+  // link costs between the domain's ranks (small domains): the scan below reads one per candidate
+  int* cost_c = s.cost_c;
+  const bool cost_cached = n <= 8;
+  if (cost_cached && n_known < 0)  // (a CTA that kept its domain since phase 0 has them already)
+    for (int idx = tid; idx < n * n; idx += nt) cost_c[idx] = p.cost[(size_t)s.dom_ranks[idx / n] * R + s.dom_ranks[idx % n]];
   if (qcached && !prefilled) {
     for (int idx = tid; idx < R * E * n; idx += nt) {
       const int se = idx / n, i = idx - se * n;
@@ -545,18 +646,26 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
     }
   }
 
-  for (int it = 0; it < iters; ++it) {
-    if (tid == 0) {
-      int bi = -1, br = -1, bl = -1, theta = -1;
-      for (int i = 0; i < n; ++i) {
-        int l = s.load[i];
-        theta = max(theta, l);
-        if (s.stuck[i] == 0 && l > bl) {  // ascending rank order: first max wins ties
-          bi = i;
-          br = s.dom_ranks[i];
-          bl = l;
-        }
+  // One iteration = two block barriers.  All threads scan the candidates of the busiest rank; then warp 0 alone
+  // picks the best one, applies it (placement, quota move, loads) and selects the busiest rank of the NEXT
+  // iteration, while the other warps wait at the second barrier.
+  // Busiest rank that is not stuck (first one on ties) and the domain's max load, by all lanes of warp 0.
+  auto select_busy = [&](int it) {
+    int theta = -1, bl = -1, bi = INT_MAX;
+    for (int base = 0; base < n; base += kWarp) {
+      const int i = base + lane;
+      const int l = i < n ? s.load[i] : -1;
+      const int cl = (i < n && s.stuck[i] == 0) ? l : -1;
+      theta = max(theta, l);
+      if (cl > bl) {  // a lane sees its ranks in ascending order: the first maximum stays
+        bl = cl;
+        bi = i;
       }
+    }
+    theta = __reduce_max_sync(kFull, theta);
+    const int top = __reduce_max_sync(kFull, bl);
+    bi = __reduce_min_sync(kFull, (bl == top && top >= 0) ? bi : INT_MAX);
+    if (lane == 0) {
       bool stop = false;
       if (probe.on) {
         if (it == 0 || theta < best_theta) {
@@ -567,27 +676,41 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
         }
         stop = stagnant >= probe.patience;
       }
-      busy_idx = bi;
-      busy_rank = br;
-      busy_load = bl;
-      finished = stop || br < 0 || bl <= 0;
+      const bool none = bi == INT_MAX;
+      busy_idx = none ? -1 : bi;
+      busy_rank = none ? -1 : s.dom_ranks[bi];
+      busy_load = none ? -1 : top;
+      finished = stop || none || top <= 0;
     }
-    __syncthreads();
+  };
+  if (warp == 0) {
+    if (lane == 0) finished = 1;
+    __syncwarp(kFull);
+    if (iters > 0) select_busy(0);
+  }
+  __syncthreads();
+  // Candidates are (expert, target) pairs; tpe threads share an expert's targets so that a domain with few experts
+  // still spreads the scan over the whole block.  The mapping does not change between iterations.
+  const int tpe = nt / E > 1 ? (nt / E < n ? nt / E : n) : 1;
+  const int my_e = tid / tpe, my_sub = tid - my_e * tpe, e_step = nt / tpe;
+  int it = 0;
+  for (; it < iters; ++it) {
     if (finished) break;
-    const int src = busy_rank, top = busy_load;
+    const int src = busy_rank, top = busy_load, bidx = busy_idx;
 
     Cand mine = no_cand();
-    for (int e = tid; e < E; e += nt) {
-      const int avail = cached ? s.erl_c[e * n + busy_idx] : p.erl[(size_t)e * R + src];
+    for (int e = my_e; e < E; e += e_step) {
+      const int avail = cached ? s.erl_c[e * n + bidx] : p.erl[(size_t)e * R + src];
       if (avail <= 0) continue;
-      for (int ti = 0; ti < n; ++ti) {
-        const int t = s.dom_ranks[ti], tl = s.load[ti];
-        if (t == src || tl >= top) continue;
+      for (int ti = my_sub; ti < n; ti += tpe) {
+        const int tl = s.load[ti];
+        if (ti == bidx || tl >= top) continue;
+        const int t = s.dom_ranks[ti];
         const bool host = cached ? s.x_c[e * n + ti] != 0 : p.x[(size_t)e * R + t] != 0;
         if (!host && s.slot[ti] >= p.n_slot) continue;
         const int delta = min(avail, (top - tl) / 2);
         if (delta < u_min) continue;
-        Cand c{delta, tl, p.cost[(size_t)src * R + t], e, t};
+        Cand c{delta, tl, cost_cached ? cost_c[bidx * n + ti] : p.cost[(size_t)src * R + t], e, t};
         if (better(c, mine)) mine = c;
       }
     }
@@ -595,40 +718,31 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
     if (lane == 0) s.wcand[warp] = mine;
     __syncthreads();
     if (warp == 0) {
-      Cand c = lane < nwarps ? s.wcand[lane] : no_cand();
-      c = warp_best(c);
-      if (lane == 0) best_sh = c;
-    }
-    __syncthreads();
-    const Cand best = best_sh;
-
-    if (u_min == 1) {
-      if (tid == 0) {
-        sel_idx = best.delta > 0 ? s.local_idx[best.target] : -1;
-        apply_move = best.delta > 0 && sel_idx >= 0;
-        if (!apply_move) {
-          s.stuck[busy_idx] = 1;
+      Cand best = lane < nwarps ? s.wcand[lane] : no_cand();
+      best = warp_best(best);  // the same on every lane: they all take the same branches below
+      if (u_min == 1) {
+        const int sel = best.delta > 0 ? s.local_idx[best.target] : -1;
+        const bool apply = best.delta > 0 && sel >= 0;
+        if (!apply) {
+          if (lane == 0) s.stuck[bidx] = 1;
         } else {
-          signed char* cell = p.x + (size_t)best.expert * R + best.target;
-          const bool hosted = cached ? s.x_c[best.expert * n + sel_idx] != 0 : *cell != 0;
-          if (!hosted) {
-            *cell = 1;
-            if (cached) s.x_c[best.expert * n + sel_idx] = 1;
-            s.slot[sel_idx] += 1;
+          if (lane == 0) {
+            signed char* cell = p.x + (size_t)best.expert * R + best.target;
+            const bool hosted = cached ? s.x_c[best.expert * n + sel] != 0 : *cell != 0;
+            if (!hosted) {
+              *cell = 1;
+              if (cached) s.x_c[best.expert * n + sel] = 1;
+              s.slot[sel] += 1;
+            }
           }
-        }
-      }
-      __syncthreads();
-      if (apply_move) {
-        if (warp == 0) {
           // prefix over source ranks: source s gives min(q_s, max(delta - sum_{s'<s} q_s', 0))
           int carry = 0;
           for (int base = 0; base < R && carry < best.delta; base += kWarp) {
             const int sr = base + lane;
             int* from = p.q + ((size_t)sr * E + best.expert) * R + src;
             int* to = p.q + ((size_t)sr * E + best.expert) * R + best.target;
-            int* cfrom = qcached && sr < R ? s.q_c + ((size_t)sr * E + best.expert) * n + busy_idx : nullptr;
-            int* cto = qcached && sr < R ? s.q_c + ((size_t)sr * E + best.expert) * n + sel_idx : nullptr;
+            int* cfrom = qcached && sr < R ? s.q_c + ((size_t)sr * E + best.expert) * n + bidx : nullptr;
+            int* cto = qcached && sr < R ? s.q_c + ((size_t)sr * E + best.expert) * n + sel : nullptr;
             const int have = sr < R ? (cfrom ? *cfrom : *from) : 0;
             int incl = have;
             for (int off = 1; off < kWarp; off <<= 1) {
@@ -648,74 +762,78 @@ __device__ void stage2_domain(const SolverParams& p, Smem& s, int d, int iters, 
             }
             carry += __shfl_sync(kFull, incl, kWarp - 1);
           }
-        }
-        if (tid == 0) {
-          if (cached) {
-            const int a = (s.erl_c[best.expert * n + busy_idx] -= best.delta);
-            const int b = (s.erl_c[best.expert * n + sel_idx] += best.delta);
-            p.erl[(size_t)best.expert * R + src] = a;
-            p.erl[(size_t)best.expert * R + best.target] = b;
-          } else {
-            p.erl[(size_t)best.expert * R + src] -= best.delta;
-            p.erl[(size_t)best.expert * R + best.target] += best.delta;
+          if (lane == 0) {
+            if (cached) {
+              const int a = (s.erl_c[best.expert * n + bidx] -= best.delta);
+              const int b = (s.erl_c[best.expert * n + sel] += best.delta);
+              p.erl[(size_t)best.expert * R + src] = a;
+              p.erl[(size_t)best.expert * R + best.target] = b;
+            } else {
+              p.erl[(size_t)best.expert * R + src] -= best.delta;
+              p.erl[(size_t)best.expert * R + best.target] += best.delta;
+            }
+            s.load[bidx] -= best.delta;
+            s.load[sel] += best.delta;
+            for (int i = 0; i < n; ++i) s.stuck[i] = 0;
           }
-          s.load[busy_idx] -= best.delta;
-          s.load[sel_idx] += best.delta;
-          for (int i = 0; i < n; ++i) s.stuck[i] = 0;
         }
-      }
-    } else if (tid == 0) {
-      if (best.delta <= 0) {
-        s.stuck[busy_idx] = 1;
-      } else {
-        const int ti = s.local_idx[best.target];
-        auto qa = [&](int sr, int dst) { return p.q + ((size_t)sr * E + best.expert) * R + dst; };
-        auto dry = [&](int limit) {
-          int left = limit, tot = 0;
-          for (int sr = 0; sr < R; ++sr) {
-            int mv = safe_move(*qa(sr, src), *qa(sr, best.target), left, u_min);
-            left -= mv;
-            tot += mv;
-          }
-          return tot;
-        };
-        int limit = best.delta;
-        int actual = dry(limit);
-        if (actual < u_min) {
-          limit = top - best.load - 1;
-          actual = dry(limit);
-        }
-        if (actual < u_min) {
-          s.stuck[busy_idx] = 1;
+      } else if (lane == 0) {
+        if (best.delta <= 0) {
+          s.stuck[bidx] = 1;
         } else {
-          signed char* cell = p.x + (size_t)best.expert * R + best.target;
-          if (*cell == 0) {
-            *cell = 1;
-            if (cached) s.x_c[best.expert * n + ti] = 1;
-            s.slot[ti] += 1;
+          const int ti = s.local_idx[best.target];
+          auto qa = [&](int sr, int dst) { return p.q + ((size_t)sr * E + best.expert) * R + dst; };
+          auto dry = [&](int limit) {
+            int left = limit, tot = 0;
+            for (int sr = 0; sr < R; ++sr) {
+              int mv = safe_move(*qa(sr, src), *qa(sr, best.target), left, u_min);
+              left -= mv;
+              tot += mv;
+            }
+            return tot;
+          };
+          int limit = best.delta;
+          int actual = dry(limit);
+          if (actual < u_min) {
+            limit = top - best.load - 1;
+            actual = dry(limit);
           }
-          int left = limit;
-          for (int sr = 0; sr < R; ++sr) {
-            int have = *qa(sr, src), there = *qa(sr, best.target);
-            int mv = safe_move(have, there, left, u_min);
-            *qa(sr, src) = have - mv;
-            *qa(sr, best.target) = there + mv;
-            left -= mv;
+          if (actual < u_min) {
+            s.stuck[bidx] = 1;
+          } else {
+            signed char* cell = p.x + (size_t)best.expert * R + best.target;
+            if (*cell == 0) {
+              *cell = 1;
+              if (cached) s.x_c[best.expert * n + ti] = 1;
+              s.slot[ti] += 1;
+            }
+            int left = limit;
+            for (int sr = 0; sr < R; ++sr) {
+              int have = *qa(sr, src), there = *qa(sr, best.target);
+              int mv = safe_move(have, there, left, u_min);
+              *qa(sr, src) = have - mv;
+              *qa(sr, best.target) = there + mv;
+              left -= mv;
+            }
+            p.erl[(size_t)best.expert * R + src] -= actual;
+            p.erl[(size_t)best.expert * R + best.target] += actual;
+            if (cached) {
+              s.erl_c[best.expert * n + bidx] -= actual;
+              s.erl_c[best.expert * n + ti] += actual;
+            }
+            s.load[bidx] -= actual;
+            s.load[ti] += actual;
+            for (int i = 0; i < n; ++i) s.stuck[i] = 0;
           }
-          p.erl[(size_t)best.expert * R + src] -= actual;
-          p.erl[(size_t)best.expert * R + best.target] += actual;
-          if (cached) {
-            s.erl_c[best.expert * n + busy_idx] -= actual;
-            s.erl_c[best.expert * n + ti] += actual;
-          }
-          s.load[busy_idx] -= actual;
-          s.load[ti] += actual;
-          for (int i = 0; i < n; ++i) s.stuck[i] = 0;
         }
       }
+      __syncwarp(kFull);
+      if (it + 1 < iters) select_busy(it + 1);
+      else if (lane == 0) finished = 1;
     }
     __syncthreads();
   }
+  if (p.trace != nullptr && blockIdx.x == 0 && tid == 0) p.trace[7] = it;  // repair iterations of the first domain
 
   for (int i = tid; i < n; i += nt) {
     int r = s.dom_ranks[i];
@@ -860,13 +978,31 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
 
   bool ok = true;
   trace_mark(p, 1);
-  for (int d = blockIdx.x; d < p.D; d += gridDim.x) phase0_domain(p, s, d);
-  trace_mark(p, 2);
-  ok = ok && grid_barrier(p, 11);
-  trace_mark(p, 3);
   // Fast path (every domain has its own CTA, <= 64 ranks, quota cache fits, plain quota floor): each CTA routes
   // exactly its own domain's columns into its caches and goes on repairing them, with no grid barrier between.
   const bool own_columns = p.cache_q && p.u_min == 1 && p.R <= 64 && (int)gridDim.x >= p.D && !p.probe;
+  // With several CTAs on the fast path each one folds its domain's max load into theta with an atomic max (no CTA
+  // has to wait for the others' loads at the end); the start value is written ahead of the barrier below.
+  const bool theta_by_atomics = own_columns && gridDim.x > 1;
+  if (theta_by_atomics && blockIdx.x == 0 && threadIdx.x == 0) p.theta[0] = -1;
+  if (own_columns) {
+    // Most quotas are zero (an expert has a handful of hosts).  The grid clears q here with full-width stores, ahead
+    // of the barrier that phase 1 waits on anyway, and phase 1 then stores only the non-zero quotas: a few
+    // thousand scattered 4-byte stores per CTA instead of R * E * n of them, which was what phase 1 spent its time on.
+    const size_t total = (size_t)p.R * p.E * p.R;
+    const size_t vecs = (reinterpret_cast<uintptr_t>(p.q) & 15) == 0 ? total / 4 : 0;  // unaligned caller buffer: scalar stores
+    uint4* qv = reinterpret_cast<uint4*>(p.q);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vecs; i += (size_t)gridDim.x * blockDim.x)
+      qv[i] = make_uint4(0, 0, 0, 0);
+    for (size_t i = vecs * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+      p.q[i] = 0;
+  }
+  int n_mine = -1;  // fast path: the size of this CTA's own domain, collected once
+  for (int d = blockIdx.x; d < p.D; d += gridDim.x) n_mine = phase0_domain(p, s, d);
+  if (!own_columns) n_mine = -1;
+  trace_mark(p, 2);
+  ok = ok && grid_barrier(p, 11);
+  trace_mark(p, 3);
   if (ok && !own_columns) {
     if (p.R <= 64) phase1_routing_masks(p, s);
     else phase1_routing(p);
@@ -876,9 +1012,14 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
   if (ok) {
     if (own_columns) {
       if ((int)blockIdx.x < p.D) {
-        phase1_domain(p, s, blockIdx.x);
+        phase1_domain(p, s, blockIdx.x, n_mine);
         trace_mark(p, 4);
-        stage2_domain(p, s, blockIdx.x, p.iters, ProbeState{false, 0}, true, true);
+        stage2_domain(p, s, blockIdx.x, p.iters, ProbeState{false, 0}, true, true, n_mine);
+        if (theta_by_atomics && threadIdx.x == 0) {
+          int top = -1;
+          for (int i = 0; i < n_mine; ++i) top = max(top, s.load[i]);
+          atomicMax(reinterpret_cast<long long*>(p.theta), (long long)top);
+        }
         trace_mark(p, 5);
       }
     } else if (!p.probe) {
@@ -931,7 +1072,7 @@ __global__ void __launch_bounds__(1024) solver_kernel(SolverParams p, RankTables
   __syncthreads();
   if (!last_out) return;
   if (ok && (gridDim.x == 1 || *reinterpret_cast<volatile int*>(p.status) == 0)) {
-    if (threadIdx.x < kWarp) {
+    if (!theta_by_atomics && threadIdx.x < kWarp) {
       const int th = global_theta_warp(p);
       if (threadIdx.x == 0) p.theta[0] = th;
     }
@@ -951,7 +1092,7 @@ __global__ void __launch_bounds__(1024) tables_kernel(SolverParams p, RankTables
 
 size_t solver_base_smem(int R, int E) {
   const size_t P = (size_t)(pow2_at_least(E) < 32 ? 32 : pow2_at_least(E));
-  return sizeof(long long) * P + sizeof(int) * P + sizeof(int) * 5 * R + sizeof(Cand) * 32 + 64;
+  return sizeof(long long) * P + sizeof(int) * P + sizeof(int) * 5 * R + sizeof(Cand) * 32 + sizeof(int) * 64 + 64;
 }
 size_t solver_cache_smem(int R, int E) { return (((size_t)E * R * 5 + 15) / 16) * 16; }  // erl (int) + x (byte) per (e, rank)
 size_t solver_qcache_smem(int R, int E) { return (size_t)R * E * R * 4; }
