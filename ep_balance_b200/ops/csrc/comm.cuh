@@ -3,11 +3,11 @@
 // (grouped_gemm.cu).
 //
 // Copy engine: every warp owns a small ring of shared-memory slots.  A row (or weight chunk) moves in
-// segments: one lane issues a bulk async load (global -> shared, completion on the slot's mbarrier) and,
-// once a segment has landed, a bulk async store (shared -> global, possibly a peer's memory).  Several
-// segments per warp are in flight with no register traffic, so two warps beside a running GEMM keep
-// enough bytes outstanding to cover memory and NVLink latency.  No load names a cluster multicast;
-// sources and destinations may be another GPU's memory.
+// segments: a lane issues a bulk async load (global -> shared, completion on the slot's mbarrier) and,
+// once the segment has landed, a bulk async store (shared -> global, possibly a peer's memory); several
+// lanes do so side by side, each for its own segment.  The segments in flight cost no register traffic, so
+// two warps beside a running GEMM keep enough bytes outstanding to cover memory and NVLink latency.  No
+// load names a cluster multicast; sources and destinations may be another GPU's memory.
 //
 // Nothing here waits on another CTA or rank, so a warp running it always makes progress; only the
 // consumers of its signals wait, and those waits are bounded.  The waits on the warp's own copies are
@@ -22,17 +22,12 @@
 namespace epb {
 
 constexpr int kCommSlotBytes = 4096;   // one segment
-constexpr int kCommCtrlBytes = 192;    // per warp: up to 8 mbarriers + 8 slot records
+constexpr int kCommCtrlBytes = 192;    // per warp: up to 8 mbarriers
 // Shared memory of one transport warp with a ring of kSlots segments (kSlots / 2 loads in flight).
 template <int kSlots>
 constexpr int comm_warp_bytes() { return kSlots * kCommSlotBytes + kCommCtrlBytes; }
 
-struct CommSlot {
-  void* dst;       // where the segment goes
-  int bytes;
-  int pad;
-};
-static_assert(8 * 8 + 8 * sizeof(CommSlot) <= kCommCtrlBytes, "per-warp control block too small");
+static_assert(8 * 8 <= kCommCtrlBytes, "per-warp control block too small");
 
 __device__ __forceinline__ void red_release_gpu_add(unsigned* p, unsigned v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -60,29 +55,31 @@ __device__ __forceinline__ void comm_bulk_load(void* smem_dst, const void* gsrc,
                ::"r"(comm_smem(smem_dst)), "l"(gsrc), "r"(bytes), "r"(comm_smem(bar))
                : "memory");
 }
-__device__ __forceinline__ void comm_bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
-               ::"l"(gdst), "r"(comm_smem(smem_src)), "r"(bytes)
-               : "memory");
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
 
 // The per-warp copy pipeline.  `smem` is the warp's private region: kSlots segments of ring (16-byte
 // aligned) followed by kCommCtrlBytes of control data.  All 32 lanes call every member together.
+//
+// The ring is two halves of kBatch = kSlots / 2 segments.  A push moves one BATCH: lane l < kBatch gives its own
+// segment (source, destination, bytes) and issues its own bulk load into slot l of the current half, then the
+// lanes complete the previous batch (each waits on its slot's mbarrier and issues its own bulk store).  So one
+// instruction issues kBatch copies -- the issuing lanes' instruction latency (mbarrier operations, bulk-copy
+// issue), not the copy engine, was what bounded a warp that moved one segment per instruction -- and the loads
+// of a batch are in flight while the previous batch is stored.  Bulk groups are per thread: every lane commits
+// one group per batch (an empty one when it had nothing to store), so "all but the newest group have been
+// read" means for each lane that its slot in the half it is about to reuse is free.
 template <int kCommSlots>
 struct CommPipe {
   static_assert(kCommSlots >= 4 && kCommSlots <= 8 && kCommSlots % 2 == 0, "ring of 4, 6 or 8 slots");
   static constexpr int kCommWarpBytes = kCommSlots * kCommSlotBytes;
-  // Half of the ring holds loads in flight; the other half holds segments whose stores may still be reading
-  // them.  The copy engine of an SM serves requests in order, behind the GEMM's own tile loads, so a store
-  // starts reading its segment a while after it was issued: the issuing lane must not wait for the newest ones.
-  static constexpr int kLoads = kCommSlots / 2;
-  static constexpr int kStoresPending = kCommSlots - kLoads - 1;
-  static constexpr int kSeg = kCommSlotBytes;  // bytes of one segment
+  static constexpr int kBatch = kCommSlots / 2;  // segments per push; lanes [0, kBatch) own one each
+  static constexpr int kSeg = kCommSlotBytes;    // bytes of one segment
   uint8_t* ring;
   uint64_t* bars;
-  CommSlot* slots;
-  unsigned pushed, popped;
+  unsigned batches;        // batches pushed
+  unsigned uses[2];        // this lane's loads issued into its slot of half 0 / 1 (mbarrier phase)
+  void* pend_dst;          // this lane's segment of the batch whose loads are in flight
+  int pend_bytes, pend_slot;
+  uint32_t pend_parity;
   int lane;
   bool failed;
   int* status;
@@ -95,8 +92,12 @@ struct CommPipe {
     t_load = t_read = t_drain = n_seg = 0ull;
     ring = smem;
     bars = reinterpret_cast<uint64_t*>(smem + kCommWarpBytes);
-    slots = reinterpret_cast<CommSlot*>(bars + kCommSlots);
-    pushed = popped = 0u;
+    batches = 0u;
+    uses[0] = uses[1] = 0u;
+    pend_dst = nullptr;
+    pend_bytes = 0;
+    pend_slot = 0;
+    pend_parity = 0u;
     lane = threadIdx.x & 31;
     failed = false;
     status = status_word;
@@ -108,74 +109,80 @@ struct CommPipe {
     __syncwarp();
   }
 
-  // Oldest segment in flight: wait for its load, store it.
-  __device__ __forceinline__ void pop() {
-    const int s = (int)(popped % kCommSlots);
-    const uint32_t parity = (popped / kCommSlots) & 1u;
+  // Complete the batch in flight: every lane waits for its own load and stores its segment.
+  __device__ __forceinline__ void flush() {
     const unsigned long long p0 = prof ? globaltimer_ns() : 0ull;
     if (!failed) {
+      bool ok = pend_bytes == 0;
       unsigned long long t0 = 0;
-      for (unsigned spin = 0; !comm_bar_try(&bars[s], parity); ++spin) {
+      for (unsigned spin = 0;; ++spin) {
+        if (!ok) ok = comm_bar_try(&bars[pend_slot], pend_parity);
+        if (__all_sync(0xffffffffu, ok)) break;
         if ((spin & 1023u) == 1023u) {
           unsigned long long now = globaltimer_ns();
           if (t0 == 0) t0 = now;
-          else if (now - t0 > kWaitBudgetNs) {
-            failed = true;
-            break;
-          }
+          else if (now - t0 > kWaitBudgetNs) failed = true;
+        }
+        if (__any_sync(0xffffffffu, failed)) {
+          failed = true;
+          break;
         }
       }
-      failed = __any_sync(0xffffffffu, failed);
       if (failed && lane == 0) set_status(status, kStatusPipeTimeout, 8, (int)blockIdx.x);
     }
     if (prof) t_load += globaltimer_ns() - p0;
-    const CommSlot rec = slots[s];
-    uint8_t* seg = ring + (size_t)s * kCommSlotBytes;
-    __syncwarp();
-    if (lane == 0 && !failed) {
-      const unsigned long long p3 = prof ? globaltimer_ns() : 0ull;
-      comm_bulk_store(rec.dst, seg, (uint32_t)rec.bytes);
-      if (prof) t_read += globaltimer_ns() - p3;
+    if (lane < kBatch && batches > 0u) {
+      if (pend_bytes > 0 && !failed) {
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                     ::"l"(pend_dst), "r"(comm_smem(ring + (size_t)pend_slot * kCommSlotBytes)), "r"((uint32_t)pend_bytes)
+                     : "memory");
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");  // one group per lane and batch, possibly empty
     }
-    ++popped;
+    pend_bytes = 0;
+    __syncwarp();
   }
 
-  // Start moving `bytes` (<= kSeg, multiple of 16) from `src` to `dst`.
+  // Start moving one batch: lane l < kBatch moves `bytes` (<= kSeg, multiple of 16; 0: nothing) from `src` to `dst`.
+  // The arguments of the other lanes are ignored.
   __device__ __forceinline__ void push(const void* src, void* dst, int bytes) {
-    if (pushed - popped >= (unsigned)kLoads) pop();
-    const int s = (int)(pushed % kCommSlots);
-    if (lane == 0 && !failed) {
-      // slot s was stored at least kCommSlots - kLoads pops ago: all but the kStoresPending newest stores must have
-      // finished reading their segments
+    const int h = (int)(batches & 1u);
+    const int s = h * kBatch + lane;
+    if (lane >= kBatch) bytes = 0;
+    if (lane < kBatch && !failed) {
+      // this lane's slot of half h was last read by the store of two batches ago, which is the newest group it has
+      // committed (the previous batch's store is issued by the flush below)
       const unsigned long long p1 = prof ? globaltimer_ns() : 0ull;
-      asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kStoresPending) : "memory");
-      if (prof) {
-        t_read += globaltimer_ns() - p1;
-        ++n_seg;
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      if (bytes > 0) {
+        comm_bar_expect(&bars[s], (uint32_t)bytes);
+        comm_bulk_load(ring + (size_t)s * kCommSlotBytes, src, (uint32_t)bytes, &bars[s]);
       }
-      slots[s] = CommSlot{dst, bytes, 0};
-      uint8_t* seg = ring + (size_t)s * kCommSlotBytes;
-      const unsigned long long p4 = prof ? globaltimer_ns() : 0ull;
-      comm_bar_expect(&bars[s], (uint32_t)bytes);
-      comm_bulk_load(seg, src, (uint32_t)bytes, &bars[s]);
-      if (prof) t_read += globaltimer_ns() - p4;
+      if (prof) t_read += globaltimer_ns() - p1;
     }
     __syncwarp();
-    ++pushed;
+    if (prof) n_seg += (unsigned long long)__popc(__ballot_sync(0xffffffffu, bytes > 0));
+    flush();  // the previous batch: its loads have been in flight for one batch
+    pend_dst = dst;
+    pend_bytes = bytes;
+    pend_slot = s;
+    pend_parity = uses[h] & 1u;
+    if (bytes > 0) ++uses[h];
+    ++batches;
   }
 
   // Finish everything in flight; on return the stores are complete and fenced for a following release.
   __device__ __forceinline__ void drain() {
     const unsigned long long p2 = prof ? globaltimer_ns() : 0ull;
-    while (popped != pushed) pop();
-    if (lane == 0) {
+    flush();
+    if (lane < kBatch) {
       asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
       asm volatile("fence.proxy.async;" ::: "memory");
     }
     __syncwarp();
     if (prof) t_drain += globaltimer_ns() - p2;
   }
-  // add this warp's counters to prof[0..3] = {load waits, read waits, drains (incl. their load waits), segments}
+  // add this warp's counters to prof[0..3] = {load waits, read waits, drains (incl. their load waits), batches x lanes}
   __device__ __forceinline__ void report() {
     if (prof != nullptr && lane == 0) {
       atomicAdd(prof, t_load);
@@ -193,17 +200,24 @@ template <int kSlots>
 __device__ __forceinline__ void comm_send_rows(const CommArgs& a, CommPipe<kSlots>& pipe, int my_u, int my_pos, int nrow, int row0,
                                                uint8_t* dbuf, int2* dmeta, float* drowp, int lane) {
   constexpr unsigned kAll = 0xffffffffu;
-  constexpr int kSeg = CommPipe<kSlots>::kSeg;
+  constexpr int kSeg = CommPipe<kSlots>::kSeg, kBatch = CommPipe<kSlots>::kBatch;
   const int row_bytes = a.H * 2;
   if (lane < nrow) {
     if (dmeta != nullptr) dmeta[row0 + lane] = make_int2(a.me, my_pos);
     if (drowp != nullptr) drowp[row0 + lane] = a.unit_prob[my_u];
   }
-  for (int i = 0; i < nrow; ++i) {
-    const int u = __shfl_sync(kAll, my_u, i);
-    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.rows) + (size_t)(u / a.topk) * row_bytes;
-    uint8_t* dst = dbuf + (size_t)(row0 + i) * row_bytes;
-    for (int off = 0; off < row_bytes; off += kSeg) pipe.push(src + off, dst + off, min(kSeg, row_bytes - off));
+  // (row, segment) pairs in order, kBatch of them per push: lane l takes pair first + l
+  const int segs = (row_bytes + kSeg - 1) / kSeg;
+  const int total = nrow * segs;
+  for (int first = 0; first < total; first += kBatch) {
+    const int idx = first + (lane < kBatch ? lane : 0);
+    const int i = idx / segs, sg = idx - i * segs;
+    const int u = __shfl_sync(kAll, my_u, i < nrow ? i : 0);
+    const bool have = lane < kBatch && idx < total;
+    const int off = sg * kSeg;
+    const uint8_t* src = reinterpret_cast<const uint8_t*>(a.rows) + (size_t)(u / a.topk) * row_bytes + off;
+    uint8_t* dst = dbuf + (size_t)(row0 + i) * row_bytes + off;
+    pipe.push(src, dst, have ? min(kSeg, row_bytes - off) : 0);
   }
 }
 
@@ -237,7 +251,11 @@ __device__ inline void comm_pull(const CommArgs& a, CommPipe<kSlots>& pipe, int 
         const int n = (int)(slot_bytes - first < (size_t)kPullChunkBytes ? slot_bytes - first : (size_t)kPullChunkBytes);
         const uint8_t* src = reinterpret_cast<const uint8_t*>(ptrs[a.main_rank[e]]) + (size_t)a.home_index[e] * slot_bytes + first;
         uint8_t* dst = reinterpret_cast<uint8_t*>(ptrs[a.me]) + (size_t)(a.home_cap + s) * slot_bytes + first;
-        for (int off = 0; off < n; off += kSeg) pipe.push(src + off, dst + off, min(kSeg, n - off));
+        constexpr int kBatch = CommPipe<kSlots>::kBatch;
+        for (int off0 = 0; off0 < n; off0 += kSeg * kBatch) {
+          const int off = off0 + (lane < kBatch ? lane : 0) * kSeg;
+          pipe.push(src + off, dst + off, off < n ? min(kSeg, n - off) : 0);
+        }
         pipe.drain();
       }
       __threadfence();
