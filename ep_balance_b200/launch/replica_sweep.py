@@ -14,8 +14,9 @@ is drawn, the plan is solved on the device, and the product's own kernels are ti
 * ``return``     gradient return: every owner adds its replicas' gradient slots with peer loads
                  -- ``MoeRuntime.reduce_weight_grads``.
 
-GB/s = bytes that cross NVLink into the busiest rank / time; the figure to compare with is the peer-copy
-bandwidth of one GPU and direction.  Plan quality (rank load max/mean) is printed beside DeepSeek-EPLB's
+GB/s = bytes that cross the busiest NVLink port / time: for the pull that is the larger of what one host receives
+and what one owner sends (a hot expert's owner serves all its replicas at once), for the return what one owner
+receives; the figure to compare with is the peer-copy bandwidth of one GPU and direction.  Plan quality (rank load max/mean) is printed beside DeepSeek-EPLB's
 on the same load matrix; the reference's CUDA solver returns bit-identical plans
 (``tests/test_gpu_solver_vs_reference.py``), so its max/mean equals ours.
 Reference sweep definition: scripts/run_slot_sweep.sh, scripts/run_solver_scaling.sh.
@@ -111,7 +112,8 @@ def main(argv=None) -> int:
             if slots > 0:
                 row["pull_ms"] = _timed(rt.pull_weights, a.iters, dev)
                 row["return_ms"] = _timed(rt.reduce_weight_grads, a.iters, dev)
-                row["pull_gbs"] = int(worst[0]) * per_expert / row["pull_ms"] / 1e6 if worst[0] else 0.0
+                busiest = max(int(worst[0]), int(worst[1]))
+                row["pull_gbs"] = busiest * per_expert / row["pull_ms"] / 1e6 if busiest else 0.0
                 row["return_gbs"] = int(worst[1]) * per_expert / row["return_ms"] / 1e6 if worst[1] else 0.0
             torch.cuda.synchronize()
             layer.check_status()

@@ -312,33 +312,59 @@ __global__ void __launch_bounds__(512) grad_reduce_kernel(GradReduceArgs a) {
   const size_t n_vec = a.elems_per_slot / 8;
   uint4* mine = reinterpret_cast<uint4*>(a.g_ptrs[a.me]) + (size_t)home * n_vec;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (!a.include_self) add8(acc, mine[i]);
+  // Four vectors per thread and pass, with the peer loads of all four issued before the first is consumed: an
+  // expert with one or two replicas is served by this home slot's CTAs only, and what bounds them is the number of
+  // bytes they keep in flight across NVLink, not the link.
+  constexpr int kUnroll = 4;
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < n_vec; i0 += stride * kUnroll) {
+    float acc[kUnroll][8];
+    uint4 own[kUnroll];
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t i = i0 + (size_t)j * stride;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) acc[j][c] = 0.f;
+      own[j] = (!a.include_self && i < n_vec) ? mine[i] : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j)
+      if (!a.include_self) add8(acc[j], own[j]);  // the owner's own gradient first, then the hosts in rank order
     for (int k = 0; k < n; ++k) {
       const uint4* peer = reinterpret_cast<const uint4*>(a.g_ptrs[host_rank[k]]) + (size_t)host_slot[k] * n_vec;
-      add8(acc, peer[i]);
-    }
-    if (accumulate && a.accum_fp32) {
-      float4* dst = reinterpret_cast<float4*>(a.accum) + ((size_t)home * n_vec + i) * 2;
-      float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
-      if (!a.overwrite) {
-        lo = dst[0];
-        hi = dst[1];
-      }
-      lo.x += acc[0]; lo.y += acc[1]; lo.z += acc[2]; lo.w += acc[3];
-      hi.x += acc[4]; hi.y += acc[5]; hi.z += acc[6]; hi.w += acc[7];
-      dst[0] = lo;
-      dst[1] = hi;
-      continue;
-    }
-    uint4* out = accumulate ? reinterpret_cast<uint4*>(a.accum) + (size_t)home * n_vec + i : mine + i;
-    if (accumulate && !a.overwrite) add8(acc, *out);
-    uint4 o;
-    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+      uint4 v[kUnroll];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    *out = o;
+      for (int j = 0; j < kUnroll; ++j) {
+        const size_t i = i0 + (size_t)j * stride;
+        v[j] = i < n_vec ? peer[i] : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < kUnroll; ++j) add8(acc[j], v[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < kUnroll; ++j) {
+      const size_t i = i0 + (size_t)j * stride;
+      if (i >= n_vec) break;
+      if (accumulate && a.accum_fp32) {
+        float4* dst = reinterpret_cast<float4*>(a.accum) + ((size_t)home * n_vec + i) * 2;
+        float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+        if (!a.overwrite) {
+          lo = dst[0];
+          hi = dst[1];
+        }
+        lo.x += acc[j][0]; lo.y += acc[j][1]; lo.z += acc[j][2]; lo.w += acc[j][3];
+        hi.x += acc[j][4]; hi.y += acc[j][5]; hi.z += acc[j][6]; hi.w += acc[j][7];
+        dst[0] = lo;
+        dst[1] = hi;
+        continue;
+      }
+      uint4* out = accumulate ? reinterpret_cast<uint4*>(a.accum) + (size_t)home * n_vec + i : mine + i;
+      if (accumulate && !a.overwrite) add8(acc[j], *out);
+      uint4 o;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) po[c] = __floats2bfloat162_rn(acc[j][2 * c], acc[j][2 * c + 1]);
+      *out = o;
+    }
   }
 }
 
@@ -464,8 +490,9 @@ cudaError_t launch_weight_pull(const WeightPullArgs& a, cudaStream_t stream) {
 cudaError_t launch_grad_reduce(const GradReduceArgs& a, cudaStream_t stream) {
   if (a.home_cap <= 0) return cudaSuccess;
   if (a.elems_per_slot % 8 != 0 || a.R > kMaxGradHosts) return cudaErrorInvalidValue;
-  int gx = (2 * sm_count() + a.home_cap - 1) / a.home_cap;  // about two waves of CTAs in total
-  if (gx < 64) gx = 64;
+  // Which home slots have replicas is known on the device only.  Every slot gets a full machine's worth of CTAs: the
+  // CTAs of slots without replicas leave at once, those of a replicated expert keep every SM loading.
+  int gx = sm_count();
   if (gx > 256) gx = 256;
   dim3 grid(gx, a.home_cap);
   grad_reduce_kernel<<<grid, 512, 0, stream>>>(a);
