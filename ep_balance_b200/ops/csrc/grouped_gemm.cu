@@ -2,10 +2,12 @@
 // accumulators in tensor memory, epilogue warps reading them back with tcgen05.ld.
 //
 // CTA = 10 warps: warp 0 issues TMA loads, warp 1 owns TMEM and issues MMAs, warps 2-9 run the
-// epilogue (two warps per 32-lane quarter of TMEM, each taking half of the tile's columns).  A 4-stage smem ring (A 16 KB + B 32 KB per
-// stage) feeds 128x256x16 UMMAs; two 256-column accumulators in TMEM let the epilogue of tile i
-// overlap the main loop of tile i+1.  The kernel is persistent: CTA c processes tiles
-// c, c+grid, ... of a tile list derived on device from the plan's group table.
+// epilogue (two warps per 32-lane quarter of TMEM, each taking half of the tile's columns).  A 4- to 6-stage
+// smem ring (A 16 KB + B 32 or 16 KB per stage, see Geometry) feeds 128x256x16 UMMAs; two 256-column accumulators
+// in TMEM let the epilogue of tile i overlap the main loop of tile i+1.  The kernel is persistent: CTA c processes
+// tiles c, c+grid, ... of a tile list derived on device from the plan's group table.  The variants with kComm = 1
+// carry two more warps that move token (or gradient) rows and replica weights between ranks (comm.cuh) while the
+// producer warp gates each tile's first load on the arrival counter of that tile.
 //
 // This replaces torch._grouped_mm / torch.bmm plus the unfused activation, slot sort, index_add
 // and activation-gradient kernels of the reference (eplb/integration/grouped_mlp.py:88-137,
@@ -35,7 +37,7 @@ constexpr int TMEM_COLS = 512;
 template <int kCtas, int kComm = 0>
 struct Geometry {
   static constexpr int STAGES = (kCtas == 2 ? 6 : 4) - (kComm ? (kCtas == 2 ? 2 : 1) : 0);
-  static constexpr int COMM_SLOTS = kCtas == 2 ? 8 : 6;  // ring slots of a transport warp: 4 (3) loads of 4 KB in flight
+  static constexpr int COMM_SLOTS = kCtas == 2 ? 8 : 6;  // ring slots of a transport warp: batches of 4 (3) segments of 4 KB
   static constexpr int B_BYTES = BN * BK * 2 / kCtas;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TILE_M = BM * kCtas;
