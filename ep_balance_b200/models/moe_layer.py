@@ -209,6 +209,11 @@ class _FusedMoEFunction(torch.autograd.Function):
         n = tokens.shape[0]
         out = torch.empty_like(tokens)
         layer.rt.forward(tokens.data_ptr(), topk_idx.data_ptr(), topk_prob.data_ptr(), out.data_ptr(), n)
+        # Backward reads what this forward left in the layer's buffers (received rows, pre-activations, routing
+        # tables): one forward, then its backward.  A second forward in between would silently replace them, so
+        # the forward is numbered and backward checks the number.
+        layer._forward_generation += 1
+        ctx.generation = layer._forward_generation
         ctx.layer = layer
         ctx.save_for_backward(topk_prob)
         ctx.n = n
@@ -218,6 +223,11 @@ class _FusedMoEFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         layer = ctx.layer
+        if ctx.generation != layer._forward_generation:
+            raise RuntimeError("FusedMoE.backward: the layer ran another forward (generation "
+                               f"{layer._forward_generation}) after the one this backward belongs to ({ctx.generation}); "
+                               "its saved activations live in the layer's buffers, so every forward must be followed "
+                               "by its backward before the next forward with autograd enabled")
         (topk_prob,) = ctx.saved_tensors
         dout = dout.contiguous()
         dtokens = torch.empty_like(dout)
@@ -245,6 +255,7 @@ class FusedMoE(nn.Module):
         super().__init__()
         self.cfg, self.heap, self.rank, self.world = cfg, heap, int(rank), int(world)
         self.layer_index = layer_index
+        self._forward_generation = 0   # forwards that went through autograd (see _FusedMoEFunction)
         sym = lambda name: region_name(name, layer_index)  # noqa: E731
         self.solver_cfg = solver_cfg or EPLBConfig()
         dev = heap.device

@@ -305,3 +305,23 @@ def test_capacity_overflow_is_detected_and_contained():
     torch.cuda.synchronize()
     cl.status.check_now()
     assert any(not torch.equal(p.detach(), b) for p, b in zip(params, before))
+
+
+def test_backward_after_another_forward_is_refused():
+    """Backward reads the layer's buffers: a second autograd forward in between must raise, not corrupt gradients."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+
+    torch.manual_seed(0)
+    cfg = MoEConfig(hidden=256, ffn=384, num_experts=8, top_k=2, max_tokens=256)
+    layer = EmulatedCluster(cfg, world=1).layers[0]
+    a = torch.randn(256, 256, device="cuda").bfloat16().requires_grad_(True)
+    b = torch.randn(256, 256, device="cuda").bfloat16().requires_grad_(True)
+    out_a = layer(a)
+    out_b = layer(b)                      # replaces what out_a's backward would read
+    with pytest.raises(RuntimeError, match="another forward"):
+        out_a.sum().backward()
+    out_b.sum().backward()                # the latest forward's backward is fine
+    torch.cuda.synchronize()
+    layer.check_status()
+    assert b.grad is not None and torch.isfinite(b.grad.float()).all()
