@@ -233,7 +233,7 @@ def run_ours(args):
     # enqueue ahead of the GPU (with device-side cross-rank barriers in every step, a host that waits for
     # its own GPU each step stalls every other rank too).  The losses still outstanding at the end are
     # read before the closing event of the timed loop.
-    DEPTH, LAG = 3, 2
+    DEPTH, LAG = 6, 4   # DEPTH >= LAG + 2: a staging slot is long consumed when its next copy is enqueued
     copy_stream = torch.cuda.Stream(device=dev)
     staging = [torch.empty_like(dev_batches[0]) for _ in range(DEPTH)]
     ready = [torch.cuda.Event() for _ in range(DEPTH)]
@@ -382,8 +382,8 @@ def run_ours(args):
                "replicas": int(plan.x.sum()) - CFG["num_experts"], "plan_digest": plan.digest()[:16]}
     notes = {"gemm_ctas": args.gemm_ctas, "fused_transport": bool(layer.rt_config["fused_comm"]),
              "e2e_step": e2e_mode, "device_step": e2e_mode, "timed_order": "end-to-end loop first, device-only loop second",
-             "e2e_loop": "input H2D prefetched on a side stream (ring of 3 staging buffers); loss D2H copied "
-                         "asynchronously and read by the host two steps later, the outstanding ones before the closing event",
+             "e2e_loop": "input H2D prefetched on a side stream (ring of 6 staging buffers); loss D2H copied "
+                         "asynchronously and read by the host four steps later, the outstanding ones before the closing event",
              "kernels": "tcgen05 grouped GEMM with transport warps (dispatch + replica pull inside GEMM1, gradient dispatch "
                         "inside Dgrad2), per-tile arrival counters, device solver, peer-load grad return, fused AdamW"}
     if rank == 0:
