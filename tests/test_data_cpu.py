@@ -38,3 +38,24 @@ def test_prepare_and_read_back(tmp_path):
     assert batch.shape == (3, 17) and batch.dtype == torch.int64 and int(batch.max()) <= 256
     g2 = torch.Generator().manual_seed(0)
     assert torch.equal(batch, ds.sample_batch(3, 16, g2))
+
+
+def test_catalogued_workloads_resolve_to_local_files(tmp_path, capsys):
+    import pytest
+
+    from ep_balance_b200.launch.prepare_data import WORKLOADS
+
+    assert {"fineweb", "starcoder", "dolma", "pes2o", "dapo_math"} <= set(WORKLOADS)
+    assert main(["--list-workloads"])["workloads"] == sorted(WORKLOADS)
+    assert "bigcode/starcoderdata" in capsys.readouterr().out
+    raw = tmp_path / "raw"
+    raw.mkdir()
+    (raw / "fineweb.jsonl").write_text("\n".join(json.dumps({"text": f"web page {i} " * 4}) for i in range(8)) + "\n")
+    (raw / "starcoder.jsonl").write_text("\n".join(json.dumps({"text": f"def f{i}(): return {i}"}) for i in range(8)) + "\n")
+    meta = main(["--out", str(tmp_path / "mix"), "--workload", "fineweb", "--workload", "starcoder:3",
+                 "--raw-dir", str(raw), "--token-budget", "400"])
+    assert meta["sources"]["fineweb"]["budget"] == 100 and meta["sources"]["starcoder"]["budget"] == 300
+    with pytest.raises(SystemExit, match="--fetch dolma"):      # a catalogued workload whose file is not there
+        main(["--out", str(tmp_path / "x"), "--workload", "dolma", "--raw-dir", str(raw)])
+    with pytest.raises(SystemExit, match="unknown workload"):
+        main(["--out", str(tmp_path / "x"), "--workload", "nope", "--raw-dir", str(raw)])

@@ -90,3 +90,15 @@ def test_aux_loss_switch_changes_the_router_gradient():
     with torch.no_grad():
         layer.route_tokens(x)
     assert layer.aux_loss is None
+
+
+def test_shell_entry_points_parse():
+    """The launcher and the machine bootstrap are shell scripts: at least their syntax is checked here."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for script in ("run_train.sh", "bootstrap.sh"):
+        path = os.path.join(root, "ep_balance_b200", "launch", script)
+        assert os.access(path, os.X_OK), script
+        assert subprocess.run(["bash", "-n", path], capture_output=True).returncode == 0, script
