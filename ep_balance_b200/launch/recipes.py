@@ -11,6 +11,8 @@ RECIPES: Dict[str, Dict[str, int]] = {
     "glm45_air": dict(layers=46, hidden=4096, heads=96, ffn=1408, experts=128, top_k=8, shared=1),
     "gpt_moe_1b": dict(layers=16, hidden=2048, heads=16, ffn=1024, experts=64, top_k=8, shared=0),
     "dsv3_stack": dict(layers=4, hidden=7168, heads=128, ffn=2048, experts=256, top_k=8, shared=1),
+    # the reference's bring-up model (scripts/run_phaseB.sh, run_phaseC.sh: 4 layers, hidden 512, 8 experts, top-2)
+    "tiny": dict(layers=4, hidden=512, heads=8, ffn=512, experts=8, top_k=2, shared=0),
 }
 
 

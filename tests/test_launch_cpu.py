@@ -102,3 +102,15 @@ def test_shell_entry_points_parse():
         path = os.path.join(root, "ep_balance_b200", "launch", script)
         assert os.access(path, os.X_OK), script
         assert subprocess.run(["bash", "-n", path], capture_output=True).returncode == 0, script
+
+
+def test_bring_up_recipe_passes_preflight():
+    from ep_balance_b200.launch import recipes
+    from ep_balance_b200.launch.preflight import check
+
+    tiny = recipes.recipe("tiny")
+    assert (tiny["layers"], tiny["hidden"], tiny["experts"], tiny["top_k"]) == (4, 512, 8, 2)
+    for mode in ("observe", "apply"):
+        for nproc in (1, 2, 4, 8):
+            res = check({"MODEL": "tiny", "EPLB_MODE": mode}, nproc)
+            assert res.ok, (mode, nproc, res.errors)
