@@ -7,8 +7,8 @@ from ..parallel.comm import a2a_raw, all_to_all_single, broadcast_from_main
 from ..parallel.grouped_mlp import (check_row_budget, grouped_expert_mlp, make_batched_gated_mlp, make_grouped_gated_mlp,
                                     row_budget_status)
 from ..parallel.hooks import Dispatcher, NullWeightMaterializer, RebalanceResult, WeightMaterializer
-from ..parallel.library_path import (AllToAllAdapter, BroadcastReplicaTransport, CommAdapter, ReplicaTransport,
-                                     sync_free_moe_forward)
+from ..parallel.library_path import (AllToAllAdapter, BroadcastReplicaTransport, CommAdapter, PaddedAllToAllAdapter,
+                                     ReplicaTransport, sync_free_moe_forward)
 from ..parallel.physical import assign_physical, build_phys_slot_table
 from ..parallel.rebalancer import EPLBRebalancer
 from ..parallel.symm_weights import SymmReplicaTransport, SymmWeightReplicator, symm_weights_enabled

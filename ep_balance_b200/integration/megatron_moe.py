@@ -1,11 +1,14 @@
 """Apply mode for Megatron-Core: replace ``MoELayer.forward`` with the balanced dispatcher.
 
-Two transports are selectable with ``EPLB_ADAPTER``:
-  ``alltoall`` (default)  the portable path over NCCL (:mod:`ep_balance_b200.parallel.library_path`),
+Three transports are selectable with ``EPLB_ADAPTER``:
+  ``alltoall`` (default)  the portable path over NCCL (:mod:`ep_balance_b200.parallel.library_path`); reads
+                          the split sizes to the host once per chunk,
+  ``padded``              the portable path with fixed-size blocks per rank pair (``EPLB_PAIR_ROWS``): no
+                          host read at all, padding travels instead,
   ``fused``               the native B200 layer; the layer's experts are re-homed into symmetric
                           memory once, at bind time (:func:`bind_fused_moe_layer`).
 ``deepep`` is rejected: DeepEP's ElasticBuffer is not available in this build; its role (zero-sync
-token transport) is what ``fused`` provides.  Reference: eplb/integration/megatron_moe.py:19-260.
+token transport) is what ``padded`` (library collectives) and ``fused`` (device-initiated) provide.  Reference: eplb/integration/megatron_moe.py:19-260.
 """
 
 from __future__ import annotations
@@ -18,7 +21,7 @@ import torch
 import torch.distributed as dist
 
 from ..parallel.grouped_mlp import make_batched_gated_mlp, make_grouped_gated_mlp
-from ..parallel.library_path import AllToAllAdapter, sync_free_moe_forward
+from ..parallel.library_path import AllToAllAdapter, PaddedAllToAllAdapter, sync_free_moe_forward
 from ..parallel.omega import local_counts_from_routing
 from ..utils import profiling
 
@@ -38,10 +41,16 @@ def _make_adapter():
         return AllToAllAdapter()
     if name == "fused":
         return "fused"
+    if name == "padded":
+        rows = _env_positive("EPLB_PAIR_ROWS")
+        if rows is None:
+            raise ValueError("EPLB_ADAPTER=padded needs EPLB_PAIR_ROWS (rows every pair of ranks exchanges per chunk)")
+        return PaddedAllToAllAdapter(rows)
     if name in ("deepep", "deep_ep"):
         raise ValueError("EPLB_ADAPTER=deepep: DeepEP is not part of this build; use EPLB_ADAPTER=fused for the "
-                         "zero-sync device-initiated transport")
-    raise ValueError(f"unknown EPLB_ADAPTER={name!r} (expected 'alltoall' | 'fused')")
+                         "zero-sync device-initiated transport, or EPLB_ADAPTER=padded for the zero-sync transport on "
+                         "library collectives")
+    raise ValueError(f"unknown EPLB_ADAPTER={name!r} (expected 'alltoall' | 'padded' | 'fused')")
 
 
 def find_moe_layers(model, class_name: str = "MoELayer") -> List:

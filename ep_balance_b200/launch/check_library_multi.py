@@ -88,8 +88,13 @@ def main() -> int:
     ok = replicas > 0
     # every weight channel x every way of holding the replicas; on GPUs the token all-to-alls run on a comm
     # stream and the weight traffic on a stream (and, for broadcasts, a communicator) of its own
+    from ..parallel.library_path import PaddedAllToAllAdapter
+
     modes = {"held": dict(), "held, 2 chunks": dict(num_chunks=2), "leased, 2 chunks": dict(overlap=True, num_chunks=2),
-             "recomputed": dict(rematerialize=True)}
+             "recomputed": dict(rematerialize=True),
+             # fixed-size blocks per rank pair: no split size is read back from the device
+             "held, padded transport": dict(adapter=PaddedAllToAllAdapter(rows_per_pair=T)),
+             "leased, 2 chunks, padded transport": dict(overlap=True, num_chunks=2, adapter=PaddedAllToAllAdapter(rows_per_pair=T))}
     for channel in ("broadcast", "symm"):
         os.environ["EPLB_WEIGHT_COMM"] = channel
         for mode, kw in modes.items():

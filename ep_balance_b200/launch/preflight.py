@@ -20,7 +20,7 @@ from typing import Dict, List, Mapping, Optional
 from .recipes import RECIPES, recipe
 
 KNOWN_MODES = ("off", "observe", "apply")
-KNOWN_ADAPTERS = ("alltoall", "fused")
+KNOWN_ADAPTERS = ("alltoall", "padded", "fused")
 KNOWN_WEIGHT_COMM = ("broadcast", "symm")
 KNOWN_ROUTER_BALANCING = ("none", "aux_loss")
 # reference knobs that have no meaning in this build; setting them is an error rather than a silent no-op
@@ -121,7 +121,10 @@ def check(env: Mapping[str, str], nproc: int, *, shape: Optional[Dict[str, int]]
             if env.get(knob, "") not in ("", "0"):
                 out.warnings.append(f"{knob} only affects EPLB_ADAPTER=alltoall; the fused transport overlaps transfer "
                                     "and GEMM tiles inside its kernels and sizes its buffers from MoEConfig.capacity_factor")
-    if mode == "apply" and adapter == "alltoall":
+    if mode == "apply" and adapter == "padded" and _int(env, "EPLB_PAIR_ROWS", 0, out, 0) <= 0:
+        out.errors.append("EPLB_ADAPTER=padded needs EPLB_PAIR_ROWS: the rows every pair of ranks exchanges per chunk "
+                          "(blocks are fixed-size so that no split size is read back from the device)")
+    if mode == "apply" and adapter in ("alltoall", "padded"):
         wc = env.get("EPLB_WEIGHT_COMM", "broadcast").strip().lower() or "broadcast"
         if wc in ("gin", "nccl_gin", "devnccl"):
             wc = "symm"  # the reference's names for its device-initiated channel select ours

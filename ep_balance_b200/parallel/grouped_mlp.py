@@ -127,11 +127,11 @@ def row_budget_status(device) -> torch.Tensor:
     return words
 
 
-def _record_overflow(total_rows: torch.Tensor, max_rows: int) -> None:
+def _record_overflow(total_rows: torch.Tensor, max_rows: int, site: int = _ROW_BUDGET_SITE) -> None:
     words = row_budget_status(total_rows.device)
     total = total_rows.reshape(()).to(torch.int64)
     over = (total > max_rows) & (words[0, 0] == 0)          # the first overflow stays on record
-    hit = torch.stack([torch.full_like(total, 4), torch.full_like(total, _ROW_BUDGET_SITE),
+    hit = torch.stack([torch.full_like(total, 4), torch.full_like(total, site),
                        total.clamp(max=2 ** 31 - 1), torch.full_like(total, max_rows)]).to(torch.int32)
     words[0].copy_(torch.where(over, hit, words[0]))
 
@@ -147,7 +147,8 @@ def check_row_budget(device=None, clear: bool = True) -> None:
             if clear:
                 words.zero_()
             err = MoEStatusError(0, code, site, detail)
-            err.args = (f"{err.args[0]}: {detail} rows arrived, EPLB_MAX_RECV_ROWS holds {budget}",)
+            what = "EPLB_MAX_RECV_ROWS" if site == _ROW_BUDGET_SITE else "the padded transport's rows per rank pair"
+            err.args = (f"{err.args[0]}: {detail} rows arrived, {what} holds {budget}",)
             raise err
 
 

@@ -103,6 +103,73 @@ class AllToAllAdapter:
         return self._splits.pop(tag, None)
 
 
+class PaddedAllToAllAdapter:
+    """Zero-sync token transport on library collectives: every (source, destination) pair exchanges a block of
+    ``rows_per_pair`` rows, so every split size is a host constant and nothing is read back from the device.
+
+    The price is padding: ``R * rows_per_pair`` rows travel and are computed on, whatever the routing.  Rows of
+    a pair beyond the block are dropped and recorded in the row-budget status word (site 21), like every other
+    row budget of the portable path.  This is the contract the reference's DeepEP adapter fulfils with its
+    fixed-size buffers (eplb_manager.py ``CommAdapter.uses_padded_layout``; tests/test_sync_free.py:485-606 pin it
+    with a fake backend): received rows come as ``R`` aligned blocks with a validity mask instead of a ragged list.
+    """
+
+    ALIGN = 8  # rows per block are rounded up so that every block starts on a 16-byte multiple for any dtype
+
+    def __init__(self, rows_per_pair: int) -> None:
+        if int(rows_per_pair) <= 0:
+            raise ValueError("rows_per_pair must be positive")
+        self.cap = -(-int(rows_per_pair) // self.ALIGN) * self.ALIGN
+        self._state: Dict[int, dict] = {}
+
+    def uses_padded_layout(self) -> bool:
+        return True
+
+    def _splits(self, world: int) -> List[int]:
+        return [self.cap] * world
+
+    def dispatch_chunk(self, payload, sent_per_dst, recv_per_src, group, *, tag: int = 0):
+        from .grouped_mlp import _record_overflow
+
+        R, cap, n = int(sent_per_dst.numel()), self.cap, int(payload.shape[0])
+        ends = sent_per_dst.cumsum(0)
+        rows = torch.arange(n, device=payload.device)
+        dst = torch.searchsorted(ends, rows, right=True).clamp_(max=R - 1)      # payload is sorted by destination
+        pos = rows - (ends - sent_per_dst)[dst]
+        keep = pos < cap
+        flat = torch.where(keep, dst * cap + pos, torch.full_like(pos, R * cap))  # overflow rows go to a spare row
+        _record_overflow(sent_per_dst.max(), cap, site=21)
+        block = payload.new_zeros((R * cap + 1,) + tuple(payload.shape[1:])).index_copy(0, flat, payload)[:-1]
+        valid = (torch.arange(cap, device=payload.device)[None, :] < recv_per_src.clamp(max=cap)[:, None]).reshape(-1)
+        self._state[tag] = {"flat": flat, "keep": keep, "valid": valid, "R": R}
+        if R == 1 and not (dist.is_available() and dist.is_initialized()):
+            return block
+        return all_to_all_single(block, self._splits(R), self._splits(R), group)
+
+    def dispatch_ids(self, ids: torch.Tensor, group, *, tag: int = 0) -> torch.Tensor:
+        st = self._state[tag]
+        R, cap = st["R"], self.cap
+        block = ids.new_zeros(R * cap + 1).index_copy(0, st["flat"], ids)[:-1]
+        if R == 1 and not (dist.is_available() and dist.is_initialized()):
+            return block
+        return a2a_raw(block, self._splits(R), self._splits(R), group)
+
+    def valid_mask(self, tag: int = 0) -> torch.Tensor:
+        """Which of the ``R * cap`` received rows are real (block of source s holds ``recv_per_src[s]`` of them)."""
+        return self._state[tag]["valid"]
+
+    def combine_chunk(self, payload, sent_per_dst, recv_per_src, group, *, tag: int = 0):
+        st = self._state[tag]
+        R = st["R"]
+        back = payload if (R == 1 and not (dist.is_available() and dist.is_initialized())) else \
+            all_to_all_single(payload, self._splits(R), self._splits(R), group)
+        back = torch.cat([back, back.new_zeros((1,) + tuple(back.shape[1:]))])          # the spare row reads as zeros
+        return back.index_select(0, st["flat"])
+
+    def chunk_state(self, tag: int):
+        return self._state.pop(tag, None)
+
+
 class LocalAdapter(AllToAllAdapter):
     """World of one process without a process group: the all-to-all is the identity."""
 
@@ -272,7 +339,7 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
     distributed = dist.is_available() and dist.is_initialized()
     my_rank = dist.get_rank(group) if distributed else 0
     adapter = adapter or (AllToAllAdapter() if distributed else LocalAdapter())
-    if not distributed and not isinstance(adapter, LocalAdapter):
+    if not distributed and not isinstance(adapter, (LocalAdapter, PaddedAllToAllAdapter)):
         adapter = LocalAdapter()  # no process group: every transport degenerates to the identity
     device, dtype = tokens.device, tokens.dtype
     n_slot = int(spec.n_slot)
@@ -322,7 +389,7 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
         join_weights = join[0]
 
     # ---- all dispatches next (their reverse legs then run last in backward, after the reductions)
-    sent_l, recv_l, perm_l, rows_l, slot_l, arrived = [], [], [], [], [], []
+    sent_l, recv_l, perm_l, rows_l, slot_l, valid_l, arrived = [], [], [], [], [], [], []
     for k in range(n_chunks):
         lo, hi = bounds[k], bounds[k + 1]
         c_dst, c_phys = dst_rank[lo:hi], phys_id[lo:hi]
@@ -341,7 +408,11 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
                 recv_phys = adapter.dispatch_ids(ids, group, tag=k)
             # still on the comm lane: the received ids may be read only after their all-to-all
             recv_slot = recv_phys - my_rank * n_slot
-        _shared_between(comm_lane, device, payload, ids, sent, recv, rows, recv_phys, recv_slot)
+            valid = adapter.valid_mask(k) if adapter.uses_padded_layout() else None
+            if valid is not None:
+                recv_slot = torch.where(valid, recv_slot, torch.zeros_like(recv_slot))
+        _shared_between(comm_lane, device, payload, ids, sent, recv, rows, recv_phys, recv_slot, valid)
+        valid_l.append(valid)
         arrived.append(join[0])
         sent_l.append(sent)
         recv_l.append(recv)
@@ -350,11 +421,11 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
         slot_l.append(recv_slot)
 
     def compute_chunk(k: int):
-        sizes = torch.zeros(n_slot, dtype=torch.int64, device=device).scatter_add_(
-            0, slot_l[k], torch.ones_like(slot_l[k]))
+        ones = torch.ones_like(slot_l[k]) if valid_l[k] is None else valid_l[k].to(slot_l[k].dtype)
+        sizes = torch.zeros(n_slot, dtype=torch.int64, device=device).scatter_add_(0, slot_l[k], ones)
 
         def compute(x, stacks):
-            return grouped_expert_mlp(x, slot_l[k], sizes, stacks, batched_mlp_fn, cap=cap,
+            return grouped_expert_mlp(x, slot_l[k], sizes, stacks, batched_mlp_fn, cap=cap, valid_mask=valid_l[k],
                                       grouped_mlp_fn=grouped_mlp_fn, max_recv_rows=max_recv_rows)
 
         return compute
