@@ -222,11 +222,13 @@ def grouped_expert_mlp(recv_tokens: torch.Tensor, recv_slot: torch.Tensor, group
     cap = int(cap)
     slot = recv_slot.to(torch.int64)
     if valid_mask is not None:
+        # padding rows are ranked in a slot of their own so that they do not take positions of slot 0's real rows
+        pos = _position_in_slot(torch.where(valid_mask, slot, torch.full_like(slot, n_slot)), n_slot + 1)
         slot = torch.where(valid_mask, slot, torch.zeros_like(slot))
-    pos = _position_in_slot(slot, n_slot)
-    inside = pos < cap
-    if valid_mask is not None:
-        inside = inside & valid_mask
+        inside = (pos < cap) & valid_mask
+    else:
+        pos = _position_in_slot(slot, n_slot)
+        inside = pos < cap
     flat = torch.where(inside, slot * cap + pos, torch.full_like(slot, n_slot * cap))  # overflow row
     x_pad = recv_tokens.new_zeros((n_slot * cap + 1, H)).index_copy(0, flat, recv_tokens)
     with profiling.record("apply/expert_gemm", time_it=True, device=recv_tokens.device):

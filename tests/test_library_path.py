@@ -81,7 +81,8 @@ def _worker(rank, port, mode):
         assert adapter.uses_padded_layout() and adapter.cap % PaddedAllToAllAdapter.ALIGN == 0
     kw = dict(rematerialize=mode == "remat", overlap=mode in ("overlap", "overlap_chunks"), adapter=adapter,
               num_chunks=2 if mode in ("chunks", "overlap_chunks", "padded_transport_chunks") else None,
-              grouped_mlp_fn=None if mode == "padded" else make_grouped_gated_mlp(True, Fn.silu))
+              grouped_mlp_fn=None if mode in ("padded", "padded_transport_padded_experts")
+              else make_grouped_gated_mlp(True, Fn.silu))
     out = sync_free_moe_forward(tokens=tok, unit_token_idx=torch.arange(T), unit_expert=unit_expert[rank],
                                 unit_prob=pr, plan=plan, spec=spec, weights_local=weights_local,
                                 weight_shapes=[(2 * F, H), (H, F)],
@@ -106,7 +107,7 @@ def _worker(rank, port, mode):
 
 @pytest.mark.parametrize("mode,port", [("plain", 6121), ("padded", 6122), ("remat", 6123), ("overlap", 6124),
                                        ("chunks", 6125), ("overlap_chunks", 6126), ("padded_transport", 6127),
-                                       ("padded_transport_chunks", 6128)])
+                                       ("padded_transport_chunks", 6128), ("padded_transport_padded_experts", 6129)])
 def test_library_path_matches_single_process_truth(mode, port):
     mp.spawn(_worker, args=(port, mode), nprocs=W, join=True)
 
