@@ -108,6 +108,9 @@ def check(env: Mapping[str, str], nproc: int, *, shape: Optional[Dict[str, int]]
     out.resolved.update(mode=mode, adapter=adapter, domains=nproc // gpn if gpn and nproc % gpn == 0 else 1,
                         n_slot=n_slot, replica_slots=max(0, n_slot - home))
 
+    if _int(env, "NNODES", 1, out, 1) > 1 and adapter == "fused":
+        out.errors.append("NNODES > 1: the fused transport maps every rank's symmetric heap through CUDA IPC, which spans "
+                          "one node (one NVLink domain); use EPLB_ADAPTER=alltoall or padded across nodes")
     if mode == "apply" and adapter == "fused":
         if H % 64:
             out.errors.append(f"EPLB_ADAPTER=fused needs hidden % 64 == 0 (hidden={H}): the grouped GEMM moves 64-element k-blocks")

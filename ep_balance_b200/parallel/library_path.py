@@ -403,7 +403,9 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
                 dist.all_to_all_single(recv, sent, group=group)
             else:
                 recv = sent
-            with profiling.record("apply/dispatch", time_it=True, device=device):
+            # bytes this rank puts on the wire for the chunk (rows + ids); shows as MiB and GB/s in the debug line
+            with profiling.record("apply/dispatch", time_it=True, device=device,
+                                  payload_bytes=payload.numel() * payload.element_size() + ids.numel() * ids.element_size()):
                 rows = adapter.dispatch_chunk(payload, sent, recv, group, tag=k)
                 recv_phys = adapter.dispatch_ids(ids, group, tag=k)
             # still on the comm lane: the received ids may be read only after their all-to-all
@@ -455,7 +457,8 @@ def sync_free_moe_forward(tokens: torch.Tensor, unit_token_idx: torch.Tensor, un
             else:
                 y = compute(rows_l[k], stacks)
         with forked(comm_lane) as join:
-            with profiling.record("apply/combine", time_it=True, device=device):
+            with profiling.record("apply/combine", time_it=True, device=device,
+                                  payload_bytes=y.numel() * y.element_size()):
                 back = adapter.combine_chunk(y, sent_l[k], recv_l[k], group, tag=k)
         _shared_between(comm_lane, device, y, back)
         adapter.chunk_state(k)

@@ -114,3 +114,12 @@ def test_bring_up_recipe_passes_preflight():
         for nproc in (1, 2, 4, 8):
             res = check({"MODEL": "tiny", "EPLB_MODE": mode}, nproc)
             assert res.ok, (mode, nproc, res.errors)
+
+
+def test_preflight_knows_the_padded_adapter_and_refuses_the_fused_one_across_nodes():
+    from ep_balance_b200.launch.preflight import check
+
+    assert "EPLB_PAIR_ROWS" in " ".join(check({"EPLB_ADAPTER": "padded", "EPLB_MODE": "apply"}, 8).errors)
+    assert check({"EPLB_ADAPTER": "padded", "EPLB_MODE": "apply", "EPLB_PAIR_ROWS": "4096"}, 8).ok
+    assert "one node" in " ".join(check({"NNODES": "4"}, 8).errors)
+    assert check({"NNODES": "4", "EPLB_ADAPTER": "alltoall"}, 8).ok
