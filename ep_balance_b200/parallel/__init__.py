@@ -9,6 +9,8 @@
   comm.py           autograd-aware collectives
   physical.py       unit -> physical instance routing on host tensors
   grouped_mlp.py    grouped / padded expert MLP callbacks
-  library_path.py   portable apply path (gloo / NCCL)
+  library_path.py   portable apply path (gloo / NCCL): ragged and zero-sync padded token transports
+  overlap.py        comm / weight lanes of the portable path, weight lease, prefetch on backward
+  transport_model.py  host model of the fused layer's transport (buffer layout, items, arrival signals)
   health.py         host-side failure detection (heartbeats, step guard)
 """
