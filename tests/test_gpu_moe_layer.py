@@ -325,3 +325,30 @@ def test_backward_after_another_forward_is_refused():
     torch.cuda.synchronize()
     layer.check_status()
     assert b.grad is not None and torch.isfinite(b.grad.float()).all()
+
+
+def test_device_routing_tables_equal_the_host_model():
+    """row_base / send_off / tiles_of built by the solver kernel on 8 emulated ranks vs parallel/transport_model.py."""
+    from ep_balance_b200.models.emulated import EmulatedCluster
+    from ep_balance_b200.models.moe_layer import MoEConfig
+    from ep_balance_b200.parallel.transport_model import sender_tables
+
+    torch.manual_seed(1)
+    world, E, N, H = 8, 16, 256, 256
+    cfg = MoEConfig(hidden=H, ffn=256, num_experts=E, top_k=2, max_tokens=N, extra_slots=2, num_domains=2,
+                    capacity_factor=float(world))
+    cl = EmulatedCluster(cfg, world=world)
+    bias = torch.zeros(E, device="cuda")
+    bias[:3] = 3.0
+    for l in cl.layers:
+        l.router_bias = bias
+    cl.step([torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)],
+            [torch.randn(N, H, device="cuda").bfloat16() for _ in range(world)])
+    torch.cuda.synchronize()
+    plan = cl.layers[0].last_plan().to("cpu")
+    x, q = plan.x.to(torch.int64), plan.q.to(torch.int64)
+    assert int(x.sum()) > E
+    for r, layer in enumerate(cl.layers):
+        want = sender_tables(x, q, layer.spec.main_rank.cpu(), r, 128 * cfg.gemm_ctas)
+        for name in ("row_base", "send_off", "tiles_of"):
+            assert torch.equal(layer.loc[name].cpu().to(torch.int64), want[name]), (r, name)
