@@ -75,7 +75,7 @@ class MegatronEPLBHook:
             profiling.begin_debug_window()
         res = self.reb.rebalance(local_counts, layer_id, micro_batch_id, group=self.ep_group)
         self.last_plan = res.plan
-        omega = self.reb._omega_ring.get((int(layer_id), int(micro_batch_id)))
+        omega = self.reb.omega_of(layer_id, micro_batch_id)
         if self.logger is not None and omega is not None:
             self._log(res.plan, omega, layer_id, micro_batch_id)
         if self.trace is not None and omega is not None:

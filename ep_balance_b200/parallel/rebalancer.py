@@ -23,6 +23,32 @@ from .hooks import NullWeightMaterializer, RebalanceResult, WeightMaterializer
 from .omega import all_gather_omega
 
 
+class _StepRing:
+    """What backward needs from the last ``size`` (layer, micro-batch) steps: the load matrix, and the plan too when
+    plans are kept.  One ordered map of records; the oldest step leaves first."""
+
+    def __init__(self, size: int, keep_plans: bool) -> None:
+        self.size, self.keep_plans = int(size), bool(keep_plans)
+        self._steps: "OrderedDict[Tuple[int, int], Tuple[torch.Tensor, Optional[Plan]]]" = OrderedDict()
+
+    def put(self, key: Tuple[int, int], omega: torch.Tensor, plan: Plan) -> None:
+        if self.size <= 0:
+            return
+        self._steps[key] = (omega, plan if self.keep_plans else None)
+        self._steps.move_to_end(key)
+        while len(self._steps) > self.size:
+            self._steps.popitem(last=False)
+
+    def get(self, key: Tuple[int, int]) -> Optional[Tuple[torch.Tensor, Optional[Plan]]]:
+        return self._steps.get(key)
+
+    def clear(self) -> None:
+        self._steps.clear()
+
+    def __len__(self) -> int:
+        return len(self._steps)
+
+
 class EPLBRebalancer:
     def __init__(self, topo: Topology, spec: ProblemSpec, cfg: Optional[EPLBConfig] = None,
                  materializer: Optional[WeightMaterializer] = None, *, cache_plans: bool = False,
@@ -32,11 +58,8 @@ class EPLBRebalancer:
         self.topo, self.spec = topo, spec
         self.cfg = cfg or EPLBConfig()
         self.materializer = materializer or NullWeightMaterializer()
-        self.cache_plans = bool(cache_plans)
-        self.ring_size = int(ring_size)
-        # insertion-ordered: the oldest (layer, mb) is evicted first
-        self._omega_ring: "OrderedDict[Tuple[int, int], torch.Tensor]" = OrderedDict()
-        self._plan_ring: dict = {}
+        self.cache_plans, self.ring_size = bool(cache_plans), int(ring_size)
+        self._ring = _StepRing(self.ring_size, self.cache_plans)
 
     # ---- forward ----------------------------------------------------------
     def plan_from_omega(self, loads: Loads) -> Plan:
@@ -45,8 +68,9 @@ class EPLBRebalancer:
 
     def rebalance_from_omega(self, loads: Loads, layer_id: int, micro_batch_id: int) -> RebalanceResult:
         plan = self.plan_from_omega(loads)
-        self._remember(layer_id, micro_batch_id, loads.omega, plan)
-        return RebalanceResult(plan, self.materializer.materialize(plan, layer_id, micro_batch_id))
+        self._ring.put((int(layer_id), int(micro_batch_id)), loads.omega, plan)
+        handle = self.materializer.materialize(plan, layer_id, micro_batch_id)
+        return RebalanceResult(plan, handle)
 
     def rebalance(self, local_row: torch.Tensor, layer_id: int, micro_batch_id: int, *, group=None) -> RebalanceResult:
         with profiling.record("all_gather_omega", time_it=True, device=local_row.device):
@@ -55,28 +79,22 @@ class EPLBRebalancer:
 
     # ---- backward ---------------------------------------------------------
     def backward(self, layer_id: int, micro_batch_id: int) -> Plan:
-        key = (int(layer_id), int(micro_batch_id))
-        plan = self._plan_ring.get(key) if self.cache_plans else None
+        """The forward's plan of that step (kept, or solved again from the kept load matrix: the solvers are
+        deterministic), after telling the materializer to fold the replicas' gradients."""
+        step = self._ring.get((int(layer_id), int(micro_batch_id)))
+        if step is None:
+            raise KeyError(f"no cached Ω for (layer={layer_id}, mb={micro_batch_id}); "
+                           f"increase ring_size (current={self.ring_size})")
+        omega, plan = step
         if plan is None:
-            if key not in self._omega_ring:
-                raise KeyError(f"no cached Ω for (layer={layer_id}, mb={micro_batch_id}); "
-                               f"increase ring_size (current={self.ring_size})")
-            plan = self.plan_from_omega(Loads(self._omega_ring[key]))
+            plan = self.plan_from_omega(Loads(omega))
         self.materializer.aggregate_gradients(plan, layer_id, micro_batch_id)
         return plan
 
-    # ---- ring -------------------------------------------------------------
-    def _remember(self, layer_id: int, micro_batch_id: int, omega: torch.Tensor, plan: Plan) -> None:
-        if self.ring_size <= 0:
-            return
-        key = (int(layer_id), int(micro_batch_id))
-        self._omega_ring[key] = omega
-        if self.cache_plans:
-            self._plan_ring[key] = plan
-        while len(self._omega_ring) > self.ring_size:
-            old, _ = self._omega_ring.popitem(last=False)
-            self._plan_ring.pop(old, None)
+    def omega_of(self, layer_id: int, micro_batch_id: int) -> Optional[torch.Tensor]:
+        """The load matrix the plan of that step was solved from, while the step is still remembered."""
+        step = self._ring.get((int(layer_id), int(micro_batch_id)))
+        return None if step is None else step[0]
 
     def clear(self) -> None:
-        self._omega_ring.clear()
-        self._plan_ring.clear()
+        self._ring.clear()
